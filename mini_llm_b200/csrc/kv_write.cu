@@ -1,0 +1,45 @@
+// Copies the step's keys and values into their page slots.
+// Source rows are column ranges of the fused QKV buffer (row stride given);
+// destination layout per layer is [page][kv_head][offset][head_dim], so one
+// (page, head) is one contiguous chunk.  slot = page * page_size + offset, the
+// reference's token_to_block/token_to_offset pair merged
+// (src/kernels/prefill/append_kv.cu:28-46; src/model/gpt2_model.cu:225-231).
+#include "common.cuh"
+
+template <typename T>
+__global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v, long long row_stride,
+                                T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                const int* __restrict__ slots, int Hkv, int dh, int page_size) {
+    const int t = blockIdx.x;
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int page = slot / page_size, off = slot % page_size;
+    const T* ks = k + (size_t)t * row_stride;
+    const T* vs = v + (size_t)t * row_stride;
+    const int n = Hkv * dh;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int h = i / dh, d = i % dh;
+        const size_t dst = (((size_t)page * Hkv + h) * page_size + off) * dh + d;
+        k_pages[dst] = ks[i];
+        v_pages[dst] = vs[i];
+    }
+}
+
+MLLM_EXPORT int mllm_kv_write(const void* k, const void* v, long long row_stride, void* k_pages, void* v_pages,
+                              const int* slots, int T, int Hkv, int dh, int page_size, int dtype,
+                              cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const int n = Hkv * dh;
+    int threads = n >= 256 ? 256 : ((n + 31) / 32) * 32;
+    if (dtype == MLLM_F32)
+        kv_write_kernel<float><<<T, threads, 0, stream>>>((const float*)k, (const float*)v, row_stride,
+                                                          (float*)k_pages, (float*)v_pages, slots, Hkv, dh, page_size);
+    else if (dtype == MLLM_BF16)
+        kv_write_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
+            (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, row_stride, (__nv_bfloat16*)k_pages,
+            (__nv_bfloat16*)v_pages, slots, Hkv, dh, page_size);
+    else
+        return mllm_fail(1, "kv_write: unknown dtype code %d", dtype);
+    MLLM_CHECK_LAUNCH("kv_write");
+    return 0;
+}

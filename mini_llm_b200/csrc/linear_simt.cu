@@ -1,0 +1,133 @@
+// out = act(A[M,K] . W[N,K]^T + bias[N]) (+ out): the plain matrix product of the
+// engine, on CUDA cores with 32-bit FMA accumulation.
+//
+// It is the whole product path of the true 32-bit mode (float operands: no tensor
+// core, no reduced-precision matrix mode) and the plain twin that the tensor-core
+// kernels are tested against (bfloat16 operands widened to 32-bit).  Both operands
+// are read along K, the layout every weight is brought to at load, so the tied head
+// uses the embedding table as it is; the reference multiplies row-major [K,N]
+// weights with its own SGEMM tiles (src/kernels/gemm.cu:238-392) and fuses the same
+// epilogues: bias (src/kernels/linear.cu:8-26), bias+GELU (:48-66), bias+residual as
+// beta=1 (:28-46).
+//
+// The sum over K of one output element always runs in the same order (K tiles in
+// sequence, no split over K), so a row's result does not depend on M or on the rows
+// beside it.
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+constexpr int THREADS = (BM / TM) * (BN / TN);   // 256
+constexpr int PAD = 4;
+
+template <typename T>
+__device__ __forceinline__ void load4(const T* __restrict__ base, long long ld, int row, int nrows, int k, int K,
+                                      bool vec, float (&v)[4]) {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (row >= nrows) return;
+    const T* p = base + (size_t)row * ld + k;
+    if (vec && k + 3 < K) {
+        if constexpr (sizeof(T) == 4) {
+            const float4 f = *reinterpret_cast<const float4*>(p);
+            v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+        } else {
+            const uint2 u = *reinterpret_cast<const uint2*>(p);
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x);
+            const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+            v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (k + i < K) v[i] = to_f32(p[i]);
+    }
+}
+
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(THREADS)
+linear_simt_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, const float* __restrict__ bias,
+                   TO* out, long long ldo, int M, int N, int K, int act, int accumulate, int vecA, int vecW) {
+    __shared__ float As[BK][BM + PAD];
+    __shared__ float Ws[BK][BN + PAD];
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int lrow = tid / 4, lk = (tid % 4) * 4;      // 64 rows x 16 k: 4 consecutive k per thread
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        float a[4], w[4];
+        load4<TA>(A, lda, m0 + lrow, M, k0 + lk, K, vecA != 0, a);
+        load4<TW>(W, (long long)K, n0 + lrow, N, k0 + lk, K, vecW != 0, w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            As[lk + i][lrow] = a[i];
+            Ws[lk + i][lrow] = w[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            const float4 av = *reinterpret_cast<const float4*>(&As[k][ty * TM]);
+            const float4 wv = *reinterpret_cast<const float4*>(&Ws[k][tx * TN]);
+            const float ar[4] = {av.x, av.y, av.z, av.w};
+            const float wr[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(ar[i], wr[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int m = m0 + ty * TM + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (bias) v += bias[n];
+            v = apply_act(v, act);
+            TO* o = out + (size_t)m * ldo + n;
+            if (accumulate) v += to_f32(*o);
+            *o = from_f32<TO>(v);
+        }
+    }
+}
+
+template <typename TA, typename TW, typename TO>
+int launch(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo, int M, int N,
+           int K, int act, int accumulate, cudaStream_t stream) {
+    const bool vecA = ((uintptr_t)A % (4 * sizeof(TA)) == 0) && (lda % 4 == 0);
+    const bool vecW = ((uintptr_t)W % (4 * sizeof(TW)) == 0) && (K % 4 == 0);
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    linear_simt_kernel<TA, TW, TO><<<grid, THREADS, 0, stream>>>(
+        (const TA*)A, lda, (const TW*)W, bias, (TO*)out, ldo, M, N, K, act, accumulate, vecA, vecW);
+    MLLM_CHECK_LAUNCH("linear_simt");
+    return 0;
+}
+
+}  // namespace
+
+// in_dtype: dtype of A and W; out_dtype: dtype of out.
+MLLM_EXPORT int mllm_linear_simt(const void* A, long long lda, const void* W, const float* bias, void* out,
+                                 long long ldo, int M, int N, int K, int act, int accumulate, int in_dtype,
+                                 int out_dtype, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0) return mllm_fail(1, "linear: K=%d", K);
+    if ((M + BM - 1) / BM > 65535) return mllm_fail(1, "linear: M=%d exceeds the grid limit of this kernel", M);
+    using bf = __nv_bfloat16;
+    if (in_dtype == MLLM_F32 && out_dtype == MLLM_F32)
+        return launch<float, float, float>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+    if (in_dtype == MLLM_BF16 && out_dtype == MLLM_BF16)
+        return launch<bf, bf, bf>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+    if (in_dtype == MLLM_BF16 && out_dtype == MLLM_F32)
+        return launch<bf, bf, float>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+    return mllm_fail(1, "linear: unsupported dtype pair in=%d out=%d", in_dtype, out_dtype);
+}

@@ -1,0 +1,212 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+The reference has two entry points, GPT2Model::prefill for whole prompts from
+position 0 (src/model/gpt2_model.cu:367-453) and GPT2Model::decode for one token
+per request (:455-689), never mixed.  ``ModelRunner.step`` takes any mix: portions
+of prompts of any length beside single decoded tokens.  It runs only the tokens
+it is given, reads everything older from the cache, and returns the logits at
+the wanted places.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache.manager import CacheManager
+from ..config.base import EngineConfig, ModelConfig, get_architecture, load_config
+from ..parts.model import Model
+from ..weights.loader import load_weights
+from .context import StepContext, StepLayout, Workspace, pack_step
+
+
+class StepError(RuntimeError):
+    pass
+
+
+class OutOfPages(StepError):
+    """The cache has no pages left for the tokens of this step."""
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and where logits are wanted."""
+
+    req: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)     # indices into ``tokens``
+
+
+@dataclass
+class Runtime:
+    dtype: torch.dtype
+    device: torch.device
+    ops: object = ops
+
+    @property
+    def act_dtype(self) -> torch.dtype:
+        return self.dtype
+
+
+def _element_size(dtype: torch.dtype) -> int:
+    return torch.empty((), dtype=dtype).element_size()
+
+
+class ModelRunner:
+    def __init__(self, model_dir: str, engine: Optional[EngineConfig] = None):
+        self.engine = engine or EngineConfig()
+        if not torch.cuda.is_available():
+            raise StepError("no CUDA device: this engine has no CPU path")
+        self.device = torch.device(self.engine.device)
+        torch.cuda.set_device(self.device)
+        ops.library()       # build/load now: fail early and loudly
+        self.config: ModelConfig = load_config(model_dir)
+        arch = get_architecture(self.config.architecture)
+        self.spec = arch.build_spec(self.config)
+        self.rt = Runtime(dtype=torch.bfloat16 if self.engine.dtype == "bfloat16" else torch.float32,
+                          device=self.device)
+        self.model = Model(self.spec)
+        load_weights(self.model, self.spec, model_dir, self.rt)
+        self.vocab_size = self.spec.vocab_size
+        self.max_positions = self.spec.max_positions
+        self._make_cache()
+        self.model.prepare(self.cache)
+        self.ws = Workspace(self.device, self.engine.max_num_batched_tokens)
+        self._host = [None, None]
+        self._host_events = [None, None]
+        self._host_turn = 0
+        self._dev: Optional[torch.Tensor] = None
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ set-up
+    def _make_cache(self) -> None:
+        e = self.engine
+        needs = self.model.layer_needs()
+        probe = CacheManager(needs, page_size=e.page_size, num_pages=0, max_num_seqs=1, allocate=False)
+        es = _element_size(self.rt.dtype)
+        if e.num_pages is not None:
+            num_pages = int(e.num_pages)
+        elif e.max_tokens is not None:
+            num_pages = (int(e.max_tokens) + e.page_size - 1) // e.page_size
+        else:
+            per_token = sum(g.bytes_per_token(es) for g in probe.groups) or 1
+            free, _ = torch.cuda.mem_get_info(self.device)
+            tokens = int(free * e.memory_fraction) // per_token
+            limit = e.max_num_seqs * (self.max_positions or 1 << 20)
+            tokens = max(e.page_size, min(tokens, limit))
+            num_pages = (tokens + e.page_size - 1) // e.page_size
+        self.cache = CacheManager(needs, page_size=e.page_size, num_pages=num_pages, max_num_seqs=e.max_num_seqs,
+                                  dtype=self.rt.dtype, device=self.device)
+        self.num_pages = num_pages
+
+    def _staging(self, n: int):
+        i = self._host_turn
+        self._host_turn ^= 1
+        if self._host[i] is None or self._host[i].numel() < n:
+            cap = max(4096, 1 << (n - 1).bit_length())
+            self._host[i] = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            self._host_events[i] = torch.cuda.Event()
+        else:
+            self._host_events[i].synchronize()      # the copy that last used this buffer is done
+        if self._dev is None or self._dev.numel() < n:
+            cap = max(4096, 1 << (n - 1).bit_length())
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self.ws.version += 1
+        return i, self._host[i]
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, req) -> None:
+        self.cache.admit(req)
+
+    def has_request(self, req) -> bool:
+        return self.cache.is_live(req)
+
+    def finish_request(self, req) -> None:
+        self.cache.release(req)
+
+    def computed(self, req) -> int:
+        return self.cache.computed(req)
+
+    # ------------------------------------------------------------------ the step
+    def prepare_step(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Reserve pages, pack the step's integers, start their copy to the device."""
+        cm = self.cache
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        for en in entries:
+            if en.req in seen:
+                raise StepError(f"request {en.req!r} appears twice in one step")
+            seen.add(en.req)
+            if not cm.is_live(en.req):
+                raise StepError(f"request {en.req!r} is not live (add_request first)")
+            n = len(en.tokens)
+            if n == 0:
+                raise StepError(f"request {en.req!r} brings no tokens")
+            start = cm.computed(en.req)
+            if self.max_positions is not None and start + n > self.max_positions:
+                raise StepError(f"request {en.req!r}: {start + n} tokens exceed the model's {self.max_positions} positions")
+            for t in en.tokens:
+                if not (0 <= int(t) < self.vocab_size):
+                    raise StepError(f"request {en.req!r}: token id {t} is outside the vocabulary of {self.vocab_size}")
+            for w in en.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"request {en.req!r}: wanted place {w} is outside its {n} tokens")
+        reserved = []
+        for en in entries:
+            if not cm.reserve(en.req, len(en.tokens)):
+                raise OutOfPages(f"no pages left for {len(en.tokens)} tokens of request {en.req!r} "
+                                 f"({[g.allocator.num_free for g in cm.groups]} free)")
+            reserved.append(en.req)
+        token_ids: List[int] = []
+        positions: List[int] = []
+        token_seq: List[int] = []
+        logit_rows: List[int] = []
+        cu_q = [0]
+        q_start, ctx_len, slots, q_lens = [], [], [], []
+        ng = len(cm.groups)
+        slot_maps: List[List[int]] = [[] for _ in range(ng)]
+        tables: List[List[List[int]]] = [[] for _ in range(ng)]
+        for s, en in enumerate(entries):
+            n = len(en.tokens)
+            start = cm.computed(en.req)
+            base = len(token_ids)
+            token_ids.extend(int(t) for t in en.tokens)
+            positions.extend(range(start, start + n))
+            token_seq.extend([s] * n)
+            logit_rows.extend(base + int(w) for w in en.want)
+            cu_q.append(base + n)
+            q_start.append(start)
+            ctx_len.append(start + n)
+            q_lens.append(n)
+            slots.append(cm.slot(en.req))
+            for g in range(ng):
+                slot_maps[g].extend(cm.slots_for(en.req, g, start, n))
+                tables[g].append(cm.table(en.req, g))
+        max_pages = []
+        for g in range(ng):
+            mp = max(len(t) for t in tables[g])
+            max_pages.append(max(8, (mp + 7) // 8 * 8))
+        layout = StepLayout.make(len(token_ids), len(entries), len(logit_rows), max_pages)
+        i, host = self._staging(layout.total)
+        pack_step(layout, host.numpy(), token_ids=token_ids, positions=positions, token_seq=token_seq,
+                  logit_rows=logit_rows, state_slots=slots, cu_q=cu_q, q_start=q_start, ctx_len=ctx_len,
+                  slot_mappings=slot_maps, block_tables=tables)
+        self._dev[:layout.total].copy_(host[:layout.total], non_blocking=True)
+        self._host_events[i].record()
+        return StepContext(layout, self._dev, self.ws, q_lens=q_lens, q_starts=q_start)
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch; returns 32-bit logits [number of wanted places, vocab] in the
+        order of the entries and of each entry's ``want`` (a view that the next step
+        overwrites), or None if nothing was wanted."""
+        ctx = self.prepare_step(entries)
+        logits = self.model.forward(ctx)
+        for en in entries:
+            self.cache.commit(en.req, len(en.tokens))
+        self.steps_run += 1
+        return logits

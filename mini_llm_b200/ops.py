@@ -1,0 +1,240 @@
+"""The kernel library: the Python face of the CUDA sources in ``csrc/``.
+
+Every function checks its arguments (device, dtype, layout, sizes the kernel can
+take) and then calls one exported C function with raw device pointers and the
+current CUDA stream.  There is no CPU fallback and no library attention or model
+code behind these names: if the shared library cannot be built or loaded, or a
+tensor is not on a CUDA device, the call fails with an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+_ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}
+_lib = None
+
+c_int, c_ll, c_float, c_void_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _signatures(lib):
+    lib.mllm_last_error.restype = ctypes.c_char_p
+    lib.mllm_abi_version.restype = c_int
+    sig = {
+        "mllm_embed": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mllm_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+        "mllm_kv_write": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                          c_void_p],
+        "mllm_linear_simt": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_void_p],
+        "mllm_attention_simt": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                c_ll, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+        "mllm_argmax": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
+        "mllm_sample": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    }
+    for name, args in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = c_int
+
+
+def library():
+    """The loaded shared library; built on first use."""
+    global _lib
+    if _lib is None:
+        path = _build.ensure_built()
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load the kernel library {path}: {e}") from e
+        _signatures(lib)
+        _lib = lib
+    return _lib
+
+
+def is_loaded() -> bool:
+    return _lib is not None
+
+
+def _call(name: str, *args) -> None:
+    lib = library()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise KernelError(f"{name}: {lib.mllm_last_error().decode(errors='replace')}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported dtype {t.dtype}: kernels take float32 and bfloat16")
+
+
+def _cuda(name: str, t: torch.Tensor, dtype=None, contiguous=True):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    return t
+
+
+def _rows(name: str, t: torch.Tensor):
+    """A 2-D tensor whose rows are contiguous; returns its row stride in elements."""
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{name} must be 2-D with contiguous rows, got shape {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+# --------------------------------------------------------------------------- embedding
+def embed(ids, positions, table, pos_table, out) -> None:
+    """out[t] = table[ids[t]] (+ pos_table[positions[t]]), 32-bit."""
+    _cuda("ids", ids, torch.int32)
+    _cuda("table", table)
+    _cuda("out", out, torch.float32)
+    T, D = out.shape
+    if ids.numel() != T or table.shape[1] != D:
+        raise KernelError(f"embed: {ids.numel()} ids, table {tuple(table.shape)}, out {tuple(out.shape)}")
+    pp = None
+    if pos_table is not None:
+        _cuda("positions", positions, torch.int32)
+        _cuda("pos_table", pos_table, table.dtype)
+        if pos_table.shape[1] != D or positions.numel() != T:
+            raise KernelError("embed: position table or positions do not fit")
+        pp = pos_table.data_ptr()
+    _call("mllm_embed", ids.data_ptr(), positions.data_ptr() if pos_table is not None else None,
+          table.data_ptr(), pp, out.data_ptr(), T, D, _dt(table), _stream())
+
+
+# --------------------------------------------------------------------------- norm
+def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
+    """out[r] = LayerNorm(x[rows[r]] or x[r]); x 32-bit, out 32-bit or bfloat16."""
+    _cuda("x", x, torch.float32)
+    _cuda("gamma", gamma, torch.float32)
+    _cuda("beta", beta, torch.float32)
+    _cuda("out", out)
+    D = x.shape[1]
+    R = out.shape[0]
+    if gamma.numel() != D or beta.numel() != D or out.shape[1] != D:
+        raise KernelError(f"layernorm: width {D} against gamma {gamma.numel()}, out {tuple(out.shape)}")
+    if rows is not None:
+        _cuda("rows", rows, torch.int32)
+        if rows.numel() != R:
+            raise KernelError("layernorm: rows and out differ in length")
+    elif x.shape[0] != R:
+        raise KernelError("layernorm: x and out differ in rows")
+    _call("mllm_layernorm", x.data_ptr(), rows.data_ptr() if rows is not None else None, gamma.data_ptr(),
+          beta.data_ptr(), out.data_ptr(), R, D, float(eps), _dt(out), _stream())
+
+
+# --------------------------------------------------------------------------- linear
+def linear(x, weight, bias, out, act: Optional[str] = None, accumulate: bool = False, impl: Optional[str] = None):
+    """out = act(x @ weight^T + bias) (+ out when ``accumulate``).
+
+    x [M,K] rows contiguous (a column slice is fine), weight [N,K] contiguous, bias
+    [N] 32-bit or None, out [M,N] rows contiguous.  float32 operands run the true
+    32-bit FMA kernel; bfloat16 operands accumulate in 32-bit.
+    """
+    _cuda("x", x, contiguous=False)
+    _cuda("weight", weight, x.dtype)
+    _cuda("out", out, contiguous=False)
+    lda = _rows("x", x)
+    ldo = _rows("out", out)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"linear: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _cuda("bias", bias, torch.float32)
+        if bias.numel() != N:
+            raise KernelError("linear: bias length")
+    if act not in _ACT:
+        raise KernelError(f"linear: unknown activation {act!r}")
+    if x.dtype == torch.float32 and out.dtype != torch.float32:
+        raise KernelError("linear: float32 operands need a float32 result")
+    _call("mllm_linear_simt", x.data_ptr(), lda, weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+          out.data_ptr(), ldo, M, N, K, _ACT[act], int(accumulate), _dt(x), _dt(out), _stream())
+    return out
+
+
+# --------------------------------------------------------------------------- cache
+def kv_write(k, v, k_pages, v_pages, slot_mapping) -> None:
+    """Copy rows of k and v ([T, kv_heads*head_dim], same row stride) to their slots."""
+    _cuda("k", k, contiguous=False)
+    _cuda("v", v, k.dtype, contiguous=False)
+    _cuda("k_pages", k_pages, k.dtype)
+    _cuda("v_pages", v_pages, k.dtype)
+    _cuda("slot_mapping", slot_mapping, torch.int32)
+    ld = _rows("k", k)
+    if _rows("v", v) != ld:
+        raise KernelError("kv_write: k and v differ in row stride")
+    _, Hkv, ps, dh = k_pages.shape
+    T = k.shape[0]
+    if k.shape[1] != Hkv * dh or slot_mapping.numel() != T or v_pages.shape != k_pages.shape:
+        raise KernelError("kv_write: shapes do not fit the pages")
+    _call("mllm_kv_write", k.data_ptr(), v.data_ptr(), ld, k_pages.data_ptr(), v_pages.data_ptr(),
+          slot_mapping.data_ptr(), T, Hkv, dh, ps, _dt(k), _stream())
+
+
+def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, num_kv_heads, head_dim, scale,
+                    window=None, impl: Optional[str] = None) -> None:
+    """Causal attention of the step's tokens over the cache.
+
+    q [T, heads*head_dim] (rows contiguous), pages [num_pages, kv_heads, page_size,
+    head_dim], block_table [S, max_pages] int32, ctx.token_seq / ctx.positions [T].
+    """
+    _cuda("q", q, contiguous=False)
+    _cuda("k_pages", k_pages, q.dtype)
+    _cuda("v_pages", v_pages, q.dtype)
+    _cuda("out", out, q.dtype, contiguous=False)
+    _cuda("block_table", block_table, torch.int32, contiguous=False)
+    ldq = _rows("q", q)
+    ldo = _rows("out", out)
+    T = q.shape[0]
+    _, Hkv, ps, dh = k_pages.shape
+    if Hkv != num_kv_heads or dh != head_dim or q.shape[1] != num_heads * head_dim:
+        raise KernelError("paged_attention: head counts or sizes do not fit the pages")
+    if head_dim % 16 != 0 or not (16 <= head_dim <= 256):
+        raise KernelError(f"paged_attention: head size {head_dim} is not a multiple of 16 in 16..256")
+    bt_stride = _rows("block_table", block_table)
+    _call("mllm_attention_simt", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+          bt_stride, ctx.token_seq.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), ldo, T, num_heads,
+          num_kv_heads, head_dim, ps, float(scale), int(window or 0), _dt(q), _stream())
+
+
+# --------------------------------------------------------------------------- sampling
+def argmax(logits, out) -> None:
+    _cuda("logits", logits, torch.float32, contiguous=False)
+    _cuda("out", out, torch.int32)
+    ld = _rows("logits", logits)
+    R, V = logits.shape
+    _call("mllm_argmax", logits.data_ptr(), ld, R, V, out.data_ptr(), _stream())
+
+
+def sample(logits, temperature, uniform, out) -> None:
+    """Per row: argmax if temperature == 0, else an inverse-CDF draw with uniform[r]."""
+    _cuda("logits", logits, torch.float32, contiguous=False)
+    _cuda("temperature", temperature, torch.float32)
+    _cuda("uniform", uniform, torch.float32)
+    _cuda("out", out, torch.int32)
+    ld = _rows("logits", logits)
+    R, V = logits.shape
+    if temperature.numel() != R or uniform.numel() != R or out.numel() != R:
+        raise KernelError("sample: per-row arguments differ in length")
+    _call("mllm_sample", logits.data_ptr(), ld, R, V, temperature.data_ptr(), uniform.data_ptr(), out.data_ptr(),
+          _stream())
