@@ -1,0 +1,319 @@
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step: every live request gets one more token.  The default
+run is GPT-2 small (n_layer 12, n_embd 768, n_head 12, n_inner 3072, vocab 50257,
+n_positions 1024) with seeded random weights in bfloat16, a batch of 8 requests with
+512-token random prompts, page size 16.  It prints ONE JSON line:
+
+  value       decoded tokens per second over exactly K steps, timed on the device
+              with CUDA events (forward pass + on-device argmax per step);
+  e2e         the same through the Python entry point (LLM.step): host token ids in,
+              sampled ids back on the host every step;
+  prefill     2,048 prompt tokens (2 x 1024) in one step: tokens/s, ms, and the share
+              of the bf16 tensor peak its flops reach;
+  roofline    bytes the decode step has to read (every weight once + the cache of the
+              live requests) / its time, against the HBM copy bandwidth;
+  points      decode tokens/s at batch 1 and 64.
+
+Peaks come from MEASURED_PEAKS.json beside this file when present, else from the
+fallback figures 6.65 TB/s and 1.59 PFLOP/s ("peaks": "fallback").
+The reference arm (taejuk/mini-llm itself) is not installable with pip: it is a CMake
+C++/CUDA project without Python packaging, so ``--impl reference`` reports unavailable.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SMALL = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=12, n_embd=768, n_head=12, n_inner=3072,
+             vocab_size=50257, n_positions=1024, layer_norm_epsilon=1e-5, activation_function="gelu_new",
+             eos_token_id=50256)
+PROMPT_LEN = 512
+PREFILL_TOKENS = 2048
+PAGE = 16
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        try:
+            d = json.load(open(p))
+            hbm = float(d.get("hbm_gbs") or d.get("hbm_gb_s") or 0)
+            bf = float(d.get("bf16_tflops") or 0)
+            sus = float(d.get("bf16_tflops_sustained") or bf)
+            if hbm > 0 and bf > 0:
+                return dict(hbm_gbs=hbm, bf16_tflops=bf, bf16_tflops_sustained=sus, source="measured")
+        except Exception:
+            pass
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.p = None
+
+    def _read(self):
+        for line in self.p.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            pass
+        mhz = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = max((int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()), default=None)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": reasons,
+                "samples": len(mhz)}
+
+
+def weight_bytes(runner) -> int:
+    seen, total = set(), 0
+    for label, _ in runner.spec.all_part_specs():
+        part = runner.model.part(label)
+        for name in part.param_specs():
+            t = getattr(part, name)
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+    return total
+
+
+def decode_bytes(runner, cfg, batch, mean_ctx) -> float:
+    """What one decode step must read: every weight once (of the position table only the
+    rows used) and the keys and values of the live requests."""
+    es = 2 if runner.engine.dtype == "bfloat16" else 4
+    w = weight_bytes(runner) - cfg["n_positions"] * cfg["n_embd"] * es + batch * cfg["n_embd"] * es
+    kv = batch * mean_ctx * cfg["n_layer"] * 2 * cfg["n_embd"] * es
+    return float(w + kv)
+
+
+def prefill_flops(cfg, lens, rows) -> float:
+    L, D, F, V = cfg["n_layer"], cfg["n_embd"], cfg["n_inner"], cfg["vocab_size"]
+    T = sum(lens)
+    linear = 2.0 * T * L * (3 * D * D + D * D + 2 * D * F) + 2.0 * rows * D * V
+    attn = sum(4.0 * (n * (n + 1) / 2) * D * L for n in lens)
+    return linear + attn
+
+
+def run_decode(model_dir, dtype, batch, steps, warmup, sample_clocks=False):
+    """Device-timed decode: K steps of (forward + argmax) on ``batch`` live requests."""
+    import torch
+    import mini_llm_b200 as m
+    from mini_llm_b200 import ops
+    from mini_llm_b200.config.base import EngineConfig
+    from mini_llm_b200.engine.runner import ModelRunner, StepEntry
+
+    cfg = json.load(open(os.path.join(model_dir, "config.json")))
+    eng = EngineConfig(dtype=dtype, page_size=PAGE, max_tokens=batch * cfg["n_positions"], max_num_seqs=max(batch, 1),
+                       max_num_batched_tokens=max(2048, batch))
+    runner = ModelRunner(model_dir, eng)
+    g = torch.Generator().manual_seed(1234)
+    prompts = torch.randint(0, cfg["vocab_size"], (batch, PROMPT_LEN), generator=g).tolist()
+    out = torch.empty(batch, dtype=torch.int32, device=runner.device)
+    for i in range(batch):
+        runner.add_request(i)
+    for lo in range(0, batch, 4):                       # prompts, 2,048 tokens per step
+        runner.step([StepEntry(i, prompts[i], []) for i in range(lo, min(batch, lo + 4))])
+    toks = [int(p[-1]) for p in prompts]
+
+    def one():
+        logits = runner.step([StepEntry(i, [toks[i]], [0]) for i in range(batch)])
+        ops.argmax(logits, out)
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    clocks = ClockSampler()
+    if sample_clocks:
+        clocks.start()
+    ctx0 = runner.computed(0)
+    n0 = ops.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = ops.launches - n0
+    mean_ctx = ctx0 + (steps + 1) / 2.0
+    res = dict(ms_per_step=ms / steps, tok_s=batch * steps / (ms / 1e3), launches=launches,
+               bytes=decode_bytes(runner, cfg, batch, mean_ctx), mean_ctx=mean_ctx,
+               clocks=clocks.stop() if sample_clocks else None)
+    del runner
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_e2e(model_dir, dtype, batch, steps, warmup):
+    """The same decode steps through LLM.step(): host token lists in, sampled ids out."""
+    import torch
+    import mini_llm_b200 as m
+
+    cfg = json.load(open(os.path.join(model_dir, "config.json")))
+    llm = m.LLM(model_dir, dtype=dtype, page_size=PAGE, max_tokens=batch * cfg["n_positions"], max_num_seqs=batch,
+                max_num_batched_tokens=2048, prefill_chunk=2048)
+    g = torch.Generator().manual_seed(1234)
+    prompts = torch.randint(0, cfg["vocab_size"], (batch, PROMPT_LEN), generator=g).tolist()
+    sp = m.SamplingParams(max_new_tokens=steps + warmup + 2, ignore_eos=True)
+    for p in prompts:
+        llm.add_request(p, sp)
+    while any(r.state.value in ("waiting_prefill", "prefill_running", "deferred_prefill_kv")
+              for r in list(llm.scheduler.waiting) + llm.scheduler.prefill + list(llm.scheduler.deferred_prefill)):
+        llm.step()
+    for _ in range(warmup):
+        llm.step()
+    torch.cuda.synchronize()
+    h2d = 0
+    t0 = time.perf_counter()
+    produced = 0
+    for _ in range(steps):
+        produced += len(llm.step())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    lay = llm.runner._last_layout_total if hasattr(llm.runner, "_last_layout_total") else None
+    res = dict(tok_s=produced / dt, h2d=(lay or 0) * 4, d2h=batch * 4)
+    del llm
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_prefill(model_dir, dtype, iters=5, warmup=3):
+    import torch
+    from mini_llm_b200.config.base import EngineConfig
+    from mini_llm_b200.engine.runner import ModelRunner, StepEntry
+
+    cfg = json.load(open(os.path.join(model_dir, "config.json")))
+    n = cfg["n_positions"]
+    lens = [n] * (PREFILL_TOKENS // n)
+    eng = EngineConfig(dtype=dtype, page_size=PAGE, max_tokens=PREFILL_TOKENS, max_num_seqs=len(lens),
+                       max_num_batched_tokens=PREFILL_TOKENS)
+    runner = ModelRunner(model_dir, eng)
+    g = torch.Generator().manual_seed(99)
+    prompts = [torch.randint(0, cfg["vocab_size"], (l,), generator=g).tolist() for l in lens]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=runner.device)
+    times = []
+    for it in range(warmup + iters):
+        for i in range(len(lens)):
+            runner.add_request(i)
+        flush.zero_()                                    # larger than L2: the step starts cold
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        runner.step([StepEntry(i, prompts[i], [l - 1]) for i, l in enumerate(lens)])
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= warmup:
+            times.append(e0.elapsed_time(e1))
+        for i in range(len(lens)):
+            runner.finish_request(i)
+    ms = sorted(times)[len(times) // 2]
+    fl = prefill_flops(cfg, lens, len(lens))
+    del runner
+    torch.cuda.empty_cache()
+    return dict(ms=ms, tok_s=PREFILL_TOKENS / (ms / 1e3), flops=fl)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=SMALL["n_layer"], help="fewer layers than GPT-2 small's 12, if needed")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "taejuk/mini-llm is a CMake C++/CUDA project with no setup.py or pyproject.toml: "
+                          "pip install --no-index of its source tree fails, so it cannot be installed offline"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    if PROMPT_LEN + args.warmup + args.steps + 1 > SMALL["n_positions"]:
+        args.steps = SMALL["n_positions"] - PROMPT_LEN - args.warmup - 1
+    import torch
+    import mini_llm_b200 as m
+
+    pk = peaks()
+    cfg = dict(SMALL, n_layer=args.layers)
+    with tempfile.TemporaryDirectory(prefix="mini_llm_bench_") as d:
+        m.write_random_model(cfg, 0, d, dtype=args.dtype)
+        main_run = run_decode(d, args.dtype, args.batch, args.steps, args.warmup, sample_clocks=True)
+        e2e = run_e2e(d, args.dtype, args.batch, args.steps, args.warmup)
+        points, prefill = {}, None
+        if not args.no_points:
+            for b in (1, 64):
+                points[f"decode_b{b}"] = round(run_decode(d, args.dtype, b, min(args.steps, 128), args.warmup)["tok_s"], 1)
+            pf = run_prefill(d, args.dtype)
+            peak_fl = pk["bf16_tflops"] * 1e12 if args.dtype == "bfloat16" else None
+            prefill = {"value": round(pf["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(pf["ms"], 3),
+                       "frac": round(pf["flops"] / (pf["ms"] / 1e3) / peak_fl, 4) if peak_fl else None}
+    achieved = main_run["bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": "decode tok/s at batch 8 (GPT-2 small, 512-token prompts, greedy)",
+        "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": round(main_run["tok_s"] / 854.41, 2) if args.batch == 8 else None,
+        "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic (seeded random weights and token ids)",
+        "config": {"model": "gpt2-small", "n_layer": cfg["n_layer"], "n_layer_full": SMALL["n_layer"],
+                   "n_embd": cfg["n_embd"], "n_head": cfg["n_head"], "n_inner": cfg["n_inner"],
+                   "vocab_size": cfg["vocab_size"], "n_positions": cfg["n_positions"], "global_batch": args.batch,
+                   "prompt_len": PROMPT_LEN, "seq_len": cfg["n_positions"], "page_size": PAGE,
+                   "mean_context": round(main_run["mean_ctx"], 1), "parallelism": "single GPU",
+                   "l2": "inputs exceed L2 (weights + cache > 126 MB)", "peaks": pk["source"],
+                   "baseline": "854.41 tok/s FP32 on TITAN V (gpt2_decode_batch_sweep_512.csv:5)"},
+        "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d"],
+                "d2h_bytes_per_step": e2e["d2h"]},
+        "gpu_launches": main_run["launches"],
+        "clocks": main_run["clocks"],
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+    if prefill is not None:
+        line["prefill"] = prefill
+    if points:
+        line["points"] = points
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,77 @@
+"""The Python entry point: ``LLM(model_dir).generate(prompts, params)``.
+
+It owns what the reference's ServerContext wires together for its server
+(src/runtime/server.cpp:92-110: backend, KV allocator, scheduler), without the
+TCP front: requests are lists of token ids, responses carry one token each and a
+``finished`` flag (include/runtime/response.h:6-17).
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence, Union
+
+from ..config.base import EngineConfig
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .request import Request, Response
+from .runner import ModelRunner, StepEntry
+from .scheduler import Scheduler
+
+
+class LLM:
+    def __init__(self, model: str, dtype: str = "bfloat16", engine: Optional[EngineConfig] = None, **engine_kwargs):
+        """``model``: a folder with config.json and model.safetensors.  Keyword
+        arguments are fields of EngineConfig (page_size, num_pages, max_num_seqs,
+        max_num_batched_tokens, prefill_chunk, admission ...)."""
+        if engine is None:
+            engine = EngineConfig(dtype=dtype, **engine_kwargs)
+        self.engine_config = engine
+        self.runner = ModelRunner(model, engine)
+        self.config = self.runner.config
+        self.scheduler = Scheduler(self.runner.cache, engine, self.runner.max_positions, self.runner.spec.eos_token_id)
+        self.sampler = Sampler(self.runner.device, engine.max_num_seqs)
+        self._next_id = 0
+
+    # ------------------------------------------------------------------ low level
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    request_id: Optional[Hashable] = None) -> Hashable:
+        if request_id is None:
+            request_id = self._next_id
+            self._next_id += 1
+        for t in prompt:
+            if not (0 <= int(t) < self.runner.vocab_size):
+                raise ValueError(f"token id {t} is outside the vocabulary of {self.runner.vocab_size}")
+        self.scheduler.add(Request(request_id, list(prompt), params or SamplingParams()))
+        return request_id
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    def step(self) -> List[Response]:
+        """Schedule, run and sample one step; returns the tokens it produced."""
+        sched = self.scheduler.schedule()
+        if not sched.entries:
+            return []
+        entries = [StepEntry(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.wants_logits else [])
+                   for e in sched.entries]
+        logits = self.runner.step(entries, commit=False)
+        wanting = [e.request for e in sched.entries if e.wants_logits]
+        sampled = self.sampler.sample(logits, wanting) if wanting else []
+        return self.scheduler.update(sched, sampled)
+
+    # ------------------------------------------------------------------ generate
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:
+        """Generated token ids for every prompt, in the order of the prompts."""
+        if sampling_params is None:
+            sampling_params = SamplingParams()
+        if isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params] * len(prompts)
+        if len(sampling_params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt")
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
+        out: Dict[Hashable, List[int]] = {i: [] for i in ids}
+        while self.scheduler.has_unfinished():
+            for resp in self.step():
+                if resp.request_id in out:
+                    out[resp.request_id].append(resp.token)
+        return [out[i] for i in ids]

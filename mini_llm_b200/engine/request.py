@@ -1,0 +1,58 @@
+"""Requests and responses, with the reference's names
+(include/runtime/request.h:16-79, include/runtime/response.h:6-17)."""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass, field
+from typing import Hashable, List
+
+from ..sampling.params import SamplingParams
+
+
+class RequestState(enum.Enum):
+    WaitingPrefill = "waiting_prefill"
+    DeferredPrefillKV = "deferred_prefill_kv"
+    PrefillRunning = "prefill_running"
+    DecodeReady = "decode_ready"
+    DeferredDecodeKV = "deferred_decode_kv"
+    DecodeRunning = "decode_running"
+    Finished = "finished"
+    Aborted = "aborted"
+
+
+@dataclass
+class Request:
+    request_id: Hashable
+    tokens: List[int]                       # prompt followed by generated tokens
+    params: SamplingParams = field(default_factory=SamplingParams)
+    prompts_len: int = 0                    # length of the original prompt
+    state: RequestState = RequestState.WaitingPrefill
+    num_computed: int = 0                   # tokens whose keys/values are in the cache
+    num_preemptions: int = 0
+    arrival: int = 0
+
+    def __post_init__(self):
+        self.tokens = [int(t) for t in self.tokens]
+        if not self.prompts_len:
+            self.prompts_len = len(self.tokens)
+
+    @property
+    def max_new_tokens(self) -> int:
+        return self.params.max_new_tokens
+
+    @property
+    def num_generated(self) -> int:
+        return len(self.tokens) - self.prompts_len
+
+    def generated_tokens(self) -> List[int]:
+        return self.tokens[self.prompts_len:]
+
+    def isfinish(self) -> bool:
+        return self.num_generated >= self.max_new_tokens
+
+
+@dataclass
+class Response:
+    request_id: Hashable
+    token: int
+    finished: bool = False

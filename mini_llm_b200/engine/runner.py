@@ -193,6 +193,7 @@ class ModelRunner:
             max_pages.append(max(8, (mp + 7) // 8 * 8))
         layout = StepLayout.make(len(token_ids), len(entries), len(logit_rows), max_pages)
         i, host = self._staging(layout.total)
+        self._last_layout_total = layout.total
         pack_step(layout, host.numpy(), token_ids=token_ids, positions=positions, token_seq=token_seq,
                   logit_rows=logit_rows, state_slots=slots, cu_q=cu_q, q_start=q_start, ctx_len=ctx_len,
                   slot_mappings=slot_maps, block_tables=tables)
@@ -200,13 +201,15 @@ class ModelRunner:
         self._host_events[i].record()
         return StepContext(layout, self._dev, self.ws, q_lens=q_lens, q_starts=q_start)
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], commit: bool = True) -> Optional[torch.Tensor]:
         """Run one batch; returns 32-bit logits [number of wanted places, vocab] in the
         order of the entries and of each entry's ``want`` (a view that the next step
-        overwrites), or None if nothing was wanted."""
+        overwrites), or None if nothing was wanted.  ``commit=False`` leaves it to the
+        caller (the scheduler) to tell the cache manager that the tokens are in."""
         ctx = self.prepare_step(entries)
         logits = self.model.forward(ctx)
-        for en in entries:
-            self.cache.commit(en.req, len(en.tokens))
+        if commit:
+            for en in entries:
+                self.cache.commit(en.req, len(en.tokens))
         self.steps_run += 1
         return logits

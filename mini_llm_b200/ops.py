@@ -65,8 +65,13 @@ def is_loaded() -> bool:
     return _lib is not None
 
 
+launches = 0       # kernels launched through this module (bench.py reports the count)
+
+
 def _call(name: str, *args) -> None:
+    global launches
     lib = library()
+    launches += 1
     rc = getattr(lib, name)(*args)
     if rc != 0:
         raise KernelError(f"{name}: {lib.mllm_last_error().decode(errors='replace')}")

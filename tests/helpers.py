@@ -124,9 +124,20 @@ class Replay:
 
 # The comparison rule of the model-level tests.  Fixed; never widened to pass.
 #   float32 : weights and arithmetic are 32-bit against a float64 oracle.
-#   bfloat16: both sides use the same bfloat16-rounded weights; the engine rounds
-#             activations to bfloat16 between kernels, the oracle does not.
-TOL = {"float32": dict(fro=2e-5, peak=1e-4), "bfloat16": dict(fro=2e-2, peak=6e-2)}
+#   bfloat16: both sides use the same bfloat16 weights and both keep the activations
+#             handed from kernel to kernel in bfloat16 (plain_gpt2's ``store``); what
+#             is left is the engine's 32-bit arithmetic against float64, and values
+#             that fall on the other side of a bfloat16 rounding edge.  One such flip
+#             moves a stored value by 2^-8 of itself and, with the sharp test weights,
+#             a row of logits by up to 4e-3: the plain implementation run in float32
+#             differs from itself in float64 by 3.6e-3 at worst on these models
+#             (median 5e-8).  The limit allows two to three such flips.
+TOL = {"float32": dict(fro=2e-5, peak=1e-4), "bfloat16": dict(fro=1e-2, peak=2e-2)}
+
+
+def oracle_store(dtype: str):
+    import plain_gpt2
+    return plain_gpt2.to_bf16 if dtype == "bfloat16" else plain_gpt2._keep
 
 
 def assert_close(got, want, dtype: str, what: str = ""):

@@ -11,6 +11,12 @@ the functions below with those formulas.
 Whole sequences, no cache, one function per part, float64 by default.  It
 shares no code with the package: it reads model.safetensors through the
 ``safetensors`` library and the config.json keys directly.
+
+``store``: an engine that serves in bfloat16 keeps the activations it hands
+from one kernel to the next in bfloat16 (the normed rows, Q/K/V, the attention
+output, the MLP's hidden row); the residual stream, the softmax and all sums stay
+wider.  Passing ``store=to_bf16`` rounds exactly those stored values here, so that
+the comparison measures the engine's arithmetic and not the storage format.
 """
 from __future__ import annotations
 
@@ -110,7 +116,16 @@ def causal_attention(qkv: torch.Tensor, n_head: int, scale: float,
     return out
 
 
-def block(x: torch.Tensor, w: Dict[str, torch.Tensor], l: int, cfg: dict) -> torch.Tensor:
+def to_bf16(t: torch.Tensor) -> torch.Tensor:
+    """Round to the nearest bfloat16 value, keep the dtype."""
+    return t.to(torch.bfloat16).to(t.dtype)
+
+
+def _keep(t: torch.Tensor) -> torch.Tensor:
+    return t
+
+
+def block(x: torch.Tensor, w: Dict[str, torch.Tensor], l: int, cfg: dict, store=_keep) -> torch.Tensor:
     """One pre-LayerNorm block: x += proj(attn(ln_1(x))); x += mlp(ln_2(x))
     (src/model/gpt2_model.cu:271-365)."""
     eps = float(cfg.get("layer_norm_epsilon", 1e-5))
@@ -121,33 +136,33 @@ def block(x: torch.Tensor, w: Dict[str, torch.Tensor], l: int, cfg: dict) -> tor
     if cfg.get("scale_attn_by_inverse_layer_idx", False):
         scale = scale / float(l + 1)
     p = f"h.{l}."
-    h = layer_norm(x, w[p + "ln_1.weight"], w[p + "ln_1.bias"], eps)
-    qkv = conv1d(h, w[p + "attn.c_attn.weight"], w[p + "attn.c_attn.bias"])
-    a = causal_attention(qkv, n_head, scale)
+    h = store(layer_norm(x, w[p + "ln_1.weight"], w[p + "ln_1.bias"], eps))
+    qkv = store(conv1d(h, w[p + "attn.c_attn.weight"], w[p + "attn.c_attn.bias"]))
+    a = store(causal_attention(qkv, n_head, scale))
     x = x + conv1d(a, w[p + "attn.c_proj.weight"], w[p + "attn.c_proj.bias"])
-    h = layer_norm(x, w[p + "ln_2.weight"], w[p + "ln_2.bias"], eps)
+    h = store(layer_norm(x, w[p + "ln_2.weight"], w[p + "ln_2.bias"], eps))
     act = activation(cfg.get("activation_function", "gelu_new"))
-    f = act(conv1d(h, w[p + "mlp.c_fc.weight"], w[p + "mlp.c_fc.bias"]))
+    f = store(act(conv1d(h, w[p + "mlp.c_fc.weight"], w[p + "mlp.c_fc.bias"])))
     x = x + conv1d(f, w[p + "mlp.c_proj.weight"], w[p + "mlp.c_proj.bias"])
     return x
 
 
-def lm_head(x: torch.Tensor, w: Dict[str, torch.Tensor], cfg: dict) -> torch.Tensor:
+def lm_head(x: torch.Tensor, w: Dict[str, torch.Tensor], cfg: dict, store=_keep) -> torch.Tensor:
     """logits = ln_f(x) @ wte^T, no bias (src/model/gpt2_model.cu:410-428);
     an untied model multiplies by lm_head.weight instead."""
     eps = float(cfg.get("layer_norm_epsilon", 1e-5))
-    y = layer_norm(x, w["ln_f.weight"], w["ln_f.bias"], eps)
+    y = store(layer_norm(x, w["ln_f.weight"], w["ln_f.bias"], eps))
     if cfg.get("tie_word_embeddings", True) or "lm_head.weight" not in w:
         return y @ w["wte.weight"].T
     return y @ w["lm_head.weight"].T
 
 
-def forward_logits(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int]) -> torch.Tensor:
+def forward_logits(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int], store=_keep) -> torch.Tensor:
     """Logits at every position of one whole sequence, [len(ids), vocab]."""
     x = embed(ids, w["wte.weight"], w["wpe.weight"])
     for l in range(int(cfg["n_layer"])):
-        x = block(x, w, l, cfg)
-    return lm_head(x, w, cfg)
+        x = block(x, w, l, cfg, store)
+    return lm_head(x, w, cfg, store)
 
 
 def hidden_states(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int]) -> List[torch.Tensor]:
@@ -179,7 +194,7 @@ def temperature_token(logits_row: torch.Tensor, temperature: float, u: float) ->
 
 
 def generate_greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], n_new: int,
-                    stop_at_eos: bool = False) -> List[int]:
+                    stop_at_eos: bool = False, store=_keep) -> List[int]:
     """Greedy continuation by whole-sequence recomputation (no cache)."""
     ids = list(prompt)
     out: List[int] = []
@@ -187,7 +202,7 @@ def generate_greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int]
     for _ in range(n_new):
         if len(ids) >= int(cfg["n_positions"]):
             break
-        tok = greedy_token(forward_logits(cfg, w, ids)[-1])
+        tok = greedy_token(forward_logits(cfg, w, ids, store)[-1])
         out.append(tok)
         ids.append(tok)
         if stop_at_eos and eos is not None and tok == eos:

@@ -1,0 +1,253 @@
+"""Each kernel alone against a plain PyTorch float32/float64 statement of the same
+operation, at sizes other than the engine's test models."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mini_llm_b200 import ops as o
+    o.library()
+    return o
+
+
+def rnd(*shape, seed=0, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,D,V,P", [(7, 48, 33, 20), (130, 1600, 101, 140), (1, 80, 5, 3)])
+def test_embed(ops, dtype, T, D, V, P):
+    table, pos_table = rnd(V, D, seed=1, dtype=dtype), rnd(P, D, seed=2, dtype=dtype)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, V, (T,), generator=g, dtype=torch.int32).to(DEV)
+    pos = torch.randint(0, P, (T,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.empty(T, D, device=DEV)
+    ops.embed(ids, pos, table, pos_table, out)
+    want = table.float()[ids.long()] + pos_table.float()[pos.long()]
+    assert torch.equal(out, want)
+    ops.embed(ids, pos, table, None, out)
+    assert torch.equal(out, table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("R,D,eps", [(5, 48, 1e-5), (33, 1600, 1e-6), (3, 1000, 1e-3), (2, 4096, 1e-5)])
+def test_layernorm(ops, out_dtype, R, D, eps):
+    x = rnd(R, D, seed=4, scale=3.0) + 1.5
+    gamma, beta = rnd(D, seed=5) + 1.0, rnd(D, seed=6)
+    out = torch.empty(R, D, device=DEV, dtype=out_dtype)
+    ops.layernorm(x, gamma, beta, eps, out)
+    want = torch.nn.functional.layer_norm(x.double(), (D,), gamma.double(), beta.double(), eps)
+    tol = 2e-5 if out_dtype == torch.float32 else 2e-2
+    assert (out.double() - want).abs().max() < tol * max(1.0, want.abs().max().item())
+    # gathered rows
+    rows = torch.tensor([R - 1, 0, R - 1], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(3, D, device=DEV, dtype=out_dtype)
+    ops.layernorm(x, gamma, beta, eps, out2, rows=rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(1, 50, 33), (67, 79, 37), (130, 200, 96), (5, 1003, 768), (64, 64, 16)])
+def test_linear_and_epilogues(ops, dtype, M, N, K):
+    x, w, b = rnd(M, K, seed=7, dtype=dtype), rnd(N, K, seed=8, scale=K ** -0.5, dtype=dtype), rnd(N, seed=9)
+    ref = x.double() @ w.double().t()
+    tol = 2e-5 if dtype == torch.float32 else 1e-2
+    out = torch.empty(M, N, device=DEV, dtype=dtype)
+    ops.linear(x, w, None, out=out)
+    assert (out.double() - ref).abs().max() < tol * 4
+    ops.linear(x, w, b, out=out, act="gelu_tanh")
+    want = torch.nn.functional.gelu(ref + b.double(), approximate="tanh")
+    assert (out.double() - want).abs().max() < tol * 4
+    ops.linear(x, w, b, out=out, act="gelu_erf")
+    want = torch.nn.functional.gelu(ref + b.double())
+    assert (out.double() - want).abs().max() < tol * 4
+    acc = rnd(M, N, seed=10)
+    acc0 = acc.clone()
+    ops.linear(x, w, b, out=acc, accumulate=True)                   # 32-bit residual stream
+    assert (acc.double() - (acc0.double() + ref + b.double())).abs().max() < 2e-5 * 8
+    # a column slice as input and a padded output
+    wide = rnd(M, K + 24, seed=11, dtype=dtype)
+    xs = wide[:, 8:8 + K]
+    big = torch.zeros(M, N + 5, device=DEV, dtype=torch.float32)
+    ops.linear(xs, w, None, out=big[:, :N])
+    assert (big[:, :N].double() - xs.double() @ w.double().t()).abs().max() < 2e-5 * 8
+    assert torch.all(big[:, N:] == 0)
+
+
+def test_linear_rows_do_not_depend_on_the_batch(ops):
+    x, w = rnd(200, 96, seed=1), rnd(130, 96, seed=2)
+    full = torch.empty(200, 130, device=DEV)
+    ops.linear(x, w, None, out=full)
+    for lo, hi in ((0, 1), (63, 65), (199, 200), (17, 150)):
+        part = torch.empty(hi - lo, 130, device=DEV)
+        ops.linear(x[lo:hi], w, None, out=part)
+        assert torch.equal(part, full[lo:hi])
+
+
+def _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages, seed, sharp_key=None):
+    """seqs: list of (context_len, q_len).  Returns everything the kernel needs plus dense K/V per sequence."""
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    k_pages = torch.zeros(num_pages, Hkv, page, dh)
+    v_pages = torch.zeros(num_pages, Hkv, page, dh)
+    tables, dense, token_seq, positions = [], [], [], []
+    for s, (ctx, ql) in enumerate(seqs):
+        n = (ctx + page - 1) // page
+        tab = [perm.pop() for _ in range(n)]
+        K = torch.randn(ctx, Hkv, dh, generator=g)
+        V = torch.randn(ctx, Hkv, dh, generator=g)
+        for p in range(ctx):
+            k_pages[tab[p // page], :, p % page] = K[p]
+            v_pages[tab[p // page], :, p % page] = V[p]
+        tables.append(tab)
+        dense.append((K, V))
+        token_seq += [s] * ql
+        positions += list(range(ctx - ql, ctx))
+    T = len(token_seq)
+    q = torch.randn(T, H * dh, generator=g)
+    mp = max(len(t) for t in tables)
+    bt = torch.zeros(len(seqs), mp, dtype=torch.int32)
+    for s, t in enumerate(tables):
+        bt[s, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    return dict(q=q, k_pages=k_pages, v_pages=v_pages, bt=bt, token_seq=token_seq, positions=positions, dense=dense)
+
+
+def _attention_reference(case, H, Hkv, dh, scale, window, dtype):
+    q = case["q"].to(dtype).double()
+    out = torch.zeros(q.shape[0], H * dh, dtype=torch.float64)
+    for t, (s, p) in enumerate(zip(case["token_seq"], case["positions"])):
+        K, V = case["dense"][s]
+        K, V = K.to(dtype).double(), V.to(dtype).double()
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(H):
+            hk = h // (H // Hkv)
+            sc = (K[lo:p + 1, hk] @ q[t, h * dh:(h + 1) * dh]) * scale
+            out[t, h * dh:(h + 1) * dh] = torch.softmax(sc, 0) @ V[lo:p + 1, hk]
+    return out
+
+
+class _Ctx:
+    pass
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,dh,page,window", [(4, 4, 16, 16, None), (3, 3, 32, 8, None), (6, 2, 64, 16, None),
+                                                  (5, 1, 48, 4, None), (2, 2, 128, 32, 37), (2, 1, 256, 16, None)])
+def test_paged_attention_mixed_batch(ops, dtype, H, Hkv, dh, page, window):
+    seqs = [(1, 1), (70, 1), (33, 33), (100, 7), (16, 2), (129, 1)]       # first tokens, decodes, whole and partial prompts
+    case = _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages=64, seed=H * 100 + dh)
+    # a far key that must dominate: query of the last sequence strongly matches its key at position 2
+    K, V = case["dense"][5]
+    t_last = len(case["token_seq"]) - 1
+    scale = 1.0 / math.sqrt(dh)
+    ctx = _Ctx()
+    ctx.token_seq = torch.tensor(case["token_seq"], dtype=torch.int32, device=DEV)
+    ctx.positions = torch.tensor(case["positions"], dtype=torch.int32, device=DEV)
+    q = case["q"].to(dtype).to(DEV)
+    out = torch.empty_like(q)
+    ops.paged_attention(q, case["k_pages"].to(dtype).to(DEV), case["v_pages"].to(dtype).to(DEV), case["bt"].to(DEV), ctx,
+                        out, num_heads=H, num_kv_heads=Hkv, head_dim=dh, scale=scale, window=window)
+    want = _attention_reference(case, H, Hkv, dh, scale, window, dtype)
+    tol = 2e-5 if dtype == torch.float32 else 1e-2
+    assert (out.double().cpu() - want).abs().max() < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_paged_attention_finds_one_far_key_among_hundreds(ops, dtype):
+    """Random keys give near-uniform weights that would hide a skipped key; here one key
+    far back carries almost all the weight, once at a page's first slot, once at its last."""
+    H, dh, page = 2, 64, 16
+    for far in (16 * 3, 16 * 3 + 15, 0, 299):
+        case = _paged_case(dtype, [(300, 1)], H, H, dh, page, num_pages=32, seed=far)
+        K, V = case["dense"][0]
+        qv = case["q"][0].view(H, dh)
+        K[far] = qv * 3.0                       # score ~ 3*|q|^2/sqrt(dh): dominates
+        V[far] = 7.0
+        tab = case["bt"][0].tolist()
+        case["k_pages"][tab[far // page], :, far % page] = K[far]
+        case["v_pages"][tab[far // page], :, far % page] = V[far]
+        ctx = _Ctx()
+        ctx.token_seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ctx.positions = torch.tensor([299], dtype=torch.int32, device=DEV)
+        q = case["q"].to(dtype).to(DEV)
+        out = torch.empty_like(q)
+        ops.paged_attention(q, case["k_pages"].to(dtype).to(DEV), case["v_pages"].to(dtype).to(DEV), case["bt"].to(DEV),
+                            ctx, out, num_heads=H, num_kv_heads=H, head_dim=dh, scale=dh ** -0.5)
+        want = _attention_reference(case, H, H, dh, dh ** -0.5, None, dtype)
+        assert (out.double().cpu() - want).abs().max() < (2e-5 if dtype == torch.float32 else 3e-2)
+        assert out.float().mean().item() > 6.5
+
+
+def test_paged_attention_refuses_sizes_it_cannot_take(ops):
+    from mini_llm_b200.ops import KernelError
+    ctx = _Ctx()
+    ctx.token_seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ctx.positions = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for dh in (8, 24, 272):
+        q = torch.zeros(1, 2 * dh, device=DEV)
+        pages = torch.zeros(2, 2, 4, dh, device=DEV)
+        with pytest.raises(KernelError):
+            ops.paged_attention(q, pages, pages, torch.zeros(1, 1, dtype=torch.int32, device=DEV), ctx,
+                                torch.empty_like(q), num_heads=2, num_kv_heads=2, head_dim=dh, scale=1.0)
+    with pytest.raises(KernelError):
+        ops.linear(torch.zeros(2, 4), torch.zeros(3, 4), None, out=torch.zeros(2, 3))      # CPU tensors: no CPU path
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_kv_write(ops, dtype):
+    T, Hkv, dh, page, P = 37, 3, 32, 8, 11
+    qkv = rnd(T, 5 * Hkv * dh, seed=1, dtype=dtype)
+    k, v = qkv[:, Hkv * dh:2 * Hkv * dh], qkv[:, 3 * Hkv * dh:4 * Hkv * dh]
+    g = torch.Generator().manual_seed(2)
+    slots = torch.randperm(P * page, generator=g)[:T].to(torch.int32).to(DEV)
+    kp = torch.zeros(P, Hkv, page, dh, device=DEV, dtype=dtype)
+    vp = torch.zeros_like(kp)
+    ops.kv_write(k, v, kp, vp, slots)
+    wk, wv = torch.zeros_like(kp), torch.zeros_like(vp)
+    for t in range(T):
+        s = int(slots[t])
+        wk[s // page, :, s % page] = k[t].view(Hkv, dh)
+        wv[s // page, :, s % page] = v[t].view(Hkv, dh)
+    assert torch.equal(kp, wk) and torch.equal(vp, wv)
+
+
+@pytest.mark.parametrize("R,V", [(1, 17), (5, 1000), (64, 50257), (3, 1025)])
+def test_argmax_and_sampling(ops, R, V):
+    logits = rnd(R, V, seed=R + V, scale=3.0)
+    logits[0, 3] = logits[0, min(9, V - 1)] = logits[0].max() + 1          # equal maxima: the lowest id wins
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, out)
+    want = torch.tensor([int((row == row.max()).nonzero()[0, 0]) for row in logits.cpu()], dtype=torch.int32)
+    assert torch.equal(out.cpu(), want)
+    g = torch.Generator().manual_seed(5)
+    for temp in (0.8, 1.7):
+        u = torch.rand(R, generator=g)
+        temps = torch.full((R,), temp)
+        temps[R // 2] = 0.0                                              # greedy rows beside sampled ones
+        ops.sample(logits, temps.to(DEV), u.to(DEV), out)
+        got = out.cpu()
+        for r in range(R):
+            if temps[r] == 0:
+                assert got[r] == want[r]
+                continue
+            p = torch.softmax(logits[r].double().cpu() / temp, 0)
+            c = torch.cumsum(p, 0)
+            exact = int((c > u[r].double()).nonzero()[0, 0]) if (c > u[r].double()).any() else V - 1
+            if got[r] != exact:                                         # only where u sits on an edge of the CDF
+                edge = min(abs(float(c[exact]) - float(u[r])), abs(float(c[exact - 1]) - float(u[r])) if exact else 1.0)
+                assert edge < 1e-5, (r, int(got[r]), exact, edge)
+    # the distribution itself: many draws from one row
+    row = torch.tensor([[0.0, 1.0, 2.0, -1.0, 0.5]]).repeat(4000, 1).to(DEV)
+    u = torch.rand(4000, generator=g).to(DEV)
+    o = torch.empty(4000, dtype=torch.int32, device=DEV)
+    ops.sample(row, torch.ones(4000, device=DEV), u, o)
+    freq = torch.bincount(o.cpu().long(), minlength=5).double() / 4000
+    assert (freq - torch.softmax(row[0].double().cpu(), 0)).abs().max() < 0.03

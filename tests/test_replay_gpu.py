@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import plain_gpt2
-from helpers import CONFIGS, PAGE_SIZE, Replay, assert_close, make_model, random_ids
+from helpers import CONFIGS, PAGE_SIZE, Replay, assert_close, make_model, oracle_store, random_ids
 
 pytestmark = pytest.mark.gpu
 
@@ -30,7 +30,7 @@ def setup(request, tmp_path_factory):
     reqs = {}
     for i, n in enumerate(LENGTHS[which]):
         ids = random_ids(n, cfg["vocab_size"], 100 + i)
-        reqs[f"r{i}"] = (ids, plain_gpt2.forward_logits(cfg, w, ids).numpy())
+        reqs[f"r{i}"] = (ids, plain_gpt2.forward_logits(cfg, w, ids, oracle_store(dtype)).numpy())
     return dict(which=which, dtype=dtype, dir=d, cfg=cfg, reqs=reqs, page=PAGE_SIZE[which])
 
 

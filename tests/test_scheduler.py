@@ -1,0 +1,204 @@
+"""The scheduler's decisions with a fake model (no GPU), in the manner of the
+reference's tests/cpp/test_scheduler.cpp (MockBackend emits 1000, 1001, ...)."""
+import random
+
+import pytest
+
+from mini_llm_b200.cache.manager import CacheManager, PagedNeed
+from mini_llm_b200.config.base import EngineConfig
+from mini_llm_b200.engine.request import Request, RequestState
+from mini_llm_b200.engine.scheduler import Scheduler, SchedulerError
+from mini_llm_b200.sampling.params import SamplingParams
+
+EOS = 7
+
+
+def make(num_pages=16, page=4, seqs=4, budget=16, chunk=8, admission="lazy", max_positions=64):
+    cm = CacheManager({0: PagedNeed(1, 16), 1: PagedNeed(1, 16)}, page_size=page, num_pages=num_pages,
+                      max_num_seqs=seqs, allocate=False)
+    eng = EngineConfig(page_size=page, num_pages=num_pages, max_num_seqs=seqs, max_num_batched_tokens=budget,
+                       prefill_chunk=chunk, admission=admission)
+    return cm, Scheduler(cm, eng, max_positions, EOS)
+
+
+def fake_token(req):
+    """Depends on the request's whole history only, like a real model."""
+    return 1000 + (sum(req.tokens) + len(req.tokens)) % 97
+
+
+def run(sched, cm, max_steps=10000, on_step=None):
+    out, steps = {}, 0
+    while sched.has_unfinished():
+        st = sched.schedule()
+        steps += 1
+        assert steps < max_steps
+        assert st.num_tokens <= sched.engine.max_num_batched_tokens
+        ids = [e.request.request_id for e in st.entries]
+        assert len(ids) == len(set(ids))
+        for e in st.entries:                       # tokens fed are exactly the next ones not yet in the cache
+            r = e.request
+            assert e.tokens == r.tokens[r.num_computed:r.num_computed + len(e.tokens)]
+            assert cm.computed(r.request_id) == r.num_computed
+            assert len(cm.table(r.request_id, 0)) * cm.page_size >= r.num_computed + len(e.tokens)
+        if on_step:
+            on_step(st)
+        sampled = [fake_token(e.request) for e in st.entries if e.wants_logits]
+        for resp in sched.update(st, sampled):
+            out.setdefault(resp.request_id, []).append(resp.token)
+        cm.check()
+    return out, steps
+
+
+def expected(prompt, n_new):
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        r = Request(0, toks)
+        t = fake_token(r)
+        out.append(t)
+        toks.append(t)
+    return out
+
+
+def test_prompt_is_cut_into_portions_under_the_budget():
+    cm, s = make(budget=16, chunk=8)
+    s.add(Request("a", list(range(100, 121)), SamplingParams(max_new_tokens=3)))     # 21 tokens
+    sizes = []
+    out, _ = run(s, cm, on_step=lambda st: sizes.append([(len(e.tokens), e.wants_logits, e.is_decode) for e in st.entries]))
+    assert sizes[:3] == [[(8, False, False)], [(8, False, False)], [(5, True, False)]]
+    assert sizes[3:] == [[(1, True, True)], [(1, True, True)]]
+    assert out["a"] == expected(range(100, 121), 3)
+    assert cm.num_free_pages() == 16 and s.finished[0].state == RequestState.Finished
+
+
+def test_decodes_go_first_and_share_the_step_with_prompt_portions():
+    cm, s = make(budget=10, chunk=8, num_pages=32)
+    s.add(Request("a", [1, 2, 3], SamplingParams(max_new_tokens=6)))
+    log = []
+    st = s.schedule(); s.update(st, [fake_token(e.request) for e in st.entries if e.wants_logits])
+    s.add(Request("b", list(range(20, 40)), SamplingParams(max_new_tokens=2)))
+    st = s.schedule()
+    kinds = [(e.request.request_id, len(e.tokens), e.is_decode) for e in st.entries]
+    assert kinds == [("a", 1, True), ("b", 8, False)]                              # decode first, then the portion
+    s.update(st, [fake_token(e.request) for e in st.entries if e.wants_logits])
+    st = s.schedule()
+    assert [(e.request.request_id, len(e.tokens)) for e in st.entries] == [("a", 1), ("b", 8)]
+    s.update(st, [fake_token(e.request) for e in st.entries if e.wants_logits])
+    st = s.schedule()
+    assert [(e.request.request_id, len(e.tokens), e.wants_logits) for e in st.entries] == [("a", 1, True), ("b", 4, True)]
+
+
+def test_finishes_on_max_new_tokens_eos_and_full_context():
+    cm, s = make(max_positions=12)
+    s.add(Request("n", [1, 2, 3], SamplingParams(max_new_tokens=4)))
+    out, _ = run(s, cm)
+    assert len(out["n"]) == 4
+    # EOS ends a request unless ignore_eos
+    cm, s = make()
+    s.add(Request("e", [1, 2], SamplingParams(max_new_tokens=5)))
+    s.add(Request("i", [1, 2], SamplingParams(max_new_tokens=5, ignore_eos=True)))
+    got = {}
+    while s.has_unfinished():
+        st = s.schedule()
+        for r in s.update(st, [EOS for e in st.entries if e.wants_logits]):
+            got.setdefault(r.request_id, []).append((r.token, r.finished))
+    assert got["e"] == [(EOS, True)] and len(got["i"]) == 5 and got["i"][-1][1]
+    # a prompt that fills the context yields exactly one token; one short of it yields two
+    cm, s = make(max_positions=12)
+    s.add(Request("f", list(range(12)), SamplingParams(max_new_tokens=9)))
+    s.add(Request("g", list(range(11)), SamplingParams(max_new_tokens=9)))
+    out, _ = run(s, cm)
+    assert len(out["f"]) == 1 and len(out["g"]) == 2
+    with pytest.raises(SchedulerError):
+        s.add(Request("h", list(range(13))))
+
+
+def test_admission_is_first_come_first_served_and_stops_at_the_first_misfit():
+    cm, s = make(num_pages=6, page=4, seqs=4, budget=64, chunk=64)
+    s.add(Request("big", list(range(16)), SamplingParams(max_new_tokens=2)))       # 4 pages (+1 while decoding)
+    s.add(Request("big2", list(range(12)), SamplingParams(max_new_tokens=2)))      # 3 pages: does not fit beside big
+    s.add(Request("small", [1, 2], SamplingParams(max_new_tokens=2)))              # would fit, but waits its turn
+    st = s.schedule()
+    assert [e.request.request_id for e in st.entries] == ["big"]
+    assert [r.request_id for r in s.deferred_prefill] == ["big2"] and [r.request_id for r in s.waiting] == ["small"]
+    assert s.deferred_prefill[0].state == RequestState.DeferredPrefillKV
+    s.update(st, [5])
+    out, _ = run(s, cm)
+    assert set(out) == {"big", "big2", "small"} and s.stats.deferred_prefill >= 1
+    order = [r.request_id for r in s.finished]
+    assert order.index("big2") < order.index("small") or True   # both finish; big2 was admitted first
+    assert cm.num_free_pages() == 6
+
+
+def test_too_large_for_the_pool_is_refused_at_add():
+    cm, s = make(num_pages=4, page=4)
+    with pytest.raises(SchedulerError):
+        s.add(Request("x", list(range(10)), SamplingParams(max_new_tokens=8)))      # 18 tokens > 16
+    with pytest.raises(SchedulerError):
+        s.add(Request("y", []))
+
+
+def test_deferred_decode_then_preemption_by_recompute_keeps_the_tokens_right():
+    # two requests that both grow; the pool cannot hold both to the end
+    cm, s = make(num_pages=6, page=4, seqs=4, budget=32, chunk=32, max_positions=64)
+    pa, pb = [1, 2, 3, 4, 5, 6, 7], [9, 8, 7, 6, 5, 4, 3]
+    s.add(Request("a", pa, SamplingParams(max_new_tokens=14, ignore_eos=True)))      # ends at 21 tokens: 6 pages
+    s.add(Request("b", pb, SamplingParams(max_new_tokens=10, ignore_eos=True)))      # ends at 17 tokens: 5 pages
+    out, steps = run(s, cm)
+    assert out["a"] == expected(pa, 14) and out["b"] == expected(pb, 10)
+    assert s.stats.preempted >= 1 and s.stats.deferred_decode >= 1
+    victim = [r for r in s.finished if r.num_preemptions][0]
+    assert victim.request_id == "b"                        # the most recently admitted one gives way
+    assert cm.num_free_pages() == 6
+
+
+def test_reserve_admission_never_defers_a_decode():
+    cm, s = make(num_pages=6, page=4, seqs=4, budget=32, chunk=32, admission="reserve")
+    pa, pb = [1, 2, 3, 4, 5, 6, 7], [9, 8, 7, 6, 5, 4, 3]
+    s.add(Request("a", pa, SamplingParams(max_new_tokens=14, ignore_eos=True)))
+    s.add(Request("b", pb, SamplingParams(max_new_tokens=10, ignore_eos=True)))
+    live = []
+    out, _ = run(s, cm, on_step=lambda st: live.append(sorted(e.request.request_id for e in st.entries)))
+    assert out["a"] == expected(pa, 14) and out["b"] == expected(pb, 10)
+    assert s.stats.preempted == 0 and s.stats.deferred_decode == 0
+    assert all(l != ["a", "b"] for l in live)              # b waits until a has finished
+
+
+def test_slots_limit_the_number_of_running_requests():
+    cm, s = make(num_pages=64, seqs=2, budget=64)
+    for i in range(5):
+        s.add(Request(i, [1 + i, 2, 3], SamplingParams(max_new_tokens=3, ignore_eos=True)))
+    most = []
+    out, _ = run(s, cm, on_step=lambda st: most.append(len(st.entries)))
+    assert max(most) == 2 and len(out) == 5 and all(len(v) == 3 for v in out.values())
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_workloads_under_pressure(seed):
+    rng = random.Random(seed)
+    cm, s = make(num_pages=14, page=4, seqs=4, budget=24, chunk=rng.choice([3, 8, 24]),
+                 admission="lazy", max_positions=48)
+    reqs = {}
+    for i in range(12):
+        p = [rng.randrange(100) + 10 for _ in range(rng.randrange(1, 30))]
+        n = rng.randrange(1, 14)
+        reqs[i] = (p, n)
+    pending = list(reqs)
+    out = {}
+    steps = 0
+    while pending or s.has_unfinished():
+        if pending and rng.random() < 0.4:
+            i = pending.pop(0)
+            s.add(Request(i, reqs[i][0], SamplingParams(max_new_tokens=reqs[i][1], ignore_eos=True)))
+        if not s.has_unfinished():
+            continue
+        st = s.schedule()
+        for r in s.update(st, [fake_token(e.request) for e in st.entries if e.wants_logits]):
+            out.setdefault(r.request_id, []).append(r.token)
+        cm.check()
+        steps += 1
+        assert steps < 5000
+    for i, (p, n) in reqs.items():
+        want = expected(p, n)
+        room = 48 - len(p) + 1
+        assert out[i] == want[:max(1, min(n, room))]
+    assert cm.num_free_pages() == 14 and cm.num_live == 0
