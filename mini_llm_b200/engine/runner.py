@@ -81,6 +81,12 @@ class ModelRunner:
         self._host_turn = 0
         self._dev: Optional[torch.Tensor] = None
         self.steps_run = 0
+        # CUDA graphs of decode-only steps, by the step's shape
+        self._graphs: Dict[tuple, object] = {}
+        self._graph_seen: Dict[tuple, int] = {}
+        self._graph_version = -1
+        self.graph_replays = 0
+        self.graph_kernels: Dict[tuple, int] = {}
 
     # ------------------------------------------------------------------ set-up
     def _make_cache(self) -> None:
@@ -190,7 +196,7 @@ class ModelRunner:
         max_pages = []
         for g in range(ng):
             mp = max(len(t) for t in tables[g])
-            max_pages.append(max(8, (mp + 7) // 8 * 8))
+            max_pages.append(max(16, (mp + 15) // 16 * 16))    # wide steps: few distinct shapes for captured graphs
         layout = StepLayout.make(len(token_ids), len(entries), len(logit_rows), max_pages)
         i, host = self._staging(layout.total)
         self._last_layout_total = layout.total
@@ -207,9 +213,52 @@ class ModelRunner:
         overwrites), or None if nothing was wanted.  ``commit=False`` leaves it to the
         caller (the scheduler) to tell the cache manager that the tokens are in."""
         ctx = self.prepare_step(entries)
-        logits = self.model.forward(ctx)
+        logits = self._forward(ctx)
         if commit:
             for en in entries:
                 self.cache.commit(en.req, len(en.tokens))
         self.steps_run += 1
+        return logits
+
+    # ------------------------------------------------------------------ CUDA graphs
+    def _forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        """Decode-only steps are launch-bound (about a hundred small kernels), so a step
+        shape seen before is replayed as one CUDA graph; everything else runs eagerly.
+        A graph fixes grid sizes and buffer addresses: its key holds every host-side
+        number a launch depends on, and all graphs are dropped when a scratch buffer
+        is replaced by a larger one."""
+        if not (self.engine.use_cuda_graphs and ctx.decode_only):
+            return self.model.forward(ctx)
+        if self._graph_version != self.ws.version:
+            self._graphs.clear()
+            self._graph_seen.clear()
+            self._graph_version = self.ws.version
+        key = (ctx.layout.key(), -(-ctx.max_ctx_len // ops.DECODE_SPLIT))
+        g = self._graphs.get(key)
+        if g is not None:
+            g[0].replay()
+            self.graph_replays += 1
+            ops.launches += self.graph_kernels[key]
+            return g[1]
+        seen = self._graph_seen.get(key, 0)
+        self._graph_seen[key] = seen + 1
+        if seen == 0:
+            return self.model.forward(ctx)             # first time: eager, buffers get allocated
+        version = self.ws.version
+        torch.cuda.current_stream().synchronize()
+        graph = torch.cuda.CUDAGraph()
+        n0 = ops.launches
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx)
+        kernels = ops.launches - n0
+        if self.ws.version != version:                  # a buffer was allocated during capture: do not keep it
+            self._graph_version = -1
+            return self.model.forward(ctx)
+        if len(self._graphs) >= 64:
+            self._graphs.pop(next(iter(self._graphs)))
+        self._graphs[key] = (graph, logits)
+        self.graph_kernels[key] = kernels
+        ops.launches = n0 + kernels
+        graph.replay()
+        self.graph_replays += 1
         return logits

@@ -16,6 +16,9 @@ import torch
 from .csrc import build as _build
 
 F32, BF16 = 0, 1
+SMALL_M = 64                 # rows up to which the weight-streaming product is used
+DECODE_SPLIT = 256           # keys per split of the decode attention (csrc/attention_decode.cu)
+_DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16, 32, 64, 128)}
 _ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}
 _lib = None
 
@@ -38,6 +41,11 @@ def _signatures(lib):
                              c_int, c_int, c_void_p],
         "mllm_attention_simt": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                 c_ll, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+        "mllm_linear_smallm": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
+                               c_int, c_void_p],
+        "mllm_attention_decode": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                  c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                  c_int, c_void_p],
         "mllm_argmax": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
         "mllm_sample": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     }
@@ -172,6 +180,18 @@ def linear(x, weight, bias, out, act: Optional[str] = None, accumulate: bool = F
         raise KernelError(f"linear: unknown activation {act!r}")
     if x.dtype == torch.float32 and out.dtype != torch.float32:
         raise KernelError("linear: float32 operands need a float32 result")
+    if impl is None:
+        impl = "simt"
+        if x.dtype == torch.bfloat16 and M <= SMALL_M and K % 8 == 0 and lda % 8 == 0 \
+                and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
+            impl = "smallm"
+    if impl == "smallm":
+        _call("mllm_linear_smallm", x.data_ptr(), lda, weight.data_ptr(),
+              bias.data_ptr() if bias is not None else None, out.data_ptr(), ldo, M, N, K, _ACT[act],
+              int(accumulate), _dt(out), _stream())
+        return out
+    if impl != "simt":
+        raise KernelError(f"linear: unknown implementation {impl!r}")
     _call("mllm_linear_simt", x.data_ptr(), lda, weight.data_ptr(), bias.data_ptr() if bias is not None else None,
           out.data_ptr(), ldo, M, N, K, _ACT[act], int(accumulate), _dt(x), _dt(out), _stream())
     return out
@@ -217,6 +237,26 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
     if head_dim % 16 != 0 or not (16 <= head_dim <= 256):
         raise KernelError(f"paged_attention: head size {head_dim} is not a multiple of 16 in 16..256")
     bt_stride = _rows("block_table", block_table)
+    if impl is None:
+        impl = "simt"
+        if getattr(ctx, "decode_only", False) and head_dim in _DECODE_HEAD_DIMS[q.dtype] and ldq % 8 == 0 \
+                and q.data_ptr() % 16 == 0:
+            impl = "decode"
+    if impl == "decode":
+        if head_dim not in _DECODE_HEAD_DIMS[q.dtype]:
+            raise KernelError(f"paged_attention: the split-key kernel takes head sizes {_DECODE_HEAD_DIMS[q.dtype]} "
+                              f"for {q.dtype}, not {head_dim}")
+        # splits cover the longest context of the step, rounded up so that captured graphs keep their grid
+        max_splits = max(1, -(-int(ctx.max_ctx_len) // DECODE_SPLIT))
+        part_o = ctx.ws.buf("attn_part_o", T * num_heads * max_splits, head_dim, torch.float32)
+        part_ml = ctx.ws.buf("attn_part_ml", T * num_heads * max_splits, 2, torch.float32)
+        _call("mllm_attention_decode", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(),
+              block_table.data_ptr(), bt_stride, ctx.token_seq.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(),
+              ldo, part_o.data_ptr(), part_ml.data_ptr(), T, num_heads, num_kv_heads, head_dim, ps, float(scale),
+              int(window or 0), max_splits, _dt(q), _stream())
+        return
+    if impl != "simt":
+        raise KernelError(f"paged_attention: unknown implementation {impl!r}")
     _call("mllm_attention_simt", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
           bt_stride, ctx.token_seq.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), ldo, T, num_heads,
           num_kv_heads, head_dim, ps, float(scale), int(window or 0), _dt(q), _stream())

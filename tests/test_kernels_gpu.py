@@ -82,6 +82,41 @@ def test_linear_and_epilogues(ops, dtype, M, N, K):
     assert torch.all(big[:, N:] == 0)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(1, 768, 768), (8, 2304, 768), (3, 50, 40), (17, 1003, 96), (64, 320, 3072),
+                                   (33, 50257, 64), (64, 9472 + 5, 128), (5, 16, 8)])
+def test_linear_small_m_against_the_plain_kernel(ops, out_dtype, M, N, K):
+    """The weight-streaming tensor-core product beside its plain twin and float64."""
+    dt = torch.bfloat16
+    x, w, b = rnd(M, K, seed=1, dtype=dt), rnd(N, K, seed=2, scale=K ** -0.5, dtype=dt), rnd(N, seed=3)
+    ref = x.double() @ w.double().t() + b.double()
+    for act in (None, "gelu_tanh", "gelu_erf"):
+        out = torch.full((M, N), 7.0, device=DEV, dtype=out_dtype)
+        ops.linear(x, w, b, out=out, act=act, impl="smallm")
+        plain = torch.empty(M, N, device=DEV, dtype=out_dtype)
+        ops.linear(x, w, b, out=plain, act=act, impl="simt")
+        want = ref if act is None else torch.nn.functional.gelu(ref, approximate="tanh" if act == "gelu_tanh" else "none")
+        tol = 2e-5 if out_dtype == torch.float32 else 1e-2
+        assert (out.double() - want).abs().max() < tol * max(1.0, want.abs().max().item())
+        assert (out.double() - plain.double()).abs().max() < tol * max(1.0, want.abs().max().item())
+    acc = rnd(M, N, seed=4)
+    acc0 = acc.clone()
+    wide = rnd(M, K + 16, seed=5, dtype=dt)
+    ops.linear(wide[:, 8:8 + K], w, None, out=acc, accumulate=True, impl="smallm")
+    want = acc0.double() + wide[:, 8:8 + K].double() @ w.double().t()
+    assert (acc.double() - want).abs().max() < 1e-4
+
+
+def test_linear_small_m_rows_do_not_depend_on_the_batch(ops):
+    x, w = rnd(64, 768, seed=1, dtype=torch.bfloat16), rnd(2304, 768, seed=2, scale=0.05, dtype=torch.bfloat16)
+    full = torch.empty(64, 2304, device=DEV)
+    ops.linear(x, w, None, out=full, impl="smallm")
+    for lo, hi in ((0, 1), (7, 9), (63, 64), (10, 40)):
+        part = torch.empty(hi - lo, 2304, device=DEV)
+        ops.linear(x[lo:hi], w, None, out=part, impl="smallm")
+        assert torch.equal(part, full[lo:hi])
+
+
 def test_linear_rows_do_not_depend_on_the_batch(ops):
     x, w = rnd(200, 96, seed=1), rnd(130, 96, seed=2)
     full = torch.empty(200, 130, device=DEV)
@@ -138,12 +173,53 @@ class _Ctx:
     pass
 
 
+def _ctx_for(case):
+    from mini_llm_b200.engine.context import Workspace
+    ctx = _Ctx()
+    ctx.token_seq = torch.tensor(case["token_seq"], dtype=torch.int32, device=DEV)
+    ctx.positions = torch.tensor(case["positions"], dtype=torch.int32, device=DEV)
+    ctx.ws = Workspace(torch.device(DEV), 64)
+    ctx.max_ctx_len = max(case["positions"]) + 1
+    ctx.decode_only = True
+    return ctx
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,dh,page,window", [(4, 4, 16, 16, None), (3, 3, 32, 8, None), (12, 12, 64, 16, None),
+                                                  (6, 2, 64, 4, None), (2, 2, 128, 32, 300), (4, 1, 64, 16, 37)])
+def test_decode_attention_split_keys(ops, dtype, H, Hkv, dh, page, window):
+    """Single tokens at contexts around the split (256) and page edges, beside the plain kernel."""
+    seqs = [(c, 1) for c in (1, 2, 16, 17, 255, 256, 257, 511, 512, 513, 700, 1024)]
+    case = _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages=4096 // page + 24, seed=dh + page)
+    ctx = _ctx_for(case)
+    q = case["q"].to(dtype).to(DEV)
+    kp, vp, bt = case["k_pages"].to(dtype).to(DEV), case["v_pages"].to(dtype).to(DEV), case["bt"].to(DEV)
+    scale = dh ** -0.5
+    out, plain = torch.empty_like(q), torch.empty_like(q)
+    kw = dict(num_heads=H, num_kv_heads=Hkv, head_dim=dh, scale=scale, window=window)
+    ops.paged_attention(q, kp, vp, bt, ctx, out, impl="decode", **kw)
+    ops.paged_attention(q, kp, vp, bt, ctx, plain, impl="simt", **kw)
+    want = _attention_reference(case, H, Hkv, dh, scale, window, dtype)
+    tol = 2e-5 if dtype == torch.float32 else 1e-2
+    assert (out.double().cpu() - want).abs().max() < tol
+    assert (out.double() - plain.double()).abs().max() < tol
+    # a token's result does not depend on the tokens beside it
+    one = _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages=4096 // page + 24, seed=dh + page)
+    for t in (0, 5, 11):
+        c1 = _Ctx()
+        c1.token_seq, c1.positions = ctx.token_seq[t:t + 1].clone(), ctx.positions[t:t + 1].clone()
+        c1.ws, c1.max_ctx_len, c1.decode_only = ctx.ws, int(ctx.positions[t]) + 1, True
+        o1 = torch.empty_like(q[t:t + 1])
+        ops.paged_attention(q[t:t + 1], kp, vp, bt, c1, o1, impl="decode", **kw)
+        assert torch.equal(o1, out[t:t + 1])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,Hkv,dh,page,window", [(4, 4, 16, 16, None), (3, 3, 32, 8, None), (6, 2, 64, 16, None),
                                                   (5, 1, 48, 4, None), (2, 2, 128, 32, 37), (2, 1, 256, 16, None)])
 def test_paged_attention_mixed_batch(ops, dtype, H, Hkv, dh, page, window):
     seqs = [(1, 1), (70, 1), (33, 33), (100, 7), (16, 2), (129, 1)]       # first tokens, decodes, whole and partial prompts
-    case = _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages=64, seed=H * 100 + dh)
+    case = _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages=128, seed=H * 100 + dh)
     # a far key that must dominate: query of the last sequence strongly matches its key at position 2
     K, V = case["dense"][5]
     t_last = len(case["token_seq"]) - 1
@@ -174,16 +250,16 @@ def test_paged_attention_finds_one_far_key_among_hundreds(ops, dtype):
         tab = case["bt"][0].tolist()
         case["k_pages"][tab[far // page], :, far % page] = K[far]
         case["v_pages"][tab[far // page], :, far % page] = V[far]
-        ctx = _Ctx()
-        ctx.token_seq = torch.zeros(1, dtype=torch.int32, device=DEV)
-        ctx.positions = torch.tensor([299], dtype=torch.int32, device=DEV)
+        ctx = _ctx_for(case)
         q = case["q"].to(dtype).to(DEV)
-        out = torch.empty_like(q)
-        ops.paged_attention(q, case["k_pages"].to(dtype).to(DEV), case["v_pages"].to(dtype).to(DEV), case["bt"].to(DEV),
-                            ctx, out, num_heads=H, num_kv_heads=H, head_dim=dh, scale=dh ** -0.5)
         want = _attention_reference(case, H, H, dh, dh ** -0.5, None, dtype)
-        assert (out.double().cpu() - want).abs().max() < (2e-5 if dtype == torch.float32 else 3e-2)
-        assert out.float().mean().item() > 6.5
+        for impl in ("simt", "decode"):
+            out = torch.empty_like(q)
+            ops.paged_attention(q, case["k_pages"].to(dtype).to(DEV), case["v_pages"].to(dtype).to(DEV),
+                                case["bt"].to(DEV), ctx, out, num_heads=H, num_kv_heads=H, head_dim=dh,
+                                scale=dh ** -0.5, impl=impl)
+            assert (out.double().cpu() - want).abs().max() < (2e-5 if dtype == torch.float32 else 3e-2), impl
+            assert out.float().mean().item() > 6.5, impl
 
 
 def test_paged_attention_refuses_sizes_it_cannot_take(ops):
