@@ -126,7 +126,7 @@ def ensure_built(verbose: Optional[bool] = None, force: bool = False) -> str:
             if force or not os.path.isfile(obj):
                 todo.append((s, obj))
         stamp = os.path.join(bdir, "lib.stamp")
-        lib_digest = hashlib.sha256(" ".join(objs).encode()).hexdigest()[:16]
+        lib_digest = hashlib.sha256(" ".join(os.path.basename(o) for o in objs).encode()).hexdigest()[:16]
         have = open(stamp).read().strip() if os.path.isfile(stamp) else ""
         if not todo and os.path.isfile(lib) and have == lib_digest:
             return lib

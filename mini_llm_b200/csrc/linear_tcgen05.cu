@@ -1,0 +1,386 @@
+// out = act(A[M,K] . W[N,K]^T + bias) (+ out) on the fifth-generation tensor cores:
+// the product of prefill steps (many rows), bfloat16 operands, 32-bit accumulation.
+//
+// One CTA computes one 128 x BN tile of the result.  Warp 0 (one elected lane) is the
+// producer: it moves 128 x 64 tiles of A and BN x 64 tiles of W from global memory to a
+// ring of shared-memory stages with TMA (cp.async.bulk.tensor, 128-byte swizzle; rows
+// and columns beyond the matrices are filled with zeros by the copy engine, so any M, N
+// and any K that is a multiple of 8 work).  Warp 1 (one lane) issues tcgen05.mma
+// (cta_group::1, kind::f16, M=128, N=BN, K=16, four per stage) with the accumulator in
+// tensor memory, and frees a stage with tcgen05.commit.  Warps 2..5 are the epilogue:
+// each reads its 32 lanes of the accumulator with tcgen05.ld, adds the bias, applies the
+// activation or the 32-bit residual sum, and stores its rows.
+//
+// The sum over K of one output element runs in the same order whatever M is (K tiles in
+// sequence, no split over K), so a row's result does not depend on the batch.
+// Every wait on an mbarrier is bounded: after the limit the kernel records an error code
+// in a device word that the host reads, lets its copies land, frees its tensor memory
+// and returns.
+//
+// The reference multiplies with FP32 SIMT tiles (src/kernels/gemm.cu:238-580), or cuBLAS
+// SGEMM when MINI_LLM_USE_CUBLAS is set (:119-156); it has no tensor-core path.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128, BK = 64;
+constexpr int THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;     // two seconds, then the wait gives up
+
+__device__ int g_tc_error = 0;          // first error code seen by any tcgen05 kernel
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait; false when the limit was hit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((i & 63) == 63) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols));
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 64
+// bf16 (128 bytes), groups of 8 rows 1024 bytes apart; version 1 (Blackwell), layout
+// type 2 (SWIZZLE_128B), leading offset 1 (unused for swizzled K-major).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor: D=F32 (bits 4-5 = 1), A=B=BF16 (bits 7-9, 10-12 = 1), both
+// K-major (bits 15, 16 = 0), N>>3 at bit 17, M>>4 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BN> struct Cfg {
+    static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+template <int BN, typename TO>
+__global__ void __launch_bounds__(THREADS, 1)
+linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                      const float* __restrict__ bias, TO* out, long long ldo, int M, int N, int K, int act,
+                      int accumulate, int vec_ok) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(tiles + (size_t)C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_ready = empty + C::STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    volatile int* failed = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int nk = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kt = 0; kt < nk; ++kt) {
+                const int s = kt % C::STAGES;
+                if (kt >= C::STAGES && !mbar_wait(&empty[s], ((kt / C::STAGES) - 1) & 1)) { *failed = 1; break; }
+                if (*failed) break;
+                uint8_t* a_dst = tiles + (size_t)s * C::STAGE_BYTES;
+                mbar_expect_tx(&full[s], C::STAGE_BYTES);
+                tma_load_2d(a_dst, &map_a, kt * BK, m0, &full[s]);
+                tma_load_2d(a_dst + C::A_BYTES, &map_w, kt * BK, n0, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BM, BN);
+            bool ok = true;
+            for (int kt = 0; kt < nk && ok; ++kt) {
+                const int s = kt % C::STAGES;
+                if (!mbar_wait(&full[s], (kt / C::STAGES) & 1)) { *failed = 2; ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
+                const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + C::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)      // 32 bytes along K inside the swizzle atom = +2 in the address field
+                    umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kt | k) != 0);
+                umma_commit(&empty[s]);                 // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(acc_ready);
+        }
+    } else {
+        const int q = warp & 3;                         // the quarter of the 128 TMEM lanes this warp may read
+        const int row = m0 + q * 32 + lane;
+        bool ok = mbar_wait(acc_ready, 0);
+        if (!ok) *failed = 3;
+        ok = __all_sync(0xffffffffu, ok && !*failed);      // tcgen05.ld is warp-wide: decide as a warp
+        tc_fence_after();
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+                const int nb = n0 + c * 32;
+                if (row < M && nb < N) {
+                    TO* o = out + (size_t)row * ldo + nb;
+                    const bool full_vec = vec_ok && nb + 32 <= N;
+                    if (full_vec) {
+                        constexpr int PER = 16 / sizeof(TO);              // elements per 16-byte store
+#pragma unroll
+                        for (int j = 0; j < 32; j += PER) {
+                            float v[PER];
+#pragma unroll
+                            for (int i = 0; i < PER; ++i) {
+                                float x = __uint_as_float(r[j + i]);
+                                if (bias) x += __ldg(bias + nb + j + i);
+                                v[i] = apply_act(x, act);
+                            }
+                            if constexpr (sizeof(TO) == 4) {
+                                float4* p = reinterpret_cast<float4*>(o + j);
+                                if (accumulate) {
+                                    const float4 old = *p;
+                                    v[0] += old.x; v[1] += old.y; v[2] += old.z; v[3] += old.w;
+                                }
+                                *p = make_float4(v[0], v[1], v[2], v[3]);
+                            } else {
+                                uint4 pk;
+                                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+                                if (accumulate) {
+                                    const uint4 old = *reinterpret_cast<const uint4*>(o + j);
+                                    const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) {
+                                        v[2 * i] += __low2float(oh[i]);
+                                        v[2 * i + 1] += __high2float(oh[i]);
+                                    }
+                                }
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                                *reinterpret_cast<uint4*>(o + j) = pk;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (nb + j < N) {
+                                float x = __uint_as_float(r[j]);
+                                if (bias) x += __ldg(bias + nb + j);
+                                x = apply_act(x, act);
+                                if (accumulate) x += to_f32(o[j]);
+                                o[j] = from_f32<TO>(x);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*failed) {
+        if (threadIdx.x == 0) atomicCAS(&g_tc_error, 0, *failed);
+        // copies already issued may still be writing this CTA's shared memory: let them land
+        for (int i = 0; i < 2000; ++i) __nanosleep(100);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, BN);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long long ld; int rows, cols, box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && ld == o.ld && rows == o.rows && cols == o.cols && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.ld;
+        h = h * 1000003u ^ (size_t)k.rows;
+        h = h * 1000003u ^ (size_t)k.cols;
+        h = h * 1000003u ^ (size_t)k.box_rows;
+        return h;
+    }
+};
+
+// A [rows, cols] bf16 matrix with row stride ld (elements), boxes of box_rows x 64, 128-byte swizzle.
+int get_map(const void* ptr, long long ld, int rows, int cols, int box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, ld, rows, cols, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return mllm_fail(3, "linear_tcgen05: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return mllm_fail(3, "linear_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, m);
+    *out = m;
+    return 0;
+}
+
+template <int BN, typename TO>
+int launch(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo, int M, int N,
+           int K, int act, int accumulate, cudaStream_t stream) {
+    using C = Cfg<BN>;
+    CUtensorMap ma, mw;
+    int rc = get_map(A, lda, M, K, BM, &ma);
+    if (rc) return rc;
+    rc = get_map(W, K, N, K, BN, &mw);
+    if (rc) return rc;
+    auto kern = linear_tcgen05_kernel<BN, TO>;
+    static bool set = false;
+    if (!set) {
+        MLLM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+        set = true;
+    }
+    const int vec_ok = ((uintptr_t)out % 16 == 0) && ((ldo * (long long)sizeof(TO)) % 16 == 0);
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    kern<<<grid, THREADS, C::SMEM, stream>>>(ma, mw, bias, (TO*)out, ldo, M, N, K, act, accumulate, vec_ok);
+    MLLM_CHECK_LAUNCH("linear_tcgen05");
+    return 0;
+}
+
+template <typename TO>
+int pick_bn(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo, int M, int N,
+            int K, int act, int accumulate, cudaStream_t stream) {
+    const long long mt = (M + BM - 1) / BM;
+    // the widest tile that still gives every one of the 148 SMs a CTA; else the narrowest
+    if (mt * ((N + 255) / 256) >= 148)
+        return launch<256, TO>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+    if (mt * ((N + 127) / 128) >= 148)
+        return launch<128, TO>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+    return launch<64, TO>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+}
+
+}  // namespace
+
+// The first error recorded by a tcgen05 kernel since the last call (0 = none); resets it.
+MLLM_EXPORT int mllm_tcgen05_error(int* code) {
+    int zero = 0;
+    MLLM_CUDA(cudaMemcpyFromSymbol(code, g_tc_error, sizeof(int)));
+    if (*code) MLLM_CUDA(cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int)));
+    return 0;
+}
+
+// bfloat16 A [M,K] (row stride lda) and W [N,K]; out bfloat16 or 32-bit.  Needs K and
+// lda multiples of 8 and 16-byte aligned operands (TMA's rules).
+MLLM_EXPORT int mllm_linear_tcgen05(const void* A, long long lda, const void* W, const float* bias, void* out,
+                                    long long ldo, int M, int N, int K, int act, int accumulate, int out_dtype,
+                                    cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || lda % 8 != 0)
+        return mllm_fail(1, "linear_tcgen05: K=%d and the row stride %lld must be multiples of 8", K, lda);
+    if ((uintptr_t)A % 16 != 0 || (uintptr_t)W % 16 != 0)
+        return mllm_fail(1, "linear_tcgen05: operands must be 16-byte aligned");
+    if ((M + BM - 1) / BM > 65535) return mllm_fail(1, "linear_tcgen05: M=%d exceeds the grid limit", M);
+    if (out_dtype == MLLM_BF16)
+        return pick_bn<__nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+    if (out_dtype == MLLM_F32)
+        return pick_bn<float>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+    return mllm_fail(1, "linear_tcgen05: unknown dtype code %d", out_dtype);
+}

@@ -43,6 +43,9 @@ def _signatures(lib):
                                 c_ll, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "mllm_linear_smallm": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_void_p],
+        "mllm_linear_tcgen05": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
+                                c_int, c_void_p],
+        "mllm_tcgen05_error": [c_void_p],
         "mllm_attention_decode": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                   c_int, c_void_p],
@@ -83,6 +86,19 @@ def _call(name: str, *args) -> None:
     rc = getattr(lib, name)(*args)
     if rc != 0:
         raise KernelError(f"{name}: {lib.mllm_last_error().decode(errors='replace')}")
+
+
+def check_device_errors() -> None:
+    """Raise if a tensor-core kernel gave up on a bounded wait since the last check.
+    Reads one device word (a synchronising copy): call it where the host waits anyway."""
+    code = c_int(0)
+    lib = library()
+    if lib.mllm_tcgen05_error(ctypes.byref(code)) != 0:
+        raise KernelError(lib.mllm_last_error().decode(errors="replace"))
+    if code.value:
+        who = {1: "the TMA producer (no free stage)", 2: "the MMA issuer (no full stage)",
+               3: "the epilogue (accumulator never ready)"}.get(code.value, "?")
+        raise KernelError(f"a tcgen05 kernel gave up waiting: code {code.value}, {who}")
 
 
 def _stream() -> int:
@@ -182,11 +198,11 @@ def linear(x, weight, bias, out, act: Optional[str] = None, accumulate: bool = F
         raise KernelError("linear: float32 operands need a float32 result")
     if impl is None:
         impl = "simt"
-        if x.dtype == torch.bfloat16 and M <= SMALL_M and K % 8 == 0 and lda % 8 == 0 \
+        if x.dtype == torch.bfloat16 and K % 8 == 0 and lda % 8 == 0 \
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
-            impl = "smallm"
-    if impl == "smallm":
-        _call("mllm_linear_smallm", x.data_ptr(), lda, weight.data_ptr(),
+            impl = "smallm" if M <= SMALL_M else "tcgen05"
+    if impl in ("smallm", "tcgen05"):
+        _call("mllm_linear_" + impl, x.data_ptr(), lda, weight.data_ptr(),
               bias.data_ptr() if bias is not None else None, out.data_ptr(), ldo, M, N, K, _ACT[act],
               int(accumulate), _dt(out), _stream())
         return out

@@ -107,6 +107,51 @@ def test_linear_small_m_against_the_plain_kernel(ops, out_dtype, M, N, K):
     assert (acc.double() - want).abs().max() < 1e-4
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(65, 64, 64), (128, 128, 64), (129, 130, 72), (300, 200, 40), (2048, 2304, 768),
+                                   (2048, 768, 3072), (257, 1003, 96), (70, 50257, 128), (1000, 320, 8)])
+def test_linear_tcgen05_against_the_plain_kernel(ops, out_dtype, M, N, K):
+    """The TMA + tcgen05 product beside its plain twin and float64: tails in M, N and K,
+    every epilogue, a sliced input, an output whose rows are not 16-byte aligned."""
+    dt = torch.bfloat16
+    x, w, b = rnd(M, K, seed=1, dtype=dt), rnd(N, K, seed=2, scale=K ** -0.5, dtype=dt), rnd(N, seed=3)
+    ref = x.double() @ w.double().t() + b.double()
+    tol = 3e-5 if out_dtype == torch.float32 else 1e-2
+    for act in (None, "gelu_tanh", "gelu_erf"):
+        out = torch.full((M, N), 7.0, device=DEV, dtype=out_dtype)
+        ops.linear(x, w, b, out=out, act=act, impl="tcgen05")
+        ops.check_device_errors()
+        want = ref if act is None else torch.nn.functional.gelu(ref, approximate="tanh" if act == "gelu_tanh" else "none")
+        assert (out.double() - want).abs().max() < tol * max(1.0, want.abs().max().item()), act
+    plain = torch.empty(M, N, device=DEV, dtype=out_dtype)
+    out = torch.empty(M, N, device=DEV, dtype=out_dtype)
+    ops.linear(x, w, None, out=plain, impl="simt")
+    ops.linear(x, w, None, out=out, impl="tcgen05")
+    assert (out.double() - plain.double()).abs().max() < tol * max(1.0, ref.abs().max().item())
+    acc = rnd(M, N, seed=4)
+    acc0 = acc.clone()
+    wide = rnd(M, K + 16, seed=5, dtype=dt)
+    ops.linear(wide[:, 8:8 + K], w, b, out=acc, accumulate=True, impl="tcgen05")
+    want = acc0.double() + wide[:, 8:8 + K].double() @ w.double().t() + b.double()
+    assert (acc.double() - want).abs().max() < 1e-4 * max(1.0, want.abs().max().item())
+    pad = torch.zeros(M, N + 3, device=DEV, dtype=out_dtype)             # row stride not a multiple of 16 bytes
+    ops.linear(x, w, b, out=pad[:, :N], impl="tcgen05")
+    assert (pad[:, :N].double() - ref).abs().max() < tol * max(1.0, ref.abs().max().item())
+    assert torch.all(pad[:, N:] == 0)
+    ops.check_device_errors()
+
+
+def test_linear_tcgen05_rows_do_not_depend_on_the_batch(ops):
+    x, w = rnd(600, 768, seed=1, dtype=torch.bfloat16), rnd(2304, 768, seed=2, scale=0.05, dtype=torch.bfloat16)
+    full = torch.empty(600, 2304, device=DEV)
+    ops.linear(x, w, None, out=full, impl="tcgen05")
+    for lo, hi in ((0, 65), (100, 400), (513, 600)):
+        part = torch.empty(hi - lo, 2304, device=DEV)
+        ops.linear(x[lo:hi], w, None, out=part, impl="tcgen05")
+        assert torch.equal(part, full[lo:hi])
+    ops.check_device_errors()
+
+
 def test_linear_small_m_rows_do_not_depend_on_the_batch(ops):
     x, w = rnd(64, 768, seed=1, dtype=torch.bfloat16), rnd(2304, 768, seed=2, scale=0.05, dtype=torch.bfloat16)
     full = torch.empty(64, 2304, device=DEV)
