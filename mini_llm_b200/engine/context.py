@@ -37,15 +37,17 @@ class StepLayout:
     S: int
     R: int
     max_pages: Tuple[int, ...]
+    n_tiles: int = 0
     offsets: Dict[str, int] = field(default_factory=dict)
     total: int = 0
 
     @classmethod
-    def make(cls, T: int, S: int, R: int, max_pages: Sequence[int]) -> "StepLayout":
-        lay = cls(T, S, R, tuple(max_pages))
+    def make(cls, T: int, S: int, R: int, max_pages: Sequence[int], n_tiles: int = 0) -> "StepLayout":
+        lay = cls(T, S, R, tuple(max_pages), n_tiles)
         off = 0
         for name, n in (("token_ids", T), ("positions", T), ("token_seq", T), ("logit_rows", R),
-                        ("state_slots", S), ("cu_q", S + 1), ("q_start", S), ("ctx_len", S)):
+                        ("state_slots", S), ("cu_q", S + 1), ("q_start", S), ("ctx_len", S),
+                        ("attn_tiles", 3 * n_tiles)):
             lay.offsets[name] = off
             off += _pad4(n)
         for g, mp in enumerate(max_pages):
@@ -57,7 +59,7 @@ class StepLayout:
         return lay
 
     def key(self):
-        return (self.T, self.S, self.R, self.max_pages)
+        return (self.T, self.S, self.R, self.max_pages, self.n_tiles)
 
 
 class Workspace:
@@ -117,6 +119,9 @@ class StepContext:
         self.cu_q = sec("cu_q", self.S + 1)
         self.q_start = sec("q_start", self.S)
         self.ctx_len = sec("ctx_len", self.S)
+        # query tiles of the tensor-core attention: (request index, first flat token, rows)
+        self.attn_tiles = sec("attn_tiles", 3 * layout.n_tiles)
+        self.n_tiles = layout.n_tiles
         self.groups: List[GroupView] = []
         for g, mp in enumerate(layout.max_pages):
             bt = dev[o[f"block_table.{g}"]:o[f"block_table.{g}"] + self.S * mp].view(self.S, mp)
@@ -129,8 +134,23 @@ class StepContext:
         self.decode_only = self.max_q_len == 1
 
 
+ATTN_TILE = 64      # query rows per tile of csrc/attention_flash.cu
+
+
+def attention_tiles(q_lens: Sequence[int]) -> List[int]:
+    """Cut every request's new tokens into tiles of at most ATTN_TILE rows; longest
+    contexts first would balance better, but the order is kept simple and fixed."""
+    out: List[int] = []
+    base = 0
+    for s, n in enumerate(q_lens):
+        for q0 in range(0, n, ATTN_TILE):
+            out += [s, base + q0, min(ATTN_TILE, n - q0)]
+        base += n
+    return out
+
+
 def pack_step(layout: StepLayout, host: np.ndarray, *, token_ids, positions, token_seq, logit_rows, state_slots,
-              cu_q, q_start, ctx_len, slot_mappings, block_tables) -> None:
+              cu_q, q_start, ctx_len, slot_mappings, block_tables, attn_tiles=()) -> None:
     """Write every section into the int32 array ``host`` (length >= layout.total)."""
     o = layout.offsets
 
@@ -146,6 +166,8 @@ def pack_step(layout: StepLayout, host: np.ndarray, *, token_ids, positions, tok
     put("cu_q", cu_q)
     put("q_start", q_start)
     put("ctx_len", ctx_len)
+    if layout.n_tiles:
+        put("attn_tiles", attn_tiles)
     for g, mp in enumerate(layout.max_pages):
         put(f"slot_mapping.{g}", slot_mappings[g])
         bt = np.zeros((layout.S, mp), dtype=np.int32)

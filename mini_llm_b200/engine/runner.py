@@ -21,7 +21,7 @@ from ..cache.manager import CacheManager
 from ..config.base import EngineConfig, ModelConfig, get_architecture, load_config
 from ..parts.model import Model
 from ..weights.loader import load_weights
-from .context import StepContext, StepLayout, Workspace, pack_step
+from .context import StepContext, StepLayout, Workspace, attention_tiles, pack_step
 
 
 class StepError(RuntimeError):
@@ -197,12 +197,13 @@ class ModelRunner:
         for g in range(ng):
             mp = max(len(t) for t in tables[g])
             max_pages.append(max(16, (mp + 15) // 16 * 16))    # wide steps: few distinct shapes for captured graphs
-        layout = StepLayout.make(len(token_ids), len(entries), len(logit_rows), max_pages)
+        tiles = [] if max(q_lens) == 1 else attention_tiles(q_lens)
+        layout = StepLayout.make(len(token_ids), len(entries), len(logit_rows), max_pages, len(tiles) // 3)
         i, host = self._staging(layout.total)
         self._last_layout_total = layout.total
         pack_step(layout, host.numpy(), token_ids=token_ids, positions=positions, token_seq=token_seq,
                   logit_rows=logit_rows, state_slots=slots, cu_q=cu_q, q_start=q_start, ctx_len=ctx_len,
-                  slot_mappings=slot_maps, block_tables=tables)
+                  slot_mappings=slot_maps, block_tables=tables, attn_tiles=tiles)
         self._dev[:layout.total].copy_(host[:layout.total], non_blocking=True)
         self._host_events[i].record()
         return StepContext(layout, self._dev, self.ws, q_lens=q_lens, q_starts=q_start)

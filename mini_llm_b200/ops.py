@@ -18,6 +18,7 @@ from .csrc import build as _build
 F32, BF16 = 0, 1
 SMALL_M = 64                 # rows up to which the weight-streaming product is used
 DECODE_SPLIT = 256           # keys per split of the decode attention (csrc/attention_decode.cu)
+_FLASH_HEAD_DIMS = (16, 32, 64, 128)
 _DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16, 32, 64, 128)}
 _ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}
 _lib = None
@@ -49,6 +50,8 @@ def _signatures(lib):
         "mllm_attention_decode": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                   c_int, c_void_p],
+        "mllm_attention_flash": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                 c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mllm_argmax": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
         "mllm_sample": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     }
@@ -258,6 +261,18 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
         if getattr(ctx, "decode_only", False) and head_dim in _DECODE_HEAD_DIMS[q.dtype] and ldq % 8 == 0 \
                 and q.data_ptr() % 16 == 0:
             impl = "decode"
+        elif q.dtype == torch.bfloat16 and head_dim in _FLASH_HEAD_DIMS and getattr(ctx, "n_tiles", 0) > 0 \
+                and ldq % 8 == 0 and q.data_ptr() % 16 == 0 and ldo % 2 == 0:
+            impl = "flash"
+    if impl == "flash":
+        if q.dtype != torch.bfloat16 or head_dim not in _FLASH_HEAD_DIMS:
+            raise KernelError(f"paged_attention: the tensor-core kernel takes bfloat16 and head sizes "
+                              f"{_FLASH_HEAD_DIMS}, not {q.dtype} / {head_dim}")
+        _call("mllm_attention_flash", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(),
+              block_table.data_ptr(), bt_stride, ctx.attn_tiles.data_ptr(), int(ctx.n_tiles),
+              ctx.positions.data_ptr(), out.data_ptr(), ldo, num_heads, num_kv_heads, head_dim, ps, float(scale),
+              int(window or 0), _stream())
+        return
     if impl == "decode":
         if head_dim not in _DECODE_HEAD_DIMS[q.dtype]:
             raise KernelError(f"paged_attention: the split-key kernel takes head sizes {_DECODE_HEAD_DIMS[q.dtype]} "
