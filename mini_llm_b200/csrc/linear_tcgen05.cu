@@ -8,8 +8,10 @@
 // and any K that is a multiple of 8 work).  Warp 1 (one lane) issues tcgen05.mma
 // (cta_group::1, kind::f16, M=128, N=BN, K=16, four per stage) with the accumulator in
 // tensor memory, and frees a stage with tcgen05.commit.  Warps 2..5 are the epilogue:
-// each reads its 32 lanes of the accumulator with tcgen05.ld, adds the bias, applies the
-// activation or the 32-bit residual sum, and stores its rows.
+// each reads its 32 lanes of the accumulator with tcgen05.ld into the (by then free)
+// stage memory, then walks its rows with a lane per 4 columns, so that the bias stays in
+// registers, the activation or the 32-bit residual sum is applied, and every store
+// instruction writes one contiguous piece of a row.
 //
 // The sum over K of one output element runs in the same order whatever M is (K tiles in
 // sequence, no split over K), so a row's result does not depend on the batch.
@@ -184,64 +186,82 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
     } else {
         const int q = warp & 3;                         // the quarter of the 128 TMEM lanes this warp may read
-        const int row = m0 + q * 32 + lane;
         bool ok = mbar_wait(acc_ready, 0);
         if (!ok) *failed = 3;
         ok = __all_sync(0xffffffffu, ok && !*failed);      // tcgen05.ld is warp-wide: decide as a warp
         tc_fence_after();
         if (ok) {
+            // Phase A: accumulator -> shared memory (the stage ring is free: every MMA has completed).
+            // A thread holds one row; rows are padded by 4 floats so 16-byte stores spread over the banks.
+            constexpr int SROW = BN + 4;
+            float* stage = reinterpret_cast<float*>(tiles) + (size_t)(q * 32) * SROW;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
-                const int nb = n0 + c * 32;
-                if (row < M && nb < N) {
-                    TO* o = out + (size_t)row * ldo + nb;
-                    const bool full_vec = vec_ok && nb + 32 <= N;
-                    if (full_vec) {
-                        constexpr int PER = 16 / sizeof(TO);              // elements per 16-byte store
+                float4* dst = reinterpret_cast<float4*>(stage + (size_t)lane * SROW + c * 32);
 #pragma unroll
-                        for (int j = 0; j < 32; j += PER) {
-                            float v[PER];
+                for (int j = 0; j < 8; ++j)
+                    dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                         __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            }
+            __syncwarp();
+            // Phase B: the warp walks its 32 rows; a lane owns 4 consecutive columns per pass of 128, so the
+            // bias sits in registers and every store instruction covers one contiguous piece of a row.
+            constexpr int PASSES = (BN + 127) / 128;
+            float bv[PASSES][4];
 #pragma unroll
-                            for (int i = 0; i < PER; ++i) {
-                                float x = __uint_as_float(r[j + i]);
-                                if (bias) x += __ldg(bias + nb + j + i);
-                                v[i] = apply_act(x, act);
+            for (int p = 0; p < PASSES; ++p)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int n = n0 + p * 128 + lane * 4 + i;
+                    bv[p][i] = (bias && p * 128 + lane * 4 + i < BN && n < N) ? __ldg(bias + n) : 0.f;
+                }
+#pragma unroll 1
+            for (int rr = 0; rr < 32; ++rr) {
+                const int row = m0 + q * 32 + rr;
+                if (row >= M) break;
+                const float* src = stage + (size_t)rr * SROW;
+#pragma unroll
+                for (int p = 0; p < PASSES; ++p) {
+                    const int col = p * 128 + lane * 4;
+                    if (col >= BN) continue;
+                    const int n = n0 + col;
+                    if (n >= N) continue;
+                    const float4 a = *reinterpret_cast<const float4*>(src + col);
+                    float v[4] = {a.x + bv[p][0], a.y + bv[p][1], a.z + bv[p][2], a.w + bv[p][3]};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) v[i] = apply_act(v[i], act);
+                    TO* o = out + (size_t)row * ldo + n;
+                    if (vec_ok && n + 4 <= N) {
+                        if constexpr (sizeof(TO) == 4) {
+                            float4* po = reinterpret_cast<float4*>(o);
+                            if (accumulate) {
+                                const float4 old = *po;
+                                v[0] += old.x; v[1] += old.y; v[2] += old.z; v[3] += old.w;
                             }
-                            if constexpr (sizeof(TO) == 4) {
-                                float4* p = reinterpret_cast<float4*>(o + j);
-                                if (accumulate) {
-                                    const float4 old = *p;
-                                    v[0] += old.x; v[1] += old.y; v[2] += old.z; v[3] += old.w;
-                                }
-                                *p = make_float4(v[0], v[1], v[2], v[3]);
-                            } else {
-                                uint4 pk;
-                                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-                                if (accumulate) {
-                                    const uint4 old = *reinterpret_cast<const uint4*>(o + j);
-                                    const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-                                    for (int i = 0; i < 4; ++i) {
-                                        v[2 * i] += __low2float(oh[i]);
-                                        v[2 * i + 1] += __high2float(oh[i]);
-                                    }
-                                }
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                                *reinterpret_cast<uint4*>(o + j) = pk;
+                            *po = make_float4(v[0], v[1], v[2], v[3]);
+                        } else {
+                            uint2* po = reinterpret_cast<uint2*>(o);
+                            if (accumulate) {
+                                const uint2 old = *po;
+                                const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&old);
+                                v[0] += __low2float(oh[0]); v[1] += __high2float(oh[0]);
+                                v[2] += __low2float(oh[1]); v[3] += __high2float(oh[1]);
                             }
+                            uint2 pk;
+                            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+                            h[0] = __floats2bfloat162_rn(v[0], v[1]);
+                            h[1] = __floats2bfloat162_rn(v[2], v[3]);
+                            *po = pk;
                         }
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (nb + j < N) {
-                                float x = __uint_as_float(r[j]);
-                                if (bias) x += __ldg(bias + nb + j);
-                                x = apply_act(x, act);
-                                if (accumulate) x += to_f32(o[j]);
-                                o[j] = from_f32<TO>(x);
+                        for (int i = 0; i < 4; ++i) {
+                            if (n + i < N) {
+                                float x = v[i];
+                                if (accumulate) x += to_f32(o[i]);
+                                o[i] = from_f32<TO>(x);
                             }
                         }
                     }
@@ -338,7 +358,8 @@ int launch(const void* A, long long lda, const void* W, const float* bias, void*
         MLLM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
         set = true;
     }
-    const int vec_ok = ((uintptr_t)out % 16 == 0) && ((ldo * (long long)sizeof(TO)) % 16 == 0);
+    // 4 consecutive outputs per store: 16 bytes (32-bit) or 8 bytes (bfloat16); column offsets are multiples of 4
+    const int vec_ok = ((uintptr_t)out % (4 * sizeof(TO)) == 0) && (ldo % 4 == 0);
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     kern<<<grid, THREADS, C::SMEM, stream>>>(ma, mw, bias, (TO*)out, ldo, M, N, K, act, accumulate, vec_ok);
     MLLM_CHECK_LAUNCH("linear_tcgen05");

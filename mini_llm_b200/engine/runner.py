@@ -223,18 +223,21 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ CUDA graphs
     def _forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
-        """Decode-only steps are launch-bound (about a hundred small kernels), so a step
-        shape seen before is replayed as one CUDA graph; everything else runs eagerly.
-        A graph fixes grid sizes and buffer addresses: its key holds every host-side
-        number a launch depends on, and all graphs are dropped when a scratch buffer
-        is replaced by a larger one."""
-        if not (self.engine.use_cuda_graphs and ctx.decode_only):
-            return self.model.forward(ctx)
+        """A step is about a hundred launches; issued one by one from Python they cost
+        more host time than a decode step or a 2,048-token prefill takes on the GPU.  So a
+        step shape that comes back (the same numbers of tokens, requests, wanted rows,
+        block-table width, attention tiles and key splits: every host-side number a launch
+        depends on) is captured once as a CUDA graph and replayed; a shape seen for the
+        first time runs eagerly.  All graphs are dropped when a scratch buffer is replaced
+        by a larger one, since a graph fixes buffer addresses."""
+        if not self.engine.use_cuda_graphs:
+            with ops.stream_scope():
+                return self.model.forward(ctx)
         if self._graph_version != self.ws.version:
             self._graphs.clear()
             self._graph_seen.clear()
             self._graph_version = self.ws.version
-        key = (ctx.layout.key(), -(-ctx.max_ctx_len // ops.DECODE_SPLIT))
+        key = (ctx.layout.key(), -(-ctx.max_ctx_len // ops.DECODE_SPLIT) if ctx.decode_only else 0)
         g = self._graphs.get(key)
         if g is not None:
             g[0].replay()
@@ -242,21 +245,28 @@ class ModelRunner:
             ops.launches += self.graph_kernels[key]
             return g[1]
         seen = self._graph_seen.get(key, 0)
+        if len(self._graph_seen) > 4096:
+            self._graph_seen.clear()
         self._graph_seen[key] = seen + 1
         if seen == 0:
-            return self.model.forward(ctx)             # first time: eager, buffers get allocated
+            with ops.stream_scope():
+                return self.model.forward(ctx)         # first time: eager, buffers get allocated
         version = self.ws.version
         torch.cuda.current_stream().synchronize()
         graph = torch.cuda.CUDAGraph()
         n0 = ops.launches
         with torch.cuda.graph(graph):
-            logits = self.model.forward(ctx)
+            with ops.stream_scope():
+                logits = self.model.forward(ctx)
         kernels = ops.launches - n0
         if self.ws.version != version:                  # a buffer was allocated during capture: do not keep it
             self._graph_version = -1
-            return self.model.forward(ctx)
+            with ops.stream_scope():
+                return self.model.forward(ctx)
         if len(self._graphs) >= 64:
-            self._graphs.pop(next(iter(self._graphs)))
+            old = next(iter(self._graphs))
+            self._graphs.pop(old)
+            self.graph_kernels.pop(old, None)
         self._graphs[key] = (graph, logits)
         self.graph_kernels[key] = kernels
         ops.launches = n0 + kernels

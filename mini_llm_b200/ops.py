@@ -104,8 +104,26 @@ def check_device_errors() -> None:
         raise KernelError(f"a tcgen05 kernel gave up waiting: code {code.value}, {who}")
 
 
+_stream_handle = None     # set by stream_scope(); None: ask torch on every call
+
+
+class stream_scope:
+    """Within the scope every launch goes to the stream that is current on entry, without
+    asking torch again on each call (a lookup costs more than the launch itself)."""
+
+    def __enter__(self):
+        global _stream_handle
+        self._old = _stream_handle
+        _stream_handle = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *a):
+        global _stream_handle
+        _stream_handle = self._old
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return _stream_handle if _stream_handle is not None else torch.cuda.current_stream().cuda_stream
 
 
 def _dt(t: torch.Tensor) -> int:
