@@ -37,17 +37,64 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MT, int RT, typename TO>
+// Fused LayerNorm on the input (x is then the 32-bit residual stream, optionally gathered by
+// `rows`): every CTA computes mean and 1/std of its M rows itself (M <= 64 rows of K floats
+// from L2) and normalises the values as it loads them, rounding to bfloat16 exactly where a
+// separate norm kernel would have stored them.
+struct NormArgs {
+    const float* x;          // [*, K] 32-bit, row stride ldx
+    const int* rows;         // optional gather
+    const float* gamma;
+    const float* beta;
+    float eps;
+};
+// Fused cache write on the output of a Q|K|V projection: columns [0, q_size) go to q_out,
+// the key and value columns go straight to their page slots
+// ([page][kv_head][offset][head_dim], slot = page * page_size + offset).
+struct KvArgs {
+    __nv_bfloat16* k_pages;
+    __nv_bfloat16* v_pages;
+    const int* slots;
+    int q_size, kv_heads, head_dim, page_size;
+};
+
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int MT, int RT, typename TO, bool LN, bool KVW>
 __global__ void __launch_bounds__(WARPS * 32)
 linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ W,
                      const float* __restrict__ bias, TO* out, long long ldo, int M, int N, int K, int act,
-                     int accumulate) {
+                     int accumulate, NormArgs ln, KvArgs kv) {
     extern __shared__ float red[];                 // [WARPS][16*RT][8*MT]
+    __shared__ float s_mean[LN ? 64 : 1], s_rstd[LN ? 64 : 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * (16 * RT);
     const int nchunks = (K + 31) / 32;
-    constexpr int U = RT == 1 ? 4 : (RT == 2 ? 2 : 1);
+    constexpr int U = LN ? 1 : (RT == 1 ? 4 : (RT == 2 ? 2 : 1));
+    if constexpr (LN) {
+        for (int m = warp; m < M; m += WARPS) {
+            const float* xr = ln.x + (size_t)(ln.rows ? ln.rows[m] : m) * ldx;
+            float s = 0.f;
+            for (int k = lane * 4; k < K; k += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(xr + k);
+                s += (v.x + v.y) + (v.z + v.w);
+            }
+            const float mean = warp_sum(s) / (float)K;
+            float q = 0.f;
+            for (int k = lane * 4; k < K; k += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(xr + k);
+                const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+                q += (a * a + b * b) + (c * c + d * d);
+            }
+            const float var = warp_sum(q) / (float)K;
+            if (lane == 0) { s_mean[m] = mean; s_rstd[m] = rsqrtf(var + ln.eps); }
+        }
+        __syncthreads();
+    }
 
     float acc[RT][MT][4];
 #pragma unroll
@@ -73,7 +120,24 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 const int row = m * 8 + g;
-                xv[u][m] = (kok && row < M) ? ldg16_cached(x + (size_t)row * ldx + k) : zero;
+                if constexpr (LN) {
+                    xv[u][m] = zero;
+                    if (kok && row < M) {
+                        const float* xr = ln.x + (size_t)(ln.rows ? ln.rows[row] : row) * ldx + k;
+                        const float4 a = *reinterpret_cast<const float4*>(xr), b = *reinterpret_cast<const float4*>(xr + 4);
+                        const float4 ga = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
+                        const float4 gb = __ldg(reinterpret_cast<const float4*>(ln.gamma + k + 4));
+                        const float4 ba = __ldg(reinterpret_cast<const float4*>(ln.beta + k));
+                        const float4 bb = __ldg(reinterpret_cast<const float4*>(ln.beta + k + 4));
+                        const float mu = s_mean[row], rs = s_rstd[row];
+                        xv[u][m].x = pack2((a.x - mu) * rs * ga.x + ba.x, (a.y - mu) * rs * ga.y + ba.y);
+                        xv[u][m].y = pack2((a.z - mu) * rs * ga.z + ba.z, (a.w - mu) * rs * ga.w + ba.w);
+                        xv[u][m].z = pack2((b.x - mu) * rs * gb.x + bb.x, (b.y - mu) * rs * gb.y + bb.y);
+                        xv[u][m].w = pack2((b.z - mu) * rs * gb.z + bb.z, (b.w - mu) * rs * gb.w + bb.w);
+                    }
+                } else {
+                    xv[u][m] = (kok && row < M) ? ldg16_cached(x + (size_t)row * ldx + k) : zero;
+                }
             }
         }
 #pragma unroll
@@ -110,17 +174,37 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
         for (int w = 0; w < WARPS; ++w) v += red[(size_t)w * ROWS * COLS + row * COLS + col];
         if (bias) v += bias[n];
         v = apply_act(v, act);
+        if constexpr (KVW) {
+            if (n >= kv.q_size) {
+                const int slot = kv.slots[col];
+                if (slot < 0) continue;
+                const int c = n - kv.q_size, kvs = kv.kv_heads * kv.head_dim;
+                const int which = c / kvs, cc = c % kvs;
+                const int head = cc / kv.head_dim, d = cc % kv.head_dim;
+                const size_t dst = (((size_t)(slot / kv.page_size) * kv.kv_heads + head) * kv.page_size +
+                                    slot % kv.page_size) * kv.head_dim + d;
+                (which == 0 ? kv.k_pages : kv.v_pages)[dst] = __float2bfloat16_rn(v);
+                continue;
+            }
+        }
         TO* o = out + (size_t)col * ldo + n;
         if (accumulate) v += to_f32(*o);
         *o = from_f32<TO>(v);
     }
 }
 
-template <int MT, int RT, typename TO>
-int launch(const void* x, long long ldx, const void* W, const float* bias, void* out, long long ldo, int M, int N,
-           int K, int act, int accumulate, cudaStream_t stream) {
+struct Call {
+    const void* x; long long ldx; const void* W; const float* bias; void* out; long long ldo;
+    int M, N, K, act, accumulate;
+    const NormArgs* ln;       // null: plain bfloat16 input
+    const KvArgs* kv;         // null: plain output
+    cudaStream_t stream;
+};
+
+template <int MT, int RT, typename TO, bool LN, bool KVW>
+int launch_k(const Call& c) {
     const size_t smem = (size_t)WARPS * 16 * RT * 8 * MT * sizeof(float);
-    auto kern = linear_smallm_kernel<MT, RT, TO>;
+    auto kern = linear_smallm_kernel<MT, RT, TO, LN, KVW>;
     if (smem > 48 * 1024) {
         static bool set = false;                   // per instantiation
         if (!set) {
@@ -128,28 +212,65 @@ int launch(const void* x, long long ldx, const void* W, const float* bias, void*
             set = true;
         }
     }
-    const int grid = (N + 16 * RT - 1) / (16 * RT);
-    kern<<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, bias, (TO*)out,
-                                             ldo, M, N, K, act, accumulate);
+    const int grid = (c.N + 16 * RT - 1) / (16 * RT);
+    kern<<<grid, WARPS * 32, smem, c.stream>>>((const __nv_bfloat16*)c.x, c.ldx, (const __nv_bfloat16*)c.W, c.bias,
+                                               (TO*)c.out, c.ldo, c.M, c.N, c.K, c.act, c.accumulate,
+                                               c.ln ? *c.ln : NormArgs{}, c.kv ? *c.kv : KvArgs{});
     MLLM_CHECK_LAUNCH("linear_smallm");
     return 0;
 }
 
+template <int MT, int RT, typename TO>
+int pick_fusion(const Call& c) {
+    if (c.kv) {
+        if constexpr (sizeof(TO) == 2) {
+            if (c.ln) return launch_k<MT, RT, TO, true, true>(c);
+            return launch_k<MT, RT, TO, false, true>(c);
+        } else {
+            return mllm_fail(1, "linear_smallm: the cache-writing epilogue produces bfloat16");
+        }
+    }
+    if (c.ln) return launch_k<MT, RT, TO, true, false>(c);
+    return launch_k<MT, RT, TO, false, false>(c);
+}
+
 template <int MT, typename TO>
-int pick_rt(int rt, const void* x, long long ldx, const void* W, const float* bias, void* out, long long ldo, int M,
-            int N, int K, int act, int accumulate, cudaStream_t stream) {
-    if (rt == 4) return launch<MT, 4, TO>(x, ldx, W, bias, out, ldo, M, N, K, act, accumulate, stream);
-    if (rt == 2) return launch<MT, 2, TO>(x, ldx, W, bias, out, ldo, M, N, K, act, accumulate, stream);
-    return launch<MT, 1, TO>(x, ldx, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+int pick_rt(int rt, const Call& c) {
+    if (rt == 4) return pick_fusion<MT, 4, TO>(c);
+    if (rt == 2) return pick_fusion<MT, 2, TO>(c);
+    return pick_fusion<MT, 1, TO>(c);
 }
 
 template <typename TO>
-int pick_mt(int rt, const void* x, long long ldx, const void* W, const float* bias, void* out, long long ldo, int M,
-            int N, int K, int act, int accumulate, cudaStream_t stream) {
-    if (M <= 8) return pick_rt<1, TO>(rt, x, ldx, W, bias, out, ldo, M, N, K, act, accumulate, stream);
-    if (M <= 16) return pick_rt<2, TO>(rt, x, ldx, W, bias, out, ldo, M, N, K, act, accumulate, stream);
-    if (M <= 32) return pick_rt<4, TO>(rt, x, ldx, W, bias, out, ldo, M, N, K, act, accumulate, stream);
-    return pick_rt<8, TO>(rt, x, ldx, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+int pick_mt(int rt, const Call& c) {
+    if (c.M <= 8) return pick_rt<1, TO>(rt, c);
+    if (c.M <= 16) return pick_rt<2, TO>(rt, c);
+    if (c.M <= 32) return pick_rt<4, TO>(rt, c);
+    return pick_rt<8, TO>(rt, c);
+}
+
+int dispatch(const Call& c, int out_dtype) {
+    if (c.M <= 0 || c.N <= 0) return 0;
+    if (c.M > 64) return mllm_fail(1, "linear_smallm: M=%d exceeds 64", c.M);
+    if (c.K <= 0 || c.K % 8 != 0) return mllm_fail(1, "linear_smallm: K=%d is not a multiple of 8", c.K);
+    if ((uintptr_t)c.W % 16 != 0) return mllm_fail(1, "linear_smallm: the weight must be 16-byte aligned");
+    if (c.ln) {
+        if (c.ldx % 4 != 0 || (uintptr_t)c.ln->x % 16 != 0 || (uintptr_t)c.ln->gamma % 16 != 0 ||
+            (uintptr_t)c.ln->beta % 16 != 0)
+            return mllm_fail(1, "linear_smallm: the normed input, gamma and beta must be 16-byte aligned");
+    } else if (c.ldx % 8 != 0 || (uintptr_t)c.x % 16 != 0) {
+        return mllm_fail(1, "linear_smallm: the input must be 16-byte aligned");
+    }
+    if (c.kv && (c.N != c.kv->q_size + 2 * c.kv->kv_heads * c.kv->head_dim || c.kv->page_size <= 0))
+        return mllm_fail(1, "linear_smallm: %d output columns do not split into %d query and 2 x %d x %d cache columns",
+                         c.N, c.kv->q_size, c.kv->kv_heads, c.kv->head_dim);
+    // rows per CTA: enough CTAs to fill the 148 SMs when N allows it
+    int rt = 1;
+    if (c.N >= 16 * 4 * 296) rt = 4;
+    else if (c.N >= 16 * 2 * 296) rt = 2;
+    if (out_dtype == MLLM_BF16) return pick_mt<__nv_bfloat16>(rt, c);
+    if (out_dtype == MLLM_F32) return pick_mt<float>(rt, c);
+    return mllm_fail(1, "linear_smallm: unknown dtype code %d", out_dtype);
 }
 
 }  // namespace
@@ -159,18 +280,23 @@ int pick_mt(int rt, const void* x, long long ldx, const void* W, const float* bi
 MLLM_EXPORT int mllm_linear_smallm(const void* x, long long ldx, const void* W, const float* bias, void* out,
                                    long long ldo, int M, int N, int K, int act, int accumulate, int out_dtype,
                                    cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return 0;
-    if (M > 64) return mllm_fail(1, "linear_smallm: M=%d exceeds 64", M);
-    if (K <= 0 || K % 8 != 0) return mllm_fail(1, "linear_smallm: K=%d is not a multiple of 8", K);
-    if (ldx % 8 != 0 || (uintptr_t)x % 16 != 0 || (uintptr_t)W % 16 != 0)
-        return mllm_fail(1, "linear_smallm: operands must be 16-byte aligned");
-    // rows per CTA: enough CTAs to fill the 148 SMs when N allows it
-    int rt = 1;
-    if (N >= 16 * 4 * 296) rt = 4;
-    else if (N >= 16 * 2 * 296) rt = 2;
-    if (out_dtype == MLLM_BF16)
-        return pick_mt<__nv_bfloat16>(rt, x, ldx, W, bias, out, ldo, M, N, K, act, accumulate, stream);
-    if (out_dtype == MLLM_F32)
-        return pick_mt<float>(rt, x, ldx, W, bias, out, ldo, M, N, K, act, accumulate, stream);
-    return mllm_fail(1, "linear_smallm: unknown dtype code %d", out_dtype);
+    Call c{x, ldx, W, bias, out, ldo, M, N, K, act, accumulate, nullptr, nullptr, stream};
+    return dispatch(c, out_dtype);
+}
+
+// The same product with LayerNorm fused on the input and/or the cache write fused on the
+// output.  norm_x != null: the input is LayerNorm(norm_x[rows[m] or m]) with gamma, beta,
+// eps (32-bit rows of K floats, row stride ldx, which is then counted in floats; `x` is
+// ignored).  k_pages != null: columns >= q_size are keys then values and go to their page
+// slots (bfloat16); `out` receives the first q_size columns only.
+MLLM_EXPORT int mllm_linear_smallm_fused(const void* x, long long ldx, const void* W, const float* bias, void* out,
+                                         long long ldo, int M, int N, int K, int act, int accumulate, int out_dtype,
+                                         const float* norm_x, const int* norm_rows, const float* gamma,
+                                         const float* beta, float eps, void* k_pages, void* v_pages,
+                                         const int* slots, int q_size, int kv_heads, int head_dim, int page_size,
+                                         cudaStream_t stream) {
+    NormArgs ln{norm_x, norm_rows, gamma, beta, eps};
+    KvArgs kv{(__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, slots, q_size, kv_heads, head_dim, page_size};
+    Call c{x, ldx, W, bias, out, ldo, M, N, K, act, accumulate, norm_x ? &ln : nullptr, k_pages ? &kv : nullptr, stream};
+    return dispatch(c, out_dtype);
 }

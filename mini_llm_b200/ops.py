@@ -44,6 +44,9 @@ def _signatures(lib):
                                 c_ll, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "mllm_linear_smallm": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_void_p],
+        "mllm_linear_smallm_fused": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int,
+                                     c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_linear_tcgen05": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p],
         "mllm_tcgen05_error": [c_void_p],
@@ -193,13 +196,106 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
 
 
 # --------------------------------------------------------------------------- linear
+class NormedInput:
+    """LayerNorm(x[rows]) not yet computed: a product that can fuse the norm into its
+    loads takes it as it is, anything else calls ``materialize()``."""
+
+    def __init__(self, x, gamma, beta, eps, rows, ws, dtype):
+        self.x, self.gamma, self.beta, self.eps, self.rows, self.ws, self.dtype = x, gamma, beta, eps, rows, ws, dtype
+        self.shape = (x.shape[0] if rows is None else rows.shape[0], x.shape[1])
+        self._out = None
+
+    def materialize(self):
+        if self._out is None:
+            out = self.ws.buf("norm_out", self.shape[0], self.shape[1], self.dtype)
+            layernorm(self.x, self.gamma, self.beta, self.eps, out, rows=self.rows)
+            self._out = out
+        return self._out
+
+
+def _fusable(weight, M, K) -> bool:
+    return weight.dtype == torch.bfloat16 and M <= SMALL_M and K % 8 == 0 and weight.data_ptr() % 16 == 0
+
+
+def _norm_ok(n: NormedInput) -> bool:
+    x = n.x
+    return (x.dtype == torch.float32 and x.stride(1) == 1 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0
+            and n.gamma.data_ptr() % 16 == 0 and n.beta.data_ptr() % 16 == 0)
+
+
+def _linear_fused(x, weight, bias, out, act, accumulate, norm: Optional[NormedInput], kv) -> None:
+    """The small-M product with the norm fused on its input and/or the cache write on its output."""
+    M = norm.shape[0] if norm is not None else x.shape[0]
+    N, K = weight.shape
+    ldo = _rows("out", out)
+    if norm is not None:
+        xp, ldx = None, norm.x.stride(0)
+        nargs = (norm.x.data_ptr(), norm.rows.data_ptr() if norm.rows is not None else None,
+                 norm.gamma.data_ptr(), norm.beta.data_ptr(), float(norm.eps))
+    else:
+        xp, ldx = x.data_ptr(), _rows("x", x)
+        nargs = (None, None, None, None, 0.0)
+    if kv is not None:
+        k_pages, v_pages, slots, q_size = kv
+        _, Hkv, ps, dh = k_pages.shape
+        kargs = (k_pages.data_ptr(), v_pages.data_ptr(), slots.data_ptr(), int(q_size), Hkv, dh, ps)
+    else:
+        kargs = (None, None, None, 0, 0, 0, 0)
+    _call("mllm_linear_smallm_fused", xp, ldx, weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+          out.data_ptr(), ldo, M, N, K, _ACT[act], int(accumulate), _dt(out), *nargs, *kargs, _stream())
+
+
+def linear_qkv_cache(x, weight, bias, q_out, k_pages, v_pages, slot_mapping, ws):
+    """Q|K|V projection whose keys and values go to their page slots; returns the queries.
+
+    weight [q_size + 2*kv_heads*head_dim, K]; q_out [M, q_size] is where the queries may be
+    put.  With few rows the cache write rides in the product's epilogue (and a NormedInput's
+    norm in its loads) and q_out is returned; otherwise the product writes a [M, N] buffer,
+    kv_write copies keys and values from it, and the buffer's query columns are returned.
+    """
+    M = x.shape[0]
+    N, K = weight.shape
+    q_size = q_out.shape[1]
+    _, Hkv, ps, dh = k_pages.shape
+    if N != q_size + 2 * Hkv * dh:
+        raise KernelError(f"linear_qkv_cache: {N} output columns against {q_size} + 2*{Hkv}*{dh}")
+    _cuda("q_out", q_out, contiguous=False)
+    _cuda("k_pages", k_pages, q_out.dtype)
+    _cuda("v_pages", v_pages, q_out.dtype)
+    _cuda("slot_mapping", slot_mapping, torch.int32)
+    norm = x if isinstance(x, NormedInput) else None
+    if q_out.dtype == torch.bfloat16 and _fusable(weight, M, K) and (
+            _norm_ok(norm) if norm is not None else
+            (x.is_cuda and x.dtype == torch.bfloat16 and _rows("x", x) % 8 == 0 and x.data_ptr() % 16 == 0)):
+        if bias is not None:
+            _cuda("bias", bias, torch.float32)
+        _linear_fused(None if norm is not None else x, weight, bias, q_out, None, False, norm,
+                      (k_pages, v_pages, slot_mapping, q_size))
+        return q_out
+    qkv = ws.buf("qkv", M, N, q_out.dtype)
+    linear(x, weight, bias, out=qkv)
+    kv_write(qkv[:, q_size:q_size + Hkv * dh], qkv[:, q_size + Hkv * dh:], k_pages, v_pages, slot_mapping)
+    return qkv[:, :q_size]
+
+
 def linear(x, weight, bias, out, act: Optional[str] = None, accumulate: bool = False, impl: Optional[str] = None):
     """out = act(x @ weight^T + bias) (+ out when ``accumulate``).
 
-    x [M,K] rows contiguous (a column slice is fine), weight [N,K] contiguous, bias
-    [N] 32-bit or None, out [M,N] rows contiguous.  float32 operands run the true
-    32-bit FMA kernel; bfloat16 operands accumulate in 32-bit.
+    x [M,K] rows contiguous (a column slice is fine) or a NormedInput, weight [N,K]
+    contiguous, bias [N] 32-bit or None, out [M,N] rows contiguous.  float32 operands run
+    the true 32-bit FMA kernel; bfloat16 operands accumulate in 32-bit.
     """
+    if isinstance(x, NormedInput):
+        if impl in (None, "smallm") and _fusable(weight, x.shape[0], weight.shape[1]) and _norm_ok(x) \
+                and x.shape[1] == weight.shape[1] and tuple(out.shape) == (x.shape[0], weight.shape[0]):
+            _cuda("out", out, contiguous=False)
+            if bias is not None:
+                _cuda("bias", bias, torch.float32)
+            if act not in _ACT:
+                raise KernelError(f"linear: unknown activation {act!r}")
+            _linear_fused(None, weight, bias, out, act, accumulate, x, None)
+            return out
+        x = x.materialize()
     _cuda("x", x, contiguous=False)
     _cuda("weight", weight, x.dtype)
     _cuda("out", out, contiguous=False)

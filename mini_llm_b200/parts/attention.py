@@ -23,6 +23,8 @@ from .base import Mixer, ParamSpec, register_part
 
 
 class Attention(Mixer):
+    accepts_lazy_norm = True
+
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, scale: float,
                  num_kv_heads: Optional[int] = None, window: Optional[int] = None, bias: bool = True):
         self.hidden_size = int(hidden_size)
@@ -54,16 +56,23 @@ class Attention(Mixer):
     def forward(self, h, ctx, cache, out_accum):
         ops = self.rt.ops
         T = h.shape[0]
-        qkv = ctx.ws.buf("qkv", T, self.q_size + 2 * self.kv_size, self.rt.act_dtype)
-        ops.linear(h, self.qkv_weight, self.qkv_bias, out=qkv)
-        q = qkv[:, :self.q_size]
-        k = qkv[:, self.q_size:self.q_size + self.kv_size]
-        v = qkv[:, self.q_size + self.kv_size:]
-        if self.positions is not None:
-            self.positions.apply_qk(q, k, ctx)
         gv = ctx.groups[cache.group]
-        if cache.write:
-            ops.kv_write(k, v, cache.k_pages, cache.v_pages, gv.slot_mapping)
+        rotates = self.positions is not None and getattr(self.positions, "acts_on_qk", False)
+        if cache.write and not rotates:
+            # keys and values go to their page slots from the projection itself
+            q = ops.linear_qkv_cache(h, self.qkv_weight, self.qkv_bias,
+                                     ctx.ws.buf("q", T, self.q_size, self.rt.act_dtype), cache.k_pages,
+                                     cache.v_pages, gv.slot_mapping, ctx.ws)
+        else:
+            qkv = ctx.ws.buf("qkv", T, self.q_size + 2 * self.kv_size, self.rt.act_dtype)
+            ops.linear(h, self.qkv_weight, self.qkv_bias, out=qkv)
+            q = qkv[:, :self.q_size]
+            k = qkv[:, self.q_size:self.q_size + self.kv_size]
+            v = qkv[:, self.q_size + self.kv_size:]
+            if rotates:
+                self.positions.apply_qk(q, k, ctx)
+            if cache.write:
+                ops.kv_write(k, v, cache.k_pages, cache.v_pages, gv.slot_mapping)
         att = ctx.ws.buf("attn_out", T, self.q_size, self.rt.act_dtype)
         ops.paged_attention(q, cache.k_pages, cache.v_pages, gv.block_table, ctx, att,
                             num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,

@@ -8,7 +8,10 @@ parameters live in the ``PartSpec`` that the architecture wrote, not here.
 Interfaces (all tensors are CUDA tensors on the engine's stream):
 
 * Norm:          ``forward(x_f32[T,D], ctx, rows=None) -> h[R,D]`` in the activation dtype;
-                 ``rows`` (int32 device tensor) gathers those rows of x first.
+                 ``rows`` (int32 device tensor) gathers those rows of x first.  A norm
+                 with ``supports_lazy = True`` also takes ``lazy=True`` and then returns an
+                 ``ops.NormedInput`` for consumers with ``accepts_lazy_norm = True``,
+                 whose first product fuses the norm into its loads.
 * Mixer:         ``forward(h[T,D], ctx, cache, out_accum)``: adds its result into the
                  32-bit residual ``out_accum[T,D]``; ``cache`` is a ``LayerCache``.
                  ``cache_need() -> PagedNeed | StateNeed | None``.
@@ -77,6 +80,7 @@ class FeedForward(Part):
 class Positions(Part):
     category = "positions"
     max_positions: Optional[int] = None
+    acts_on_qk = False          # True: apply_qk changes queries/keys (a rotation) before keys are cached
 
     def embedding_table(self):
         return None

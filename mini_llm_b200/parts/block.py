@@ -8,11 +8,16 @@ from __future__ import annotations
 from .base import register_part
 
 
+def _norm(norm, consumer, x, ctx):
+    # a consumer that says so gets the norm unevaluated, to fuse it into its first product
+    if getattr(consumer, "accepts_lazy_norm", False) and getattr(norm, "supports_lazy", False):
+        return norm.forward(x, ctx, lazy=True)
+    return norm.forward(x, ctx)
+
+
 def pre_norm(layer, x, ctx, cache):
-    h = layer.mixer_norm.forward(x, ctx)
-    layer.mixer.forward(h, ctx, cache, x)
-    h = layer.ff_norm.forward(x, ctx)
-    layer.ff.forward(h, ctx, x)
+    layer.mixer.forward(_norm(layer.mixer_norm, layer.mixer, x, ctx), ctx, cache, x)
+    layer.ff.forward(_norm(layer.ff_norm, layer.ff, x, ctx), ctx, x)
     return x
 
 

@@ -13,6 +13,8 @@ from .base import Head, ParamSpec, register_part
 
 
 class TiedHead(Head):
+    accepts_lazy_norm = True
+
     def __init__(self, hidden_size: int, vocab_size: int):
         self.hidden_size = int(hidden_size)
         self.vocab_size = int(vocab_size)
@@ -28,6 +30,8 @@ class TiedHead(Head):
 
 
 class LinearHead(Head):
+    accepts_lazy_norm = True
+
     def __init__(self, hidden_size: int, vocab_size: int):
         self.hidden_size = int(hidden_size)
         self.vocab_size = int(vocab_size)

@@ -13,6 +13,8 @@ ACTIVATIONS = ("gelu_tanh", "gelu_erf")
 
 
 class MLP(FeedForward):
+    accepts_lazy_norm = True
+
     def __init__(self, hidden_size: int, inner_size: int, activation: str, bias: bool = True):
         if activation not in ACTIVATIONS:
             raise ValueError(f"MLP activation must be one of {ACTIVATIONS}, got {activation!r}")

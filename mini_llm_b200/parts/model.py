@@ -96,5 +96,8 @@ class Model:
             x = layer.arrangement(layer, x, ctx, cache)
         if ctx.R == 0:
             return None
-        y = self.final_norm.forward(x, ctx, rows=ctx.logit_rows)
+        if getattr(self.head, "accepts_lazy_norm", False) and getattr(self.final_norm, "supports_lazy", False):
+            y = self.final_norm.forward(x, ctx, rows=ctx.logit_rows, lazy=True)
+        else:
+            y = self.final_norm.forward(x, ctx, rows=ctx.logit_rows)
         return self.head.forward(y, ctx)

@@ -11,6 +11,8 @@ from .base import Norm, ParamSpec, register_part
 
 
 class LayerNorm(Norm):
+    supports_lazy = True
+
     def __init__(self, hidden_size: int, eps: float):
         self.hidden_size = int(hidden_size)
         self.eps = float(eps)
@@ -19,7 +21,11 @@ class LayerNorm(Norm):
         return {"weight": ParamSpec((self.hidden_size,), "vector"),
                 "bias": ParamSpec((self.hidden_size,), "vector")}
 
-    def forward(self, x, ctx, rows=None):
+    def forward(self, x, ctx, rows=None, lazy=False):
+        """``lazy``: the consumer is a product that can fuse the norm into its loads; it gets
+        a NormedInput instead of a tensor (and may still ask for the tensor)."""
+        if lazy:
+            return self.rt.ops.NormedInput(x, self.weight, self.bias, self.eps, rows, ctx.ws, self.rt.act_dtype)
         n = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.ws.buf("norm_out", n, self.hidden_size, self.rt.act_dtype)
         self.rt.ops.layernorm(x, self.weight, self.bias, self.eps, out, rows=rows)

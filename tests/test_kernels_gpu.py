@@ -152,6 +152,75 @@ def test_linear_tcgen05_rows_do_not_depend_on_the_batch(ops):
     ops.check_device_errors()
 
 
+@pytest.mark.parametrize("M,N,K,eps", [(1, 768, 768, 1e-5), (8, 2304, 768, 1e-5), (5, 1000, 96, 1e-6), (64, 320, 1600, 1e-5),
+                                       (33, 50257, 64, 1e-3)])
+def test_small_m_product_with_the_norm_fused_in(ops, M, N, K, eps):
+    """LayerNorm fused into the loads of the weight-streaming product, also with gathered rows,
+    against the two separate kernels."""
+    from mini_llm_b200.engine.context import Workspace
+    ws = Workspace(torch.device(DEV), 64)
+    x = rnd(M + 3, K, seed=1, scale=2.0) + 0.5
+    gamma, beta = rnd(K, seed=2) + 1.0, rnd(K, seed=3)
+    w, b = rnd(N, K, seed=4, scale=K ** -0.5, dtype=torch.bfloat16), rnd(N, seed=5)
+    for rows in (None, torch.tensor([(3 * i + 1) % (M + 3) for i in range(M)], dtype=torch.int32, device=DEV)):
+        xin = x[:M] if rows is None else x
+        normed = torch.empty(M, K, device=DEV, dtype=torch.bfloat16)
+        ops.layernorm(xin, gamma, beta, eps, normed, rows=rows)
+        for act, out_dtype in ((None, torch.float32), ("gelu_tanh", torch.bfloat16), ("gelu_erf", torch.bfloat16)):
+            want = torch.empty(M, N, device=DEV, dtype=out_dtype)
+            ops.linear(normed, w, b, out=want, act=act, impl="smallm")
+            got = torch.full((M, N), 3.0, device=DEV, dtype=out_dtype)
+            ops.linear(ops.NormedInput(xin, gamma, beta, eps, rows, ws, torch.bfloat16), w, b, out=got, act=act)
+            # the fused norm sums a row in another order: a normed value may round to the other bfloat16 neighbour
+            scale = max(1.0, want.float().abs().max().item())
+            assert (got.double() - want.double()).abs().max() < (2e-3 if out_dtype == torch.float32 else 1.6e-2) * scale
+        ref = torch.nn.functional.layer_norm(xin.double() if rows is None else xin.double()[rows.long()], (K,),
+                                             gamma.double(), beta.double(), eps) @ w.double().t() + b.double()
+        got = torch.empty(M, N, device=DEV)
+        ops.linear(ops.NormedInput(xin, gamma, beta, eps, rows, ws, torch.bfloat16), w, b, out=got)
+        assert (got.double() - ref).abs().max() < 2e-2 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("M,H,Hkv,dh,page,K", [(1, 12, 12, 64, 16, 768), (8, 4, 4, 16, 16, 64), (13, 3, 3, 32, 8, 96),
+                                               (64, 6, 2, 64, 4, 128)])
+def test_small_m_qkv_product_writes_the_cache(ops, M, H, Hkv, dh, page, K):
+    """The Q|K|V projection whose epilogue puts keys and values into their page slots, against
+    the product followed by the copy kernel."""
+    from mini_llm_b200.engine.context import Workspace
+    ws = Workspace(torch.device(DEV), 64)
+    q_size, kv = H * dh, Hkv * dh
+    N = q_size + 2 * kv
+    x = rnd(M, K, seed=1, dtype=torch.bfloat16)
+    w, b = rnd(N, K, seed=2, scale=K ** -0.5, dtype=torch.bfloat16), rnd(N, seed=3)
+    P = 40
+    g = torch.Generator().manual_seed(4)
+    slots = torch.randperm(P * page, generator=g)[:M].to(torch.int32).to(DEV)
+    qkv = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.linear(x, w, b, out=qkv, impl="smallm")
+    wk = torch.full((P, Hkv, page, dh), 9.0, device=DEV, dtype=torch.bfloat16)
+    wv = wk.clone()
+    ops.kv_write(qkv[:, q_size:q_size + kv], qkv[:, q_size + kv:], wk, wv, slots)
+    gk = torch.full((P, Hkv, page, dh), 9.0, device=DEV, dtype=torch.bfloat16)
+    gv = gk.clone()
+    q_buf = torch.empty(M, q_size, device=DEV, dtype=torch.bfloat16)
+    q = ops.linear_qkv_cache(x, w, b, q_buf, gk, gv, slots, ws)
+    assert q.data_ptr() == q_buf.data_ptr()
+    assert torch.equal(q, qkv[:, :q_size]) and torch.equal(gk, wk) and torch.equal(gv, wv)
+    # many rows: the unfused route gives the same cache
+    M2 = 100
+    x2 = rnd(M2, K, seed=5, dtype=torch.bfloat16)
+    slots2 = torch.randperm(P * page, generator=g)[:M2].to(torch.int32).to(DEV)
+    gk.fill_(9.0), gv.fill_(9.0)
+    q2 = ops.linear_qkv_cache(x2, w, b, torch.empty(M2, q_size, device=DEV, dtype=torch.bfloat16), gk, gv, slots2, ws)
+    full = torch.empty(M2, N, device=DEV, dtype=torch.bfloat16)
+    ops.linear(x2, w, b, out=full)
+    assert torch.equal(q2, full[:, :q_size])
+    for t in (0, 57, 99):
+        s_ = int(slots2[t])
+        assert torch.equal(gk[s_ // page, :, s_ % page].reshape(-1), full[t, q_size:q_size + kv])
+        assert torch.equal(gv[s_ // page, :, s_ % page].reshape(-1), full[t, q_size + kv:])
+
+
 def test_linear_small_m_rows_do_not_depend_on_the_batch(ops):
     x, w = rnd(64, 768, seed=1, dtype=torch.bfloat16), rnd(2304, 768, seed=2, scale=0.05, dtype=torch.bfloat16)
     full = torch.empty(64, 2304, device=DEV)
