@@ -1,38 +1,40 @@
 // Attention of single tokens over the paged cache, split along the keys: the decode
-// step's attention, where the time goes into reading keys and values once.
+// step's attention, where the time goes into reading keys and values once and, at small
+// batches, into the latency of the chain position -> block table -> key/value rows.
 //
-// Grid (split, head, token).  A split is a fixed range of 256 key positions counted
+// Grid (split, head, token).  A split is a fixed range of 128 key positions counted
 // from position 0, so which keys are added together never depends on the batch.
 // Inside a CTA (4 warps) a group of LPK lanes owns one key at a time: each lane loads
 // 16 bytes of the key row and of the value row (the cache layout keeps one
-// (page, head, slot) row contiguous), the group reduces the dot product with
-// shuffles and keeps its own online-softmax state (m, l, o) in 32-bit
-// (src/kernels/prefill/flashattention.cu:129-168 gives the recurrence); groups are
-// merged in group order through shared memory, and the split's (m, l, o) goes to a
-// scratch buffer.  A second kernel merges the splits of a (token, head) in split
-// order and divides by l.  The reference's decode kernel walks all keys with one
-// thread per key and one thread per output element
+// (page, head, slot) row contiguous).  A group first fetches the page ids of all its
+// keys, then issues all its key and value loads at once (up to 8 keys in flight per
+// group), and only then starts computing: three dependent memory round trips per CTA
+// instead of two per key.  The group reduces each dot product with shuffles and keeps its
+// own online-softmax state (m, l, o) in 32-bit (src/kernels/prefill/flashattention.cu:
+// 129-168 gives the recurrence); groups are merged in group order through shared memory
+// and the split's (m, l, o) goes to a scratch buffer.  The CTA that finishes last for a
+// (token, head) - found with a counter that it resets - merges the splits in split order
+// and divides by l, so one launch does it all.  The reference's decode kernel walks all
+// keys with one thread per key and one thread per output element
 // (src/kernels/decode/paged_attention.cu:60-120).
 #include "common.cuh"
 
 namespace {
 
-constexpr int SPLIT = 256;
+constexpr int SPLIT = 128;
 constexpr int THREADS = 128;
-constexpr int UNR = 4;
 
 template <typename T> struct Vec16;
 template <> struct Vec16<float> {
     static constexpr int N = 4;
-    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
-        const float4 f = *reinterpret_cast<const float4*>(p);
-        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    static __device__ __forceinline__ void unpack(const uint4& u, float (&v)[4]) {
+        v[0] = __uint_as_float(u.x); v[1] = __uint_as_float(u.y);
+        v[2] = __uint_as_float(u.z); v[3] = __uint_as_float(u.w);
     }
 };
 template <> struct Vec16<__nv_bfloat16> {
     static constexpr int N = 8;
-    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
-        const uint4 u = *reinterpret_cast<const uint4*>(p);
+    static __device__ __forceinline__ void unpack(const uint4& u, float (&v)[8]) {
         const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -44,75 +46,93 @@ template <> struct Vec16<__nv_bfloat16> {
 
 template <typename T, int LPK>
 __global__ void __launch_bounds__(THREADS)
-attn_decode_split_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
-                         const T* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
-                         const int* __restrict__ token_seq, const int* __restrict__ positions,
-                         float* __restrict__ part_o, float* __restrict__ part_ml, int H, int Hkv, int page_size,
-                         float scale, int window, int max_splits) {
+attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
+                   const T* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
+                   const int* __restrict__ token_seq, const int* __restrict__ positions, T* __restrict__ out,
+                   long long out_stride, float* __restrict__ part_o, float* __restrict__ part_ml,
+                   unsigned int* __restrict__ counters, int H, int Hkv, int page_size, float scale, int window,
+                   int max_splits) {
     constexpr int VEC = Vec16<T>::N;
     constexpr int DH = LPK * VEC;
-    constexpr int NG = THREADS / LPK;
+    constexpr int NG = THREADS / LPK;                 // key groups per CTA
+    constexpr int KPG = SPLIT / NG;                   // keys per group in a split
+    constexpr int UNR = KPG < 8 ? KPG : 8;            // keys in flight per group
     __shared__ float sm_m[NG], sm_l[NG];
     __shared__ float sm_o[NG * DH];
+    __shared__ int s_last;
     const int split = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
     const int p = positions[t];
+    const int seq = token_seq[t];
     int first = 0;
     if (window > 0 && p - window + 1 > 0) first = p - window + 1;
     const int k_lo = split * SPLIT, k_hi = min(k_lo + SPLIT, p + 1);
     if (k_lo > p || k_lo + SPLIT <= first) return;           // nothing visible in this split
+    const int s_lo = first / SPLIT, s_hi = p / SPLIT;         // splits that have work, inclusive
     const int hk = h / (H / Hkv);
-    const int* bt = block_table + (size_t)token_seq[t] * bt_stride;
+    const int* bt = block_table + (size_t)seq * bt_stride;
     const int gi = threadIdx.x / LPK, li = threadIdx.x % LPK;
 
-    float qv[VEC];
-    Vec16<T>::load(q + (size_t)t * q_stride + (size_t)h * DH + li * VEC, qv);
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) qv[i] *= scale;
+    const uint4 qraw = *reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)h * DH + li * VEC);
     float m = -INFINITY, l = 0.f, o[VEC];
 #pragma unroll
     for (int i = 0; i < VEC; ++i) o[i] = 0.f;
+    float qv[VEC];
+    Vec16<T>::unpack(qraw, qv);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) qv[i] *= scale;
 
+#pragma unroll 1
     for (int kb = k_lo + gi; kb < k_lo + SPLIT; kb += NG * UNR) {   // same trip count for every lane
-        float kv[UNR][VEC], vv[UNR][VEC], s[UNR];
+        int page[UNR];
         bool ok[UNR];
 #pragma unroll
         for (int u = 0; u < UNR; ++u) {
             const int kp = kb + u * NG;
             ok[u] = kp < k_hi && kp >= first;
-            if (ok[u]) {
-                const int page = bt[kp / page_size];
-                const size_t off = (((size_t)page * Hkv + hk) * page_size + kp % page_size) * DH + li * VEC;
-                Vec16<T>::load(k_pages + off, kv[u]);
-                Vec16<T>::load(v_pages + off, vv[u]);
-            } else {
+            page[u] = ok[u] ? bt[kp / page_size] : 0;
+        }
+        uint4 kr[UNR], vr[UNR];
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) { kv[u][i] = 0.f; vv[u][i] = 0.f; }
+        for (int u = 0; u < UNR; ++u) {
+            const int kp = kb + u * NG;
+            kr[u] = make_uint4(0, 0, 0, 0);
+            vr[u] = make_uint4(0, 0, 0, 0);
+            if (ok[u]) {
+                const size_t off = (((size_t)page[u] * Hkv + hk) * page_size + kp % page_size) * DH + li * VEC;
+                kr[u] = *reinterpret_cast<const uint4*>(k_pages + off);
+                vr[u] = *reinterpret_cast<const uint4*>(v_pages + off);
             }
         }
+        float s[UNR];
         float mx = m;
 #pragma unroll
         for (int u = 0; u < UNR; ++u) {
+            float kv[VEC];
+            Vec16<T>::unpack(kr[u], kv);
             float d = 0.f;
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) d = fmaf(qv[i], kv[u][i], d);
+            for (int i = 0; i < VEC; ++i) d = fmaf(qv[i], kv[i], d);
 #pragma unroll
             for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
             s[u] = ok[u] ? d : -INFINITY;
             mx = fmaxf(mx, s[u]);
         }
-        if (mx == -INFINITY) continue;                       // uniform within the group
-        const float alpha = expf(m - mx);
-        l *= alpha;
+        if (mx != -INFINITY) {                               // uniform within the group; no shuffles inside
+            const float alpha = expf(m - mx);
+            l *= alpha;
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] *= alpha;
+            for (int i = 0; i < VEC; ++i) o[i] *= alpha;
 #pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            const float pr = ok[u] ? expf(s[u] - mx) : 0.f;
-            l += pr;
+            for (int u = 0; u < UNR; ++u) {
+                const float pr = ok[u] ? expf(s[u] - mx) : 0.f;
+                float vv[VEC];
+                Vec16<T>::unpack(vr[u], vv);
+                l += pr;
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) o[i] = fmaf(pr, vv[u][i], o[i]);
+                for (int i = 0; i < VEC; ++i) o[i] = fmaf(pr, vv[i], o[i]);
+            }
+            m = mx;
         }
-        m = mx;
     }
     if (li == 0) { sm_m[gi] = m; sm_l[gi] = l; }
 #pragma unroll
@@ -120,63 +140,65 @@ attn_decode_split_kernel(const T* __restrict__ q, long long q_stride, const T* _
     __syncthreads();
     float M = -INFINITY;
     for (int g = 0; g < NG; ++g) M = fmaxf(M, sm_m[g]);
-    const size_t slot = ((size_t)t * H + h) * max_splits + split;
+    const size_t pair = (size_t)t * H + h;
+    const size_t slot = pair * max_splits + split;
+    const bool single = s_lo == s_hi;                        // the only split: write the result directly
+    float L = 0.f;
+    for (int g = 0; g < NG; ++g) {
+        const float w = sm_m[g] == -INFINITY ? 0.f : expf(sm_m[g] - M);
+        L = fmaf(w, sm_l[g], L);
+    }
     for (int d = threadIdx.x; d < DH; d += THREADS) {
         float acc = 0.f;
         for (int g = 0; g < NG; ++g) {
             const float w = sm_m[g] == -INFINITY ? 0.f : expf(sm_m[g] - M);
             acc = fmaf(w, sm_o[g * DH + d], acc);
         }
-        part_o[slot * DH + d] = acc;
+        if (single) out[(size_t)t * out_stride + (size_t)h * DH + d] = from_f32<T>(acc / L);
+        else part_o[slot * DH + d] = acc;
     }
+    if (single) return;
     if (threadIdx.x == 0) {
-        float L = 0.f;
-        for (int g = 0; g < NG; ++g) {
-            const float w = sm_m[g] == -INFINITY ? 0.f : expf(sm_m[g] - M);
-            L = fmaf(w, sm_l[g], L);
-        }
         part_ml[slot * 2] = M;
         part_ml[slot * 2 + 1] = L;
     }
-}
-
-template <typename T>
-__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         const int* __restrict__ positions, T* __restrict__ out, long long out_stride,
-                                         int H, int dh, int window, int max_splits) {
-    const int h = blockIdx.x, t = blockIdx.y;
-    const int p = positions[t];
-    int first = 0;
-    if (window > 0 && p - window + 1 > 0) first = p - window + 1;
-    const int s_lo = first / SPLIT, s_hi = p / SPLIT;           // inclusive
-    const size_t base = ((size_t)t * H + h) * max_splits;
-    float M = -INFINITY;
-    for (int s = s_lo; s <= s_hi; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-    float L = 0.f;
-    for (int s = s_lo; s <= s_hi; ++s) L = fmaf(expf(part_ml[(base + s) * 2] - M), part_ml[(base + s) * 2 + 1], L);
-    const float inv = 1.f / L;
-    for (int d = threadIdx.x; d < dh; d += blockDim.x) {
+    // the CTA that arrives last merges the splits of this (token, head)
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int n = (unsigned int)(s_hi - s_lo + 1);
+        const unsigned int old = atomicAdd(&counters[pair], 1u);
+        s_last = (old == n - 1);
+        if (s_last) counters[pair] = 0;                      // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const size_t base = pair * max_splits;
+    float MM = -INFINITY;
+    for (int s = s_lo; s <= s_hi; ++s) MM = fmaxf(MM, __ldcg(&part_ml[(base + s) * 2]));
+    float LL = 0.f;
+    for (int s = s_lo; s <= s_hi; ++s)
+        LL = fmaf(expf(__ldcg(&part_ml[(base + s) * 2]) - MM), __ldcg(&part_ml[(base + s) * 2 + 1]), LL);
+    const float inv = 1.f / LL;
+    for (int d = threadIdx.x; d < DH; d += THREADS) {
         float acc = 0.f;
         for (int s = s_lo; s <= s_hi; ++s)
-            acc = fmaf(expf(part_ml[(base + s) * 2] - M), part_o[(base + s) * dh + d], acc);
-        out[(size_t)t * out_stride + (size_t)h * dh + d] = from_f32<T>(acc * inv);
+            acc = fmaf(expf(__ldcg(&part_ml[(base + s) * 2]) - MM), __ldcg(&part_o[(base + s) * DH + d]), acc);
+        out[(size_t)t * out_stride + (size_t)h * DH + d] = from_f32<T>(acc * inv);
     }
 }
 
 template <typename T, int LPK>
 int launch(const void* q, long long q_stride, const void* k_pages, const void* v_pages, const int* block_table,
            int bt_stride, const int* token_seq, const int* positions, void* out, long long out_stride,
-           float* part_o, float* part_ml, int T_tokens, int H, int Hkv, int page_size, float scale, int window,
-           int max_splits, cudaStream_t stream) {
+           float* part_o, float* part_ml, unsigned int* counters, int T_tokens, int H, int Hkv, int page_size,
+           float scale, int window, int max_splits, cudaStream_t stream) {
     dim3 grid(max_splits, H, T_tokens);
-    attn_decode_split_kernel<T, LPK><<<grid, THREADS, 0, stream>>>(
+    attn_decode_kernel<T, LPK><<<grid, THREADS, 0, stream>>>(
         (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table, bt_stride, token_seq, positions,
-        part_o, part_ml, H, Hkv, page_size, scale, window, max_splits);
-    MLLM_CHECK_LAUNCH("attention_decode(split)");
-    constexpr int DH = LPK * Vec16<T>::N;
-    attn_decode_merge_kernel<T><<<dim3(H, T_tokens), DH < 32 ? 32 : (DH > 128 ? 128 : DH), 0, stream>>>(
-        part_o, part_ml, positions, (T*)out, out_stride, H, DH, window, max_splits);
-    MLLM_CHECK_LAUNCH("attention_decode(merge)");
+        (T*)out, out_stride, part_o, part_ml, counters, H, Hkv, page_size, scale, window, max_splits);
+    MLLM_CHECK_LAUNCH("attention_decode");
     return 0;
 }
 
@@ -184,20 +206,23 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
 
 MLLM_EXPORT int mllm_attention_decode_split_len() { return SPLIT; }
 
-// Scratch: part_o [T*H*max_splits*dh] and part_ml [T*H*max_splits*2] floats, where
-// max_splits >= ceil((largest position + 1) / 256).  Returns 1 with a message for head
-// sizes this kernel does not take (the caller then uses the general kernel).
+// Scratch: part_o [T*H*max_splits*dh] and part_ml [T*H*max_splits*2] floats and counters
+// [T*H] 32-bit words that must be zero before the first call (the kernel leaves them
+// zero), where max_splits >= ceil((largest position + 1) / 128).  Fails for head sizes
+// this kernel does not take (the caller then uses the general kernel).
 MLLM_EXPORT int mllm_attention_decode(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                       const int* block_table, int bt_stride, const int* token_seq,
                                       const int* positions, void* out, long long out_stride, float* part_o,
-                                      float* part_ml, int T, int H, int Hkv, int dh, int page_size, float scale,
-                                      int window, int max_splits, int dtype, cudaStream_t stream) {
+                                      float* part_ml, unsigned int* counters, int T, int H, int Hkv, int dh,
+                                      int page_size, float scale, int window, int max_splits, int dtype,
+                                      cudaStream_t stream) {
     if (T <= 0) return 0;
     if (Hkv <= 0 || H % Hkv != 0) return mllm_fail(1, "attention_decode: %d heads over %d key/value heads", H, Hkv);
     if (max_splits <= 0 || T > 65535 || H > 65535) return mllm_fail(1, "attention_decode: grid out of range");
 #define GO(TT, LPK)                                                                                            \
     return launch<TT, LPK>(q, q_stride, k_pages, v_pages, block_table, bt_stride, token_seq, positions, out,    \
-                           out_stride, part_o, part_ml, T, H, Hkv, page_size, scale, window, max_splits, stream)
+                           out_stride, part_o, part_ml, counters, T, H, Hkv, page_size, scale, window,          \
+                           max_splits, stream)
     if (dtype == MLLM_BF16) {
         using bf = __nv_bfloat16;
         if (q_stride % 8 || (uintptr_t)q % 16) return mllm_fail(1, "attention_decode: queries must be 16-byte aligned");

@@ -74,21 +74,77 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * (16 * RT);
     const int nchunks = (K + 31) / 32;
-    constexpr int U = LN ? 1 : (RT == 1 ? 4 : (RT == 2 ? 2 : 1));
+    constexpr int U = RT == 1 ? 4 : (RT == 2 ? 2 : 1);
+    constexpr int ROWS = 16 * RT, COLS = 8 * MT;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+
+    // The weight loads of the first round go out before anything else: they come from HBM and
+    // nothing they need depends on the norm statistics or on the epilogue's operands.
+    uint4 wa[U][RT], wb[U][RT];
+    auto load_w = [&](int c0) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k = (c0 + u * WARPS) * 32 + 8 * t;
+            const bool kok = k < K;                 // K is a multiple of 8: a lane's 8 values are in or out together
+#pragma unroll
+            for (int r = 0; r < RT; ++r) {
+                const int ra = n0 + r * 16 + g, rb = ra + 8;
+                wa[u][r] = (kok && ra < N) ? ldg16(W + (size_t)ra * K + k) : zero;
+                wb[u][r] = (kok && rb < N) ? ldg16(W + (size_t)rb * K + k) : zero;
+            }
+        }
+    };
+    load_w(warp);
+
+    // The epilogue's operands of this thread's first output element, fetched early as well.
+    const int e_row = threadIdx.x % ROWS, e_col = threadIdx.x / ROWS;
+    const int e_n = n0 + e_row;
+    const bool e_ok = threadIdx.x < ROWS * COLS && e_n < N && e_col < M;
+    float e_bias = 0.f, e_old = 0.f;
+    int e_slot = 0;
+    if (e_ok) {
+        if (bias) e_bias = bias[e_n];
+        if (KVW && e_n >= kv.q_size) e_slot = kv.slots[e_col];
+        else if (accumulate) e_old = to_f32(out[(size_t)e_col * ldo + e_n]);
+    }
+
     if constexpr (LN) {
+        // mean and 1/std of every row: one pass over the row in registers when it is short enough
+        constexpr int KEEP = 8;                      // float4 per lane kept: rows up to 1024 wide
         for (int m = warp; m < M; m += WARPS) {
             const float* xr = ln.x + (size_t)(ln.rows ? ln.rows[m] : m) * ldx;
+            float4 keep[KEEP];
+            const bool fits = K <= KEEP * 128;
             float s = 0.f;
-            for (int k = lane * 4; k < K; k += 128) {
-                const float4 v = *reinterpret_cast<const float4*>(xr + k);
-                s += (v.x + v.y) + (v.z + v.w);
+            if (fits) {
+#pragma unroll
+                for (int i = 0; i < KEEP; ++i) {
+                    const int k = lane * 4 + i * 128;
+                    keep[i] = k < K ? *reinterpret_cast<const float4*>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    s += (keep[i].x + keep[i].y) + (keep[i].z + keep[i].w);
+                }
+            } else {
+                for (int k = lane * 4; k < K; k += 128) {
+                    const float4 v = *reinterpret_cast<const float4*>(xr + k);
+                    s += (v.x + v.y) + (v.z + v.w);
+                }
             }
             const float mean = warp_sum(s) / (float)K;
             float q = 0.f;
-            for (int k = lane * 4; k < K; k += 128) {
-                const float4 v = *reinterpret_cast<const float4*>(xr + k);
-                const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
-                q += (a * a + b * b) + (c * c + d * d);
+            if (fits) {
+#pragma unroll
+                for (int i = 0; i < KEEP; ++i) {
+                    if (lane * 4 + i * 128 < K) {
+                        const float a = keep[i].x - mean, b = keep[i].y - mean, c = keep[i].z - mean, d = keep[i].w - mean;
+                        q += (a * a + b * b) + (c * c + d * d);
+                    }
+                }
+            } else {
+                for (int k = lane * 4; k < K; k += 128) {
+                    const float4 v = *reinterpret_cast<const float4*>(xr + k);
+                    const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+                    q += (a * a + b * b) + (c * c + d * d);
+                }
             }
             const float var = warp_sum(q) / (float)K;
             if (lane == 0) { s_mean[m] = mean; s_rstd[m] = rsqrtf(var + ln.eps); }
@@ -104,25 +160,18 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[r][m][i] = 0.f;
 
-    const uint4 zero = make_uint4(0, 0, 0, 0);
     for (int c0 = warp; c0 < nchunks; c0 += WARPS * U) {
-        uint4 wa[U][RT], wb[U][RT], xv[U][MT];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int k = (c0 + u * WARPS) * 32 + 8 * t;
-            const bool kok = k < K;                 // K is a multiple of 8: a lane's 8 values are in or out together
-#pragma unroll
-            for (int r = 0; r < RT; ++r) {
-                const int ra = n0 + r * 16 + g, rb = ra + 8;
-                wa[u][r] = (kok && ra < N) ? ldg16(W + (size_t)ra * K + k) : zero;
-                wb[u][r] = (kok && rb < N) ? ldg16(W + (size_t)rb * K + k) : zero;
-            }
+            const bool kok = k < K;
+            uint4 xv[MT];
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 const int row = m * 8 + g;
-                if constexpr (LN) {
-                    xv[u][m] = zero;
-                    if (kok && row < M) {
+                xv[m] = zero;
+                if (kok && row < M) {
+                    if constexpr (LN) {
                         const float* xr = ln.x + (size_t)(ln.rows ? ln.rows[row] : row) * ldx + k;
                         const float4 a = *reinterpret_cast<const float4*>(xr), b = *reinterpret_cast<const float4*>(xr + 4);
                         const float4 ga = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
@@ -130,28 +179,26 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
                         const float4 ba = __ldg(reinterpret_cast<const float4*>(ln.beta + k));
                         const float4 bb = __ldg(reinterpret_cast<const float4*>(ln.beta + k + 4));
                         const float mu = s_mean[row], rs = s_rstd[row];
-                        xv[u][m].x = pack2((a.x - mu) * rs * ga.x + ba.x, (a.y - mu) * rs * ga.y + ba.y);
-                        xv[u][m].y = pack2((a.z - mu) * rs * ga.z + ba.z, (a.w - mu) * rs * ga.w + ba.w);
-                        xv[u][m].z = pack2((b.x - mu) * rs * gb.x + bb.x, (b.y - mu) * rs * gb.y + bb.y);
-                        xv[u][m].w = pack2((b.z - mu) * rs * gb.z + bb.z, (b.w - mu) * rs * gb.w + bb.w);
+                        xv[m].x = pack2((a.x - mu) * rs * ga.x + ba.x, (a.y - mu) * rs * ga.y + ba.y);
+                        xv[m].y = pack2((a.z - mu) * rs * ga.z + ba.z, (a.w - mu) * rs * ga.w + ba.w);
+                        xv[m].z = pack2((b.x - mu) * rs * gb.x + bb.x, (b.y - mu) * rs * gb.y + bb.y);
+                        xv[m].w = pack2((b.z - mu) * rs * gb.z + bb.z, (b.w - mu) * rs * gb.w + bb.w);
+                    } else {
+                        xv[m] = ldg16_cached(x + (size_t)row * ldx + k);
                     }
-                } else {
-                    xv[u][m] = (kok && row < M) ? ldg16_cached(x + (size_t)row * ldx + k) : zero;
                 }
             }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u)
 #pragma unroll
             for (int r = 0; r < RT; ++r)
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
-                    mma_bf16(acc[r][m], wa[u][r].x, wb[u][r].x, wa[u][r].y, wb[u][r].y, xv[u][m].x, xv[u][m].y);
-                    mma_bf16(acc[r][m], wa[u][r].z, wb[u][r].z, wa[u][r].w, wb[u][r].w, xv[u][m].z, xv[u][m].w);
+                    mma_bf16(acc[r][m], wa[u][r].x, wb[u][r].x, wa[u][r].y, wb[u][r].y, xv[m].x, xv[m].y);
+                    mma_bf16(acc[r][m], wa[u][r].z, wb[u][r].z, wa[u][r].w, wb[u][r].w, xv[m].z, xv[m].w);
                 }
+        }
+        if (c0 + WARPS * U < nchunks) load_w(c0 + WARPS * U);
     }
     // partial sums of this warp -> shared memory
-    constexpr int ROWS = 16 * RT, COLS = 8 * MT;
     float* mine = red + (size_t)warp * ROWS * COLS;
 #pragma unroll
     for (int r = 0; r < RT; ++r)
@@ -169,14 +216,15 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
         const int row = i % ROWS, col = i / ROWS;
         const int n = n0 + row;
         if (n >= N || col >= M) continue;
+        const bool first = i == threadIdx.x;           // operands already in registers
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) v += red[(size_t)w * ROWS * COLS + row * COLS + col];
-        if (bias) v += bias[n];
+        if (bias) v += first ? e_bias : bias[n];
         v = apply_act(v, act);
         if constexpr (KVW) {
             if (n >= kv.q_size) {
-                const int slot = kv.slots[col];
+                const int slot = first ? e_slot : kv.slots[col];
                 if (slot < 0) continue;
                 const int c = n - kv.q_size, kvs = kv.kv_heads * kv.head_dim;
                 const int which = c / kvs, cc = c % kvs;
@@ -188,7 +236,7 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
             }
         }
         TO* o = out + (size_t)col * ldo + n;
-        if (accumulate) v += to_f32(*o);
+        if (accumulate) v += first ? e_old : to_f32(*o);
         *o = from_f32<TO>(v);
     }
 }

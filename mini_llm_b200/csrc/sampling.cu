@@ -41,6 +41,59 @@ argmax_kernel(const float* __restrict__ logits, long long ld, int V, int* __rest
     if (threadIdx.x == 0) out[blockIdx.x] = bi[0] == 0x7fffffff ? 0 : bi[0];
 }
 
+// argmax of long rows with few rows in the batch: every row is cut into slices, one CTA
+// each; the CTA that finishes a row last (a counter it resets) reduces the slices' results.
+__global__ void __launch_bounds__(256)
+argmax_sliced_kernel(const float* __restrict__ logits, long long ld, int V, int* __restrict__ out,
+                     float* __restrict__ part_val, int* __restrict__ part_idx, unsigned int* __restrict__ counters) {
+    __shared__ float bv[256];
+    __shared__ int bi[256];
+    __shared__ int s_last;
+    const int r = blockIdx.y, slices = gridDim.x, sl = blockIdx.x;
+    const int per = (V + slices - 1) / slices;
+    const int lo = min(V, sl * per), hi = min(V, lo + per);
+    const float* row = logits + (size_t)r * ld;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    }
+    bv[threadIdx.x] = best;
+    bi[threadIdx.x] = idx;
+    __syncthreads();
+    for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float ov = bv[threadIdx.x + s];
+            const int oi = bi[threadIdx.x + s];
+            if (ov > bv[threadIdx.x] || (ov == bv[threadIdx.x] && oi < bi[threadIdx.x])) {
+                bv[threadIdx.x] = ov;
+                bi[threadIdx.x] = oi;
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        part_val[(size_t)r * slices + sl] = bv[0];
+        part_idx[(size_t)r * slices + sl] = bi[0];
+        __threadfence();
+        const unsigned int old = atomicAdd(&counters[r], 1u);
+        s_last = old == (unsigned int)slices - 1;
+        if (s_last) counters[r] = 0;
+    }
+    __syncthreads();
+    if (!s_last || threadIdx.x != 0) return;
+    __threadfence();
+    float b = -INFINITY;
+    int bidx = 0x7fffffff;
+    for (int s = 0; s < slices; ++s) {
+        const float v = __ldcg(&part_val[(size_t)r * slices + s]);
+        const int i = __ldcg(&part_idx[(size_t)r * slices + s]);
+        if (v > b || (v == b && i < bidx)) { b = v; bidx = i; }
+    }
+    out[r] = bidx == 0x7fffffff ? 0 : bidx;
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
               const float* __restrict__ uniform, int* __restrict__ out) {
@@ -107,6 +160,16 @@ MLLM_EXPORT int mllm_argmax(const float* logits, long long ld, int R, int V, int
     if (V <= 0) return mllm_fail(1, "argmax: vocabulary %d", V);
     argmax_kernel<<<R, 256, 0, stream>>>(logits, ld, V, out);
     MLLM_CHECK_LAUNCH("argmax");
+    return 0;
+}
+
+// Scratch: part_val/part_idx [R * slices], counters [R] zero before the first call (left zero).
+MLLM_EXPORT int mllm_argmax_sliced(const float* logits, long long ld, int R, int V, int* out, float* part_val,
+                                   int* part_idx, unsigned int* counters, int slices, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (V <= 0 || slices <= 0 || R > 65535) return mllm_fail(1, "argmax: vocabulary %d, %d slices, %d rows", V, slices, R);
+    argmax_sliced_kernel<<<dim3(slices, R), 256, 0, stream>>>(logits, ld, V, out, part_val, part_idx, counters);
+    MLLM_CHECK_LAUNCH("argmax_sliced");
     return 0;
 }
 

@@ -86,6 +86,17 @@ class Workspace:
             self.version += 1
         return t[:rows]
 
+    def zeroed(self, name: str, n: int) -> torch.Tensor:
+        """``n`` int32 words that are zero when first handed out; kernels that use them as
+        counters leave them zero."""
+        key = (name, 0, torch.int32)
+        t = self._bufs.get(key)
+        if t is None or t.numel() < n:
+            t = torch.zeros(max(n, 4096), dtype=torch.int32, device=self.device)
+            self._bufs[key] = t
+            self.version += 1
+        return t[:n]
+
     def logits(self, rows: int, vocab: int) -> torch.Tensor:
         t = self._logits
         if t is None or t.shape[0] < rows or t.shape[1] != vocab:

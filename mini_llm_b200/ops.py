@@ -17,7 +17,7 @@ from .csrc import build as _build
 
 F32, BF16 = 0, 1
 SMALL_M = 64                 # rows up to which the weight-streaming product is used
-DECODE_SPLIT = 256           # keys per split of the decode attention (csrc/attention_decode.cu)
+DECODE_SPLIT = 128           # keys per split of the decode attention (csrc/attention_decode.cu)
 _FLASH_HEAD_DIMS = (16, 32, 64, 128)
 _DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16, 32, 64, 128)}
 _ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}
@@ -51,11 +51,12 @@ def _signatures(lib):
                                 c_int, c_void_p],
         "mllm_tcgen05_error": [c_void_p],
         "mllm_attention_decode": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                  c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                  c_int, c_void_p],
+                                  c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                  c_int, c_int, c_int, c_void_p],
         "mllm_attention_flash": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                  c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mllm_argmax": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
+        "mllm_argmax_sliced": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mllm_sample": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     }
     for name, args in sig.items():
@@ -217,9 +218,12 @@ def _fusable(weight, M, K) -> bool:
     return weight.dtype == torch.bfloat16 and M <= SMALL_M and K % 8 == 0 and weight.data_ptr() % 16 == 0
 
 
+NORM_FUSE_M = 16             # rows up to which the norm is recomputed inside every CTA of the product
+
+
 def _norm_ok(n: NormedInput) -> bool:
     x = n.x
-    return (x.dtype == torch.float32 and x.stride(1) == 1 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0
+    return (n.shape[0] <= NORM_FUSE_M and x.dtype == torch.float32 and x.stride(1) == 1 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0
             and n.gamma.data_ptr() % 16 == 0 and n.beta.data_ptr() % 16 == 0)
 
 
@@ -264,6 +268,8 @@ def linear_qkv_cache(x, weight, bias, q_out, k_pages, v_pages, slot_mapping, ws)
     _cuda("v_pages", v_pages, q_out.dtype)
     _cuda("slot_mapping", slot_mapping, torch.int32)
     norm = x if isinstance(x, NormedInput) else None
+    if norm is not None and not _norm_ok(norm):
+        x, norm = norm.materialize(), None
     if q_out.dtype == torch.bfloat16 and _fusable(weight, M, K) and (
             _norm_ok(norm) if norm is not None else
             (x.is_cuda and x.dtype == torch.bfloat16 and _rows("x", x) % 8 == 0 and x.data_ptr() % 16 == 0)):
@@ -395,9 +401,10 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
         max_splits = max(1, -(-int(ctx.max_ctx_len) // DECODE_SPLIT))
         part_o = ctx.ws.buf("attn_part_o", T * num_heads * max_splits, head_dim, torch.float32)
         part_ml = ctx.ws.buf("attn_part_ml", T * num_heads * max_splits, 2, torch.float32)
+        counters = ctx.ws.zeroed("attn_counters", T * num_heads)     # the kernel leaves them zero
         _call("mllm_attention_decode", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(),
               block_table.data_ptr(), bt_stride, ctx.token_seq.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(),
-              ldo, part_o.data_ptr(), part_ml.data_ptr(), T, num_heads, num_kv_heads, head_dim, ps, float(scale),
+              ldo, part_o.data_ptr(), part_ml.data_ptr(), counters.data_ptr(), T, num_heads, num_kv_heads, head_dim, ps, float(scale),
               int(window or 0), max_splits, _dt(q), _stream())
         return
     if impl != "simt":
@@ -408,12 +415,32 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
 
 
 # --------------------------------------------------------------------------- sampling
+_argmax_scratch = {}
+
+
 def argmax(logits, out) -> None:
+    """out[r] = index of the largest value of row r, the lowest index among equals."""
     _cuda("logits", logits, torch.float32, contiguous=False)
     _cuda("out", out, torch.int32)
     ld = _rows("logits", logits)
     R, V = logits.shape
-    _call("mllm_argmax", logits.data_ptr(), ld, R, V, out.data_ptr(), _stream())
+    if out.numel() != R:
+        raise KernelError("argmax: one output per row")
+    slices = 1
+    if R * 4 < 592 and V >= 8192:            # few long rows: cut them so that the SMs have work
+        slices = min(64, max(2, 592 // max(R, 1)), V // 1024)
+    if slices == 1:
+        _call("mllm_argmax", logits.data_ptr(), ld, R, V, out.data_ptr(), _stream())
+        return
+    dev = logits.device
+    sc = _argmax_scratch.get(dev)
+    if sc is None or sc[0].numel() < R * slices or sc[2].numel() < R:
+        n = max(R * slices, 4096)
+        sc = (torch.empty(n, dtype=torch.float32, device=dev), torch.empty(n, dtype=torch.int32, device=dev),
+              torch.zeros(max(R, 1024), dtype=torch.int32, device=dev))
+        _argmax_scratch[dev] = sc
+    _call("mllm_argmax_sliced", logits.data_ptr(), ld, R, V, out.data_ptr(), sc[0].data_ptr(), sc[1].data_ptr(),
+          sc[2].data_ptr(), slices, _stream())
 
 
 def sample(logits, temperature, uniform, out) -> None:

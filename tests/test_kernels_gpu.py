@@ -152,8 +152,8 @@ def test_linear_tcgen05_rows_do_not_depend_on_the_batch(ops):
     ops.check_device_errors()
 
 
-@pytest.mark.parametrize("M,N,K,eps", [(1, 768, 768, 1e-5), (8, 2304, 768, 1e-5), (5, 1000, 96, 1e-6), (64, 320, 1600, 1e-5),
-                                       (33, 50257, 64, 1e-3)])
+@pytest.mark.parametrize("M,N,K,eps", [(1, 768, 768, 1e-5), (8, 2304, 768, 1e-5), (5, 1000, 96, 1e-6), (16, 320, 1600, 1e-5),
+                                       (13, 50257, 64, 1e-3), (40, 200, 1024, 1e-5)])
 def test_small_m_product_with_the_norm_fused_in(ops, M, N, K, eps):
     """LayerNorm fused into the loads of the weight-streaming product, also with gathered rows,
     against the two separate kernels."""
@@ -302,8 +302,8 @@ def _ctx_for(case):
 @pytest.mark.parametrize("H,Hkv,dh,page,window", [(4, 4, 16, 16, None), (3, 3, 32, 8, None), (12, 12, 64, 16, None),
                                                   (6, 2, 64, 4, None), (2, 2, 128, 32, 300), (4, 1, 64, 16, 37)])
 def test_decode_attention_split_keys(ops, dtype, H, Hkv, dh, page, window):
-    """Single tokens at contexts around the split (256) and page edges, beside the plain kernel."""
-    seqs = [(c, 1) for c in (1, 2, 16, 17, 255, 256, 257, 511, 512, 513, 700, 1024)]
+    """Single tokens at contexts around the split (128) and page edges, beside the plain kernel."""
+    seqs = [(c, 1) for c in (1, 2, 16, 17, 127, 128, 129, 255, 256, 257, 513, 700, 1024)]
     case = _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages=4096 // page + 24, seed=dh + page)
     ctx = _ctx_for(case)
     q = case["q"].to(dtype).to(DEV)
@@ -319,7 +319,7 @@ def test_decode_attention_split_keys(ops, dtype, H, Hkv, dh, page, window):
     assert (out.double() - plain.double()).abs().max() < tol
     # a token's result does not depend on the tokens beside it
     one = _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages=4096 // page + 24, seed=dh + page)
-    for t in (0, 5, 11):
+    for t in (0, 5, 12):
         c1 = _Ctx()
         c1.token_seq, c1.positions = ctx.token_seq[t:t + 1].clone(), ctx.positions[t:t + 1].clone()
         c1.ws, c1.max_ctx_len, c1.decode_only = ctx.ws, int(ctx.positions[t]) + 1, True
@@ -460,7 +460,7 @@ def test_kv_write(ops, dtype):
     assert torch.equal(kp, wk) and torch.equal(vp, wv)
 
 
-@pytest.mark.parametrize("R,V", [(1, 17), (5, 1000), (64, 50257), (3, 1025)])
+@pytest.mark.parametrize("R,V", [(1, 17), (5, 1000), (64, 50257), (3, 1025), (8, 50257), (1, 151936), (2, 8192)])
 def test_argmax_and_sampling(ops, R, V):
     logits = rnd(R, V, seed=R + V, scale=3.0)
     logits[0, 3] = logits[0, min(9, V - 1)] = logits[0].max() + 1          # equal maxima: the lowest id wins
