@@ -247,3 +247,72 @@ MLLM_EXPORT int mllm_attention_decode(const void* q, long long q_stride, const v
 #undef GO
     return mllm_fail(1, "attention_decode: head size %d is not one of this kernel's", dh);
 }
+
+// ---------------------------------------------------------------------------------------
+// The same attention for callers that cannot allocate device memory (declared in
+// attention_decode_noalloc.h, which says who they are).  Its scratch - the per-split partial
+// results and the per-(token, head) arrival counters - lives in this file-scope device array
+// instead of in buffers that the caller provides.  Every GPU that loads the library carries
+// the array until the process exits.
+#include "attention_decode_noalloc.h"
+
+namespace {
+
+constexpr size_t NA_PART_O = (size_t)MLLM_NOALLOC_MAX_SLOTS * MLLM_NOALLOC_MAX_HEAD_DIM * sizeof(float);
+constexpr size_t NA_PART_ML = (size_t)MLLM_NOALLOC_MAX_SLOTS * 2 * sizeof(float);
+constexpr size_t NA_COUNTERS = (size_t)MLLM_NOALLOC_MAX_SLOTS * sizeof(unsigned int);
+constexpr size_t NA_TOTAL = NA_PART_O + NA_PART_ML + NA_COUNTERS;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NA_TOTAL];
+
+constexpr int NA_MAX_DEVICES = 64;
+unsigned char* g_noalloc_ptr[NA_MAX_DEVICES] = {};       // device address of the array, per device
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a
+// kernel could use: the device address has to be asked for, once per device, with that
+// device current.
+int noalloc_scratch(unsigned char** out) {
+    int dev = -1;
+    MLLM_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= NA_MAX_DEVICES) return mllm_fail(1, "attention_decode_noalloc: device index %d", dev);
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p)
+            return mllm_fail(3, "attention_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    *out = g_noalloc_ptr[dev];
+    return 0;
+}
+
+}  // namespace
+
+MLLM_EXPORT int mllm_attention_decode_noalloc(const void* q, long long q_stride, const void* k_pages,
+                                              const void* v_pages, const int* block_table, int bt_stride,
+                                              const int* token_seq, const int* positions, void* out,
+                                              long long out_stride, int T, int H, int Hkv, int dh, int page_size,
+                                              float scale, int window, int max_splits, int dtype,
+                                              cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || max_splits <= 0) return mllm_fail(1, "attention_decode_noalloc: %d heads, %d splits", H, max_splits);
+    const long long slots = (long long)T * H * max_splits;
+    if (slots > MLLM_NOALLOC_MAX_SLOTS)
+        return mllm_fail(1, "attention_decode_noalloc: tokens x heads x splits = %d x %d x %d = %lld exceeds the "
+                            "built-in scratch of %d; use mllm_attention_decode with your own buffers",
+                         T, H, max_splits, slots, MLLM_NOALLOC_MAX_SLOTS);
+    if (dh > MLLM_NOALLOC_MAX_HEAD_DIM)
+        return mllm_fail(1, "attention_decode_noalloc: head size %d exceeds %d", dh, MLLM_NOALLOC_MAX_HEAD_DIM);
+    unsigned char* base = nullptr;
+    const int rc = noalloc_scratch(&base);
+    if (rc) return rc;
+    float* part_o = reinterpret_cast<float*>(base);
+    float* part_ml = reinterpret_cast<float*>(base + NA_PART_O);
+    unsigned int* counters = reinterpret_cast<unsigned int*>(base + NA_PART_O + NA_PART_ML);
+    // The array keeps what the last call left.  The partial results are fully rewritten before
+    // they are read; the counters must start at zero, so they are cleared on this stream.
+    MLLM_CUDA(cudaMemsetAsync(counters, 0, (size_t)T * H * sizeof(unsigned int), stream));
+    return mllm_attention_decode(q, q_stride, k_pages, v_pages, block_table, bt_stride, token_seq, positions, out,
+                                 out_stride, part_o, part_ml, counters, T, H, Hkv, dh, page_size, scale, window,
+                                 max_splits, dtype, stream);
+}
