@@ -87,6 +87,9 @@ class ModelRunner:
         self._graph_version = -1
         self.graph_replays = 0
         self.graph_kernels: Dict[tuple, int] = {}
+        # a part that reads device data on the host while it runs sets graph_safe = False
+        self._graph_ok = all(getattr(self.model.part(label), "graph_safe", True)
+                             for label, _ in self.spec.all_part_specs())
 
     # ------------------------------------------------------------------ set-up
     def _make_cache(self) -> None:
@@ -230,7 +233,7 @@ class ModelRunner:
         depends on) is captured once as a CUDA graph and replayed; a shape seen for the
         first time runs eagerly.  All graphs are dropped when a scratch buffer is replaced
         by a larger one, since a graph fixes buffer addresses."""
-        if not self.engine.use_cuda_graphs:
+        if not (self.engine.use_cuda_graphs and self._graph_ok):
             with ops.stream_scope():
                 return self.model.forward(ctx)
         if self._graph_version != self.ws.version:

@@ -1,0 +1,177 @@
+"""A toy architecture defined here, in the test: a mixer with a state of its own (a running
+mean of its inputs, kept per request in a state slot) beside an attention layer that borrows
+nothing from GPT-2's description.  It is registered, its random weights are written and
+loaded, and it is stepped whole, in portions and mixed with other requests through the same
+ModelRunner as GPT-2, without any change to the package's files."""
+import json
+import os
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _register():
+    import mini_llm_b200 as m
+    from mini_llm_b200.cache.manager import StateNeed
+    from mini_llm_b200.config.base import ModelConfig
+    from mini_llm_b200.parts.base import Mixer, ParamSpec
+    from mini_llm_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, WeightRef
+
+    class RunningMean(Mixer):
+        """out[t] = W . mean(h[0..t]) of the request; the state is (sum of h, count)."""
+        graph_safe = False                      # reads the batch's slot ids on the host
+
+        def __init__(self, hidden_size):
+            self.hidden_size = hidden_size
+
+        def param_specs(self):
+            return {"w": ParamSpec((self.hidden_size, self.hidden_size), "matrix")}
+
+        def cache_need(self):
+            return StateNeed((self.hidden_size + 1,), "float32")
+
+        def forward(self, h, ctx, cache, out_accum):
+            D = self.hidden_size
+            slots = ctx.state_slots.tolist()
+            base = 0
+            for s, n in enumerate(ctx.q_lens):
+                st = cache.state[slots[s]]
+                x = h[base:base + n].float()
+                csum = torch.cumsum(x, 0) + st[:D]
+                cnt = st[D] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+                mean = csum / cnt[:, None]
+                out_accum[base:base + n] += mean @ self.w.float().t()
+                if cache.write:
+                    st[:D] = csum[-1]
+                    st[D] = cnt[-1]
+                base += n
+
+    @dataclass
+    class ToyConfig(ModelConfig):
+        hidden: int = 0
+        vocab: int = 0
+        heads: int = 0
+        inner: int = 0
+        eps: float = 1e-5
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(hidden=d["hidden"], vocab=d["vocab"], heads=d["heads"], inner=d["inner"], eps=d["eps"])
+
+        def to_dict(self):
+            return dict(architectures=["ToyStateLM"], hidden=self.hidden, vocab=self.vocab, heads=self.heads,
+                        inner=self.inner, eps=self.eps)
+
+    def build(cfg):
+        D = cfg.hidden
+
+        def norm(name):
+            return PartSpec("layernorm", dict(hidden_size=D, eps=cfg.eps),
+                            {"weight": WeightRef((name + ".g",), init=("ones",)), "bias": WeightRef((name + ".b",), init=("zeros",))})
+
+        def ff(i):
+            return PartSpec("mlp", dict(hidden_size=D, inner_size=cfg.inner, activation="gelu_erf", bias=False),
+                            {"fc_weight": WeightRef((f"l{i}.up",), init=("normal", 0.2)),
+                             "proj_weight": WeightRef((f"l{i}.down",), init=("normal", 0.2))})
+
+        l0 = LayerSpec(mixer=PartSpec("toy_running_mean", dict(hidden_size=D), {"w": WeightRef(("l0.mix",), init=("normal", 0.3))}),
+                       ff=ff(0), mixer_norm=norm("l0.n1"), ff_norm=norm("l0.n2"))
+        l1 = LayerSpec(mixer=PartSpec("attention", dict(hidden_size=D, num_heads=cfg.heads, head_dim=D // cfg.heads,
+                                                        scale=(D // cfg.heads) ** -0.5, bias=False),
+                                      {"qkv_weight": WeightRef(("l1.qkv",), init=("normal", 0.3)),
+                                       "out_weight": WeightRef(("l1.o",), init=("normal", 0.3))}),
+                       ff=ff(1), mixer_norm=norm("l1.n1"), ff_norm=norm("l1.n2"))
+        # the order of layers is data: state mixer, attention, the state mixer's layer again
+        # (second run borrows layer 1's ... no: it names layer 0 twice; the second run must not write)
+        return ModelSpec(hidden_size=D, vocab_size=cfg.vocab,
+                         embedding=PartSpec("token", dict(hidden_size=D, vocab_size=cfg.vocab),
+                                            {"table": WeightRef(("emb",), init=("normal", 1.0))}),
+                         positions=PartSpec("none", {}), layers=[l0, l1], final_norm=norm("nf"),
+                         head=PartSpec("tied", dict(hidden_size=D, vocab_size=cfg.vocab)),
+                         schedule=[ScheduleEntry(0), ScheduleEntry(1)], max_positions=None)
+
+    m.register_part("mixer", "toy_running_mean", RunningMean, replace=True)
+    m.register_architecture("ToyStateLM", ToyConfig, build, replace=True)
+    return dict(architectures=["ToyStateLM"], hidden=48, vocab=97, heads=3, inner=80, eps=1e-5)
+
+
+def _reference(folder, ids):
+    """Whole-sequence float64 statement of the toy model."""
+    from safetensors.torch import load_file
+    w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    cfg = json.load(open(os.path.join(folder, "config.json")))
+    D, H = cfg["hidden"], cfg["heads"]
+    dh = D // H
+
+    def ln(x, n):
+        return torch.nn.functional.layer_norm(x, (D,), w[n + ".g"], w[n + ".b"], cfg["eps"])
+
+    x = w["emb"][torch.tensor(ids)]
+    T = len(ids)
+    h = ln(x, "l0.n1")
+    mean = torch.cumsum(h, 0) / torch.arange(1, T + 1, dtype=torch.float64)[:, None]
+    x = x + mean @ w["l0.mix"].t()
+    x = x + torch.nn.functional.gelu(ln(x, "l0.n2") @ w["l0.up"].t()) @ w["l0.down"].t()
+    qkv = ln(x, "l1.n1") @ w["l1.qkv"].t()
+    att = torch.zeros(T, D, dtype=torch.float64)
+    mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
+    for hh in range(H):
+        q, k, v = (qkv[:, i * D + hh * dh:i * D + (hh + 1) * dh] for i in range(3))
+        s = (q @ k.t()) * dh ** -0.5
+        att[:, hh * dh:(hh + 1) * dh] = torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ v
+    x = x + att @ w["l1.o"].t()
+    x = x + torch.nn.functional.gelu(ln(x, "l1.n2") @ w["l1.up"].t()) @ w["l1.down"].t()
+    return ln(x, "nf") @ w["emb"].t()
+
+
+def test_toy_architecture_with_a_state_mixer(tmp_path):
+    import mini_llm_b200 as m
+    from mini_llm_b200.config.base import EngineConfig
+    from mini_llm_b200.engine.runner import ModelRunner, StepEntry
+
+    cfg = _register()
+    folder = m.write_random_model(cfg, 3, str(tmp_path / "toy"))
+    runner = ModelRunner(folder, EngineConfig(dtype="float32", page_size=8, num_pages=40, max_num_seqs=3))
+    assert runner.cache.state_layers and list(runner.cache.state_layers) == [0]
+    assert runner.cache.group_of_layer == {1: 0}
+    g = torch.Generator().manual_seed(0)
+    reqs = {r: torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for r, n in (("a", 37), ("b", 9), ("c", 64))}
+    want = {r: _reference(folder, ids) for r, ids in reqs.items()}
+    # whole
+    for r, ids in reqs.items():
+        runner.add_request(r)
+        got = runner.step([StepEntry(r, ids, list(range(len(ids))))])
+        assert (got.double().cpu() - want[r]).abs().max() < 2e-4 * want[r].abs().max(), r
+        runner.finish_request(r)
+    # in portions, mixed with the others, slots reused: the state carries over from step to step
+    plan = {"a": [5, 2, 13, 1, 1, 15], "b": [2, 7], "c": [30, 1, 1, 32]}
+    pos = {r: 0 for r in reqs}
+    got = {r: [] for r in reqs}
+    for r in ("a", "b"):
+        runner.add_request(r)
+    live = ["a", "b"]
+    while live:
+        entries = []
+        for r in list(live):
+            n = plan[r].pop(0)
+            entries.append(StepEntry(r, reqs[r][pos[r]:pos[r] + n], list(range(n))))
+            pos[r] += n
+        out = runner.step(entries)
+        k = 0
+        for e in entries:
+            got[e.req].append(out[k:k + len(e.tokens)].double().cpu())
+            k += len(e.tokens)
+        for r in list(live):
+            if not plan[r]:
+                runner.finish_request(r)
+                live.remove(r)
+                if r == "b":                 # c takes b's slot: its state must start from zero
+                    runner.add_request("c")
+                    live.append("c")
+    for r in reqs:
+        assert (torch.cat(got[r]) - want[r]).abs().max() < 2e-4 * want[r].abs().max(), r
+    runner.cache.check()
+    assert runner.cache.num_live == 0
