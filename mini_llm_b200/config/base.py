@@ -51,6 +51,7 @@ class EngineConfig:
     admission: str = "lazy"            # "lazy" | "reserve"
     memory_fraction: float = 0.5       # of free device memory, when sizes are not given
     use_cuda_graphs: bool = True
+    use_pdl: bool = True               # programmatic dependent launch between the kernels of a step
     device: str = "cuda:0"
 
     def __post_init__(self):

@@ -17,11 +17,21 @@
 // and divides by l, so one launch does it all.  The reference's decode kernel walks all
 // keys with one thread per key and one thread per output element
 // (src/kernels/decode/paged_attention.cu:60-120).
+//
+// When a request's splits fit a thread-block cluster (up to 8, i.e. contexts up to 1024),
+// the splits of a (token, head) are launched as one cluster and meet in distributed shared
+// memory: every CTA leaves its (m, l, o) in its own shared memory, the first CTA with work
+// reads them over the SM-to-SM network in split order and writes the result; no scratch in
+// global memory, no fence, no counter.  Longer contexts use the scratch path.
 #include "common.cuh"
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 namespace {
 
 constexpr int SPLIT = 128;
+constexpr int MAX_CLUSTER = 8;
 constexpr int THREADS = 128;
 
 template <typename T> struct Vec16;
@@ -44,7 +54,7 @@ template <> struct Vec16<__nv_bfloat16> {
     }
 };
 
-template <typename T, int LPK>
+template <typename T, int LPK, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
                    const T* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
@@ -59,15 +69,27 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
     constexpr int UNR = KPG < 8 ? KPG : 8;            // keys in flight per group
     __shared__ float sm_m[NG], sm_l[NG];
     __shared__ float sm_o[NG * DH];
+    __shared__ float sm_res[DH + 2];                          // this split's (o, m, l) for the cluster merge
     __shared__ int s_last;
     const int split = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
+    pdl_wait();
+    pdl_launch();
     const int p = positions[t];
     const int seq = token_seq[t];
     int first = 0;
     if (window > 0 && p - window + 1 > 0) first = p - window + 1;
     const int k_lo = split * SPLIT, k_hi = min(k_lo + SPLIT, p + 1);
-    if (k_lo > p || k_lo + SPLIT <= first) return;           // nothing visible in this split
     const int s_lo = first / SPLIT, s_hi = p / SPLIT;         // splits that have work, inclusive
+    if (k_lo > p || k_lo + SPLIT <= first) {                  // nothing visible in this split
+        if constexpr (CLUSTER) {
+            if (s_lo != s_hi) {                               // the others still meet at the cluster's barriers
+                cg::cluster_group cluster = cg::this_cluster();
+                cluster.sync();
+                cluster.sync();
+            }
+        }
+        return;
+    }
     const int hk = h / (H / Hkv);
     const int* bt = block_table + (size_t)seq * bt_stride;
     const int gi = threadIdx.x / LPK, li = threadIdx.x % LPK;
@@ -155,9 +177,37 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
             acc = fmaf(w, sm_o[g * DH + d], acc);
         }
         if (single) out[(size_t)t * out_stride + (size_t)h * DH + d] = from_f32<T>(acc / L);
+        else if (CLUSTER) sm_res[d] = acc;
         else part_o[slot * DH + d] = acc;
     }
+    if (CLUSTER && !single && threadIdx.x == 0) { sm_res[DH] = M; sm_res[DH + 1] = L; }
     if (single) return;
+    if constexpr (CLUSTER) {
+        // (o, m, l) of this split stay in shared memory; the cluster's first CTA collects them
+        // (the loop above wrote o to part_o only on the scratch path: redo it into sm_res)
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();                                       // every split's result is in place
+        if (split == s_lo) {                                  // the first split with work collects (rank == split)
+            float MM = -INFINITY;
+            for (int s = s_lo; s <= s_hi; ++s) MM = fmaxf(MM, cluster.map_shared_rank(sm_res, s)[DH]);
+            float LL = 0.f;
+            for (int s = s_lo; s <= s_hi; ++s) {
+                const float* r = cluster.map_shared_rank(sm_res, s);
+                LL = fmaf(expf(r[DH] - MM), r[DH + 1], LL);
+            }
+            const float inv = 1.f / LL;
+            for (int d = threadIdx.x; d < DH; d += THREADS) {
+                float acc = 0.f;
+                for (int s = s_lo; s <= s_hi; ++s) {
+                    const float* r = cluster.map_shared_rank(sm_res, s);
+                    acc = fmaf(expf(r[DH] - MM), r[d], acc);
+                }
+                out[(size_t)t * out_stride + (size_t)h * DH + d] = from_f32<T>(acc * inv);
+            }
+        }
+        cluster.sync();                                       // nobody leaves while its memory may be read
+        return;
+    }
     if (threadIdx.x == 0) {
         part_ml[slot * 2] = M;
         part_ml[slot * 2 + 1] = L;
@@ -193,12 +243,32 @@ template <typename T, int LPK>
 int launch(const void* q, long long q_stride, const void* k_pages, const void* v_pages, const int* block_table,
            int bt_stride, const int* token_seq, const int* positions, void* out, long long out_stride,
            float* part_o, float* part_ml, unsigned int* counters, int T_tokens, int H, int Hkv, int page_size,
-           float scale, int window, int max_splits, cudaStream_t stream) {
+           float scale, int window, int max_splits, bool scratch_path, cudaStream_t stream) {
     dim3 grid(max_splits, H, T_tokens);
-    attn_decode_kernel<T, LPK><<<grid, THREADS, 0, stream>>>(
-        (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table, bt_stride, token_seq, positions,
-        (T*)out, out_stride, part_o, part_ml, counters, H, Hkv, page_size, scale, window, max_splits);
-    MLLM_CHECK_LAUNCH("attention_decode");
+    if (!scratch_path && max_splits <= MAX_CLUSTER) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(THREADS);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = max_splits;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g_mllm_pdl ? 2 : 1;
+        MLLM_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel<T, LPK, true>, (const T*)q, q_stride, (const T*)k_pages,
+                                     (const T*)v_pages, block_table, bt_stride, token_seq, positions, (T*)out,
+                                     out_stride, part_o, part_ml, counters, H, Hkv, page_size, scale, window,
+                                     max_splits));
+        return 0;
+    }
+    MLLM_CUDA(mllm_launch(attn_decode_kernel<T, LPK, false>, grid, dim3(THREADS), 0, stream, true, (const T*)q,
+                          q_stride, (const T*)k_pages, (const T*)v_pages, block_table, bt_stride, token_seq, positions,
+                          (T*)out, out_stride, part_o, part_ml, counters, H, Hkv, page_size, scale, window,
+                          max_splits));
     return 0;
 }
 
@@ -206,23 +276,18 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
 
 MLLM_EXPORT int mllm_attention_decode_split_len() { return SPLIT; }
 
-// Scratch: part_o [T*H*max_splits*dh] and part_ml [T*H*max_splits*2] floats and counters
-// [T*H] 32-bit words that must be zero before the first call (the kernel leaves them
-// zero), where max_splits >= ceil((largest position + 1) / 128).  Fails for head sizes
-// this kernel does not take (the caller then uses the general kernel).
-MLLM_EXPORT int mllm_attention_decode(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
-                                      const int* block_table, int bt_stride, const int* token_seq,
-                                      const int* positions, void* out, long long out_stride, float* part_o,
-                                      float* part_ml, unsigned int* counters, int T, int H, int Hkv, int dh,
-                                      int page_size, float scale, int window, int max_splits, int dtype,
-                                      cudaStream_t stream) {
+static int attention_decode_impl(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                 const int* block_table, int bt_stride, const int* token_seq, const int* positions,
+                                 void* out, long long out_stride, float* part_o, float* part_ml,
+                                 unsigned int* counters, int T, int H, int Hkv, int dh, int page_size, float scale,
+                                 int window, int max_splits, int dtype, bool scratch_path, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (Hkv <= 0 || H % Hkv != 0) return mllm_fail(1, "attention_decode: %d heads over %d key/value heads", H, Hkv);
     if (max_splits <= 0 || T > 65535 || H > 65535) return mllm_fail(1, "attention_decode: grid out of range");
 #define GO(TT, LPK)                                                                                            \
     return launch<TT, LPK>(q, q_stride, k_pages, v_pages, block_table, bt_stride, token_seq, positions, out,    \
                            out_stride, part_o, part_ml, counters, T, H, Hkv, page_size, scale, window,          \
-                           max_splits, stream)
+                           max_splits, scratch_path, stream)
     if (dtype == MLLM_BF16) {
         using bf = __nv_bfloat16;
         if (q_stride % 8 || (uintptr_t)q % 16) return mllm_fail(1, "attention_decode: queries must be 16-byte aligned");
@@ -246,6 +311,23 @@ MLLM_EXPORT int mllm_attention_decode(const void* q, long long q_stride, const v
     }
 #undef GO
     return mllm_fail(1, "attention_decode: head size %d is not one of this kernel's", dh);
+}
+
+// Scratch (used when max_splits > 8 or scratch_only != 0): part_o [T*H*max_splits*dh] and
+// part_ml [T*H*max_splits*2] floats and counters [T*H] 32-bit words that must be zero before
+// the first call (the kernel leaves them zero), where max_splits >= ceil((largest position
+// + 1) / 128).  With up to 8 splits the splits meet in a thread-block cluster instead and the
+// scratch is not touched.  Fails for head sizes this kernel does not take (the caller then
+// uses the general kernel).
+MLLM_EXPORT int mllm_attention_decode(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                      const int* block_table, int bt_stride, const int* token_seq,
+                                      const int* positions, void* out, long long out_stride, float* part_o,
+                                      float* part_ml, unsigned int* counters, int T, int H, int Hkv, int dh,
+                                      int page_size, float scale, int window, int max_splits, int dtype,
+                                      int scratch_only, cudaStream_t stream) {
+    return attention_decode_impl(q, q_stride, k_pages, v_pages, block_table, bt_stride, token_seq, positions, out,
+                                 out_stride, part_o, part_ml, counters, T, H, Hkv, dh, page_size, scale, window,
+                                 max_splits, dtype, scratch_only != 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -312,7 +394,7 @@ MLLM_EXPORT int mllm_attention_decode_noalloc(const void* q, long long q_stride,
     // The array keeps what the last call left.  The partial results are fully rewritten before
     // they are read; the counters must start at zero, so they are cleared on this stream.
     MLLM_CUDA(cudaMemsetAsync(counters, 0, (size_t)T * H * sizeof(unsigned int), stream));
-    return mllm_attention_decode(q, q_stride, k_pages, v_pages, block_table, bt_stride, token_seq, positions, out,
+    return attention_decode_impl(q, q_stride, k_pages, v_pages, block_table, bt_stride, token_seq, positions, out,
                                  out_stride, part_o, part_ml, counters, T, H, Hkv, dh, page_size, scale, window,
-                                 max_splits, dtype, stream);
+                                 max_splits, dtype, /*scratch_path=*/true, stream);
 }

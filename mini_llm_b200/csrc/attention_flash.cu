@@ -62,6 +62,8 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     __nv_bfloat16* sV = sK + 2 * BKV * ROW;           // [2][BKV][ROW]
 
     const int tile = blockIdx.x, h = blockIdx.y;
+    pdl_wait();
+    pdl_launch();
     const int seq = tiles[tile * 3], tok0 = tiles[tile * 3 + 1], rows = tiles[tile * 3 + 2];
     const int pos0 = positions[tok0];
     const int pos_max = pos0 + rows - 1;
@@ -237,10 +239,9 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
         set = true;
     }
     using bf = __nv_bfloat16;
-    kern<<<dim3(n_tiles, H), WARPS * 32, smem, stream>>>((const bf*)q, q_stride, (const bf*)k_pages, (const bf*)v_pages,
-                                                         block_table, bt_stride, tiles, positions, (bf*)out, out_stride,
-                                                         H, Hkv, page_size, scale, window);
-    MLLM_CHECK_LAUNCH("attention_flash");
+    MLLM_CUDA(mllm_launch(kern, dim3(n_tiles, H), dim3(WARPS * 32), smem, stream, true, (const bf*)q, q_stride,
+                          (const bf*)k_pages, (const bf*)v_pages, block_table, bt_stride, tiles, positions, (bf*)out,
+                          out_stride, H, Hkv, page_size, scale, window));
     return 0;
 }
 

@@ -29,6 +29,7 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
                       long long out_stride, int T_tokens, int H, int Hkv, int dh, int page_size, float scale,
                       int window) {
     __shared__ float qs[WARPS][MAX_DH];
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long gw = (long long)blockIdx.x * WARPS + warp;
     if (gw >= (long long)T_tokens * H) return;

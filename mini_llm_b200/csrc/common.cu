@@ -15,3 +15,11 @@ int mllm_fail(int code, const char* fmt, ...) {
 MLLM_EXPORT const char* mllm_last_error() { return g_err; }
 
 MLLM_EXPORT int mllm_abi_version() { return 1; }
+
+int g_mllm_pdl = 0;
+
+// Programmatic dependent launch on (1) or off (0) for the kernels that support it.
+MLLM_EXPORT int mllm_set_pdl(int on) {
+    g_mllm_pdl = on ? 1 : 0;
+    return 0;
+}

@@ -30,6 +30,33 @@ int mllm_fail(int code, const char* fmt, ...);
             return mllm_fail(3, "%s failed: %s", #call, cudaGetErrorString(e__)); \
     } while (0)
 
+// Programmatic dependent launch: a kernel launched with the attribute may start while the
+// kernel before it on the stream is still running.  pdl_wait() returns once that kernel has
+// completed and its writes are visible; until then only data that no kernel of the step
+// writes (weights) may be touched.  pdl_launch() lets the kernel after this one start its
+// own prologue.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 1: launches that allow it carry the programmatic-serialization attribute (mllm_set_pdl).
+extern int g_mllm_pdl;
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t mllm_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (pdl && g_mllm_pdl) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 

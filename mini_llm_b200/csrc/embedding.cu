@@ -9,6 +9,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
                              const T* __restrict__ table, const T* __restrict__ pos_table,
                              float* __restrict__ out, int D) {
     const int t = blockIdx.x;
+    pdl_launch();               // the first kernel of a step: nothing before it to wait for
     const T* row = table + (size_t)ids[t] * D;
     const T* prow = pos_table ? pos_table + (size_t)pos[t] * D : nullptr;
     float* o = out + (size_t)t * D;

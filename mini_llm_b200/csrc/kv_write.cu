@@ -11,6 +11,8 @@ __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v
                                 T* __restrict__ k_pages, T* __restrict__ v_pages,
                                 const int* __restrict__ slots, int Hkv, int dh, int page_size) {
     const int t = blockIdx.x;
+    pdl_wait();
+    pdl_launch();
     const int slot = slots[t];
     if (slot < 0) return;
     const int page = slot / page_size, off = slot % page_size;

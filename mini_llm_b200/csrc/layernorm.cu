@@ -10,6 +10,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
                                  const float* __restrict__ gamma, const float* __restrict__ beta,
                                  TOut* __restrict__ out, int D, float eps) {
     __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
     TOut* o = out + (size_t)r * D;
@@ -33,9 +35,11 @@ MLLM_EXPORT int mllm_layernorm(const float* x, const int* rows, const float* gam
     if (D <= 0) return mllm_fail(1, "layernorm: width %d", D);
     int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : ((D + 31) / 32) * 32);
     if (out_dtype == MLLM_F32)
-        layernorm_kernel<float><<<R, threads, 0, stream>>>(x, rows, gamma, beta, (float*)out, D, eps);
+        MLLM_CUDA(mllm_launch(layernorm_kernel<float>, dim3(R), dim3(threads), 0, stream, true, x, rows, gamma, beta,
+                              (float*)out, D, eps));
     else if (out_dtype == MLLM_BF16)
-        layernorm_kernel<__nv_bfloat16><<<R, threads, 0, stream>>>(x, rows, gamma, beta, (__nv_bfloat16*)out, D, eps);
+        MLLM_CUDA(mllm_launch(layernorm_kernel<__nv_bfloat16>, dim3(R), dim3(threads), 0, stream, true, x, rows, gamma,
+                              beta, (__nv_bfloat16*)out, D, eps));
     else
         return mllm_fail(1, "layernorm: unknown dtype code %d", out_dtype);
     MLLM_CHECK_LAUNCH("layernorm");

@@ -50,6 +50,7 @@ linear_simt_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict
                    TO* out, long long ldo, int M, int N, int K, int act, int accumulate, int vecA, int vecW) {
     __shared__ float As[BK][BM + PAD];
     __shared__ float Ws[BK][BN + PAD];
+    pdl_wait();
     const int tid = threadIdx.x;
     const int tx = tid % (BN / TN), ty = tid / (BN / TN);
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;

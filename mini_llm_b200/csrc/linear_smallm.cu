@@ -80,8 +80,8 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
 
     // The weight loads of the first round go out before anything else: they come from HBM and
     // nothing they need depends on the norm statistics or on the epilogue's operands.
-    uint4 wa[U][RT], wb[U][RT];
-    auto load_w = [&](int c0) {
+    uint4 wa[U][RT], wb[U][RT], wa_next[U][RT], wb_next[U][RT];
+    auto load_w = [&](int c0, uint4 (&da)[U][RT], uint4 (&db)[U][RT]) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int k = (c0 + u * WARPS) * 32 + 8 * t;
@@ -89,12 +89,14 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
 #pragma unroll
             for (int r = 0; r < RT; ++r) {
                 const int ra = n0 + r * 16 + g, rb = ra + 8;
-                wa[u][r] = (kok && ra < N) ? ldg16(W + (size_t)ra * K + k) : zero;
-                wb[u][r] = (kok && rb < N) ? ldg16(W + (size_t)rb * K + k) : zero;
+                da[u][r] = (kok && ra < N) ? ldg16(W + (size_t)ra * K + k) : zero;
+                db[u][r] = (kok && rb < N) ? ldg16(W + (size_t)rb * K + k) : zero;
             }
         }
     };
-    load_w(warp);
+    load_w(warp, wa, wb);
+    pdl_wait();                 // everything below reads what earlier kernels of the step wrote
+    pdl_launch();
 
     // The epilogue's operands of this thread's first output element, fetched early as well.
     const int e_row = threadIdx.x % ROWS, e_col = threadIdx.x / ROWS;
@@ -161,6 +163,8 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
             for (int i = 0; i < 4; ++i) acc[r][m][i] = 0.f;
 
     for (int c0 = warp; c0 < nchunks; c0 += WARPS * U) {
+        const bool more = c0 + WARPS * U < nchunks;
+        if (more) load_w(c0 + WARPS * U, wa_next, wb_next);     // the next round's weights fly while this one is used
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int k = (c0 + u * WARPS) * 32 + 8 * t;
@@ -196,7 +200,12 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
                     mma_bf16(acc[r][m], wa[u][r].z, wb[u][r].z, wa[u][r].w, wb[u][r].w, xv[m].z, xv[m].w);
                 }
         }
-        if (c0 + WARPS * U < nchunks) load_w(c0 + WARPS * U);
+        if (more) {
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int r = 0; r < RT; ++r) { wa[u][r] = wa_next[u][r]; wb[u][r] = wb_next[u][r]; }
+        }
     }
     // partial sums of this warp -> shared memory
     float* mine = red + (size_t)warp * ROWS * COLS;
@@ -261,10 +270,9 @@ int launch_k(const Call& c) {
         }
     }
     const int grid = (c.N + 16 * RT - 1) / (16 * RT);
-    kern<<<grid, WARPS * 32, smem, c.stream>>>((const __nv_bfloat16*)c.x, c.ldx, (const __nv_bfloat16*)c.W, c.bias,
-                                               (TO*)c.out, c.ldo, c.M, c.N, c.K, c.act, c.accumulate,
-                                               c.ln ? *c.ln : NormArgs{}, c.kv ? *c.kv : KvArgs{});
-    MLLM_CHECK_LAUNCH("linear_smallm");
+    MLLM_CUDA(mllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, c.stream, true, (const __nv_bfloat16*)c.x, c.ldx,
+                          (const __nv_bfloat16*)c.W, c.bias, (TO*)c.out, c.ldo, c.M, c.N, c.K, c.act, c.accumulate,
+                          c.ln ? *c.ln : NormArgs{}, c.kv ? *c.kv : KvArgs{}));
     return 0;
 }
 

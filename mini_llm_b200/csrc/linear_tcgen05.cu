@@ -154,6 +154,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                 // barriers, tensor memory and descriptors are ready; now the operands may be read
+    pdl_launch();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -361,8 +363,8 @@ int launch(const void* A, long long lda, const void* W, const float* bias, void*
     // 4 consecutive outputs per store: 16 bytes (32-bit) or 8 bytes (bfloat16); column offsets are multiples of 4
     const int vec_ok = ((uintptr_t)out % (4 * sizeof(TO)) == 0) && (ldo % 4 == 0);
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    kern<<<grid, THREADS, C::SMEM, stream>>>(ma, mw, bias, (TO*)out, ldo, M, N, K, act, accumulate, vec_ok);
-    MLLM_CHECK_LAUNCH("linear_tcgen05");
+    MLLM_CUDA(mllm_launch(kern, grid, dim3(THREADS), C::SMEM, stream, true, ma, mw, bias, (TO*)out, ldo, M, N, K, act,
+                          accumulate, vec_ok));
     return 0;
 }
 

@@ -17,6 +17,7 @@ __global__ void __launch_bounds__(256)
 argmax_kernel(const float* __restrict__ logits, long long ld, int V, int* __restrict__ out) {
     __shared__ float bv[256];
     __shared__ int bi[256];
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * ld;
     float best = -INFINITY;
     int idx = 0x7fffffff;
@@ -49,6 +50,7 @@ argmax_sliced_kernel(const float* __restrict__ logits, long long ld, int V, int*
     __shared__ float bv[256];
     __shared__ int bi[256];
     __shared__ int s_last;
+    pdl_wait();
     const int r = blockIdx.y, slices = gridDim.x, sl = blockIdx.x;
     const int per = (V + slices - 1) / slices;
     const int lo = min(V, sl * per), hi = min(V, lo + per);
@@ -101,6 +103,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
     __shared__ float sums[SAMPLE_THREADS];
     __shared__ int s_idx;
     __shared__ int s_best;
+    pdl_wait();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * ld;
     const float temp = temperature[r];
@@ -158,8 +161,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
 MLLM_EXPORT int mllm_argmax(const float* logits, long long ld, int R, int V, int* out, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0) return mllm_fail(1, "argmax: vocabulary %d", V);
-    argmax_kernel<<<R, 256, 0, stream>>>(logits, ld, V, out);
-    MLLM_CHECK_LAUNCH("argmax");
+    MLLM_CUDA(mllm_launch(argmax_kernel, dim3(R), dim3(256), 0, stream, true, logits, ld, V, out));
     return 0;
 }
 
@@ -168,8 +170,8 @@ MLLM_EXPORT int mllm_argmax_sliced(const float* logits, long long ld, int R, int
                                    int* part_idx, unsigned int* counters, int slices, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0 || slices <= 0 || R > 65535) return mllm_fail(1, "argmax: vocabulary %d, %d slices, %d rows", V, slices, R);
-    argmax_sliced_kernel<<<dim3(slices, R), 256, 0, stream>>>(logits, ld, V, out, part_val, part_idx, counters);
-    MLLM_CHECK_LAUNCH("argmax_sliced");
+    MLLM_CUDA(mllm_launch(argmax_sliced_kernel, dim3(slices, R), dim3(256), 0, stream, true, logits, ld, V, out,
+                          part_val, part_idx, counters));
     return 0;
 }
 
@@ -177,7 +179,7 @@ MLLM_EXPORT int mllm_sample(const float* logits, long long ld, int R, int V, con
                             const float* uniform, int* out, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0) return mllm_fail(1, "sample: vocabulary %d", V);
-    sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, uniform, out);
-    MLLM_CHECK_LAUNCH("sample");
+    MLLM_CUDA(mllm_launch(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, true, logits, ld, V, temperature,
+                          uniform, out));
     return 0;
 }

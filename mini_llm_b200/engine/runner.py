@@ -64,6 +64,7 @@ class ModelRunner:
         self.device = torch.device(self.engine.device)
         torch.cuda.set_device(self.device)
         ops.library()       # build/load now: fail early and loudly
+        ops.set_pdl(self.engine.use_pdl)
         self.config: ModelConfig = load_config(model_dir)
         arch = get_architecture(self.config.architecture)
         self.spec = arch.build_spec(self.config)

@@ -33,6 +33,8 @@ class KernelError(RuntimeError):
 def _signatures(lib):
     lib.mllm_last_error.restype = ctypes.c_char_p
     lib.mllm_abi_version.restype = c_int
+    lib.mllm_set_pdl.argtypes = [c_int]
+    lib.mllm_set_pdl.restype = c_int
     sig = {
         "mllm_embed": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "mllm_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
@@ -52,7 +54,7 @@ def _signatures(lib):
         "mllm_tcgen05_error": [c_void_p],
         "mllm_attention_decode": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                  c_int, c_int, c_int, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_void_p],
         "mllm_attention_flash": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                  c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mllm_argmax": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
@@ -77,6 +79,12 @@ def library():
         _signatures(lib)
         _lib = lib
     return _lib
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for the kernels that support it: the next kernel's
+    blocks may start (and prefetch weights) while the current kernel drains."""
+    library().mllm_set_pdl(int(bool(on)))
 
 
 def is_loaded() -> bool:
@@ -393,7 +401,7 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
               ctx.positions.data_ptr(), out.data_ptr(), ldo, num_heads, num_kv_heads, head_dim, ps, float(scale),
               int(window or 0), _stream())
         return
-    if impl == "decode":
+    if impl in ("decode", "decode_scratch"):        # "decode_scratch": splits meet in global scratch, not in a cluster
         if head_dim not in _DECODE_HEAD_DIMS[q.dtype]:
             raise KernelError(f"paged_attention: the split-key kernel takes head sizes {_DECODE_HEAD_DIMS[q.dtype]} "
                               f"for {q.dtype}, not {head_dim}")
@@ -405,7 +413,7 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
         _call("mllm_attention_decode", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(),
               block_table.data_ptr(), bt_stride, ctx.token_seq.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(),
               ldo, part_o.data_ptr(), part_ml.data_ptr(), counters.data_ptr(), T, num_heads, num_kv_heads, head_dim, ps, float(scale),
-              int(window or 0), max_splits, _dt(q), _stream())
+              int(window or 0), max_splits, _dt(q), int(impl == "decode_scratch"), _stream())
         return
     if impl != "simt":
         raise KernelError(f"paged_attention: unknown implementation {impl!r}")

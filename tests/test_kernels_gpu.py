@@ -317,6 +317,10 @@ def test_decode_attention_split_keys(ops, dtype, H, Hkv, dh, page, window):
     tol = 2e-5 if dtype == torch.float32 else 1e-2
     assert (out.double().cpu() - want).abs().max() < tol
     assert (out.double() - plain.double()).abs().max() < tol
+    # the same splits merged through global scratch (the route of contexts beyond a cluster) give the same bits
+    via_scratch = torch.empty_like(q)
+    ops.paged_attention(q, kp, vp, bt, ctx, via_scratch, impl="decode_scratch", **kw)
+    assert torch.equal(via_scratch, out)
     # a token's result does not depend on the tokens beside it
     one = _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages=4096 // page + 24, seed=dh + page)
     for t in (0, 5, 12):
