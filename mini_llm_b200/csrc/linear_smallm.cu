@@ -230,7 +230,7 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) v += red[(size_t)w * ROWS * COLS + row * COLS + col];
         if (bias) v += first ? e_bias : bias[n];
-        v = apply_act(v, act);
+        v = (act == MLLM_ACT_GELU_TANH && sizeof(TO) == 2) ? gelu_tanh_fast(v) : apply_act(v, act);
         if constexpr (KVW) {
             if (n >= kv.q_size) {
                 const int slot = first ? e_slot : kv.slots[col];

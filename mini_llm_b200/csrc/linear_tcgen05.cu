@@ -1,17 +1,18 @@
 // out = act(A[M,K] . W[N,K]^T + bias) (+ out) on the fifth-generation tensor cores:
 // the product of prefill steps (many rows), bfloat16 operands, 32-bit accumulation.
 //
-// One CTA computes one 128 x BN tile of the result.  Warp 0 (one elected lane) is the
+// CTAs are persistent (one per SM) and walk over 128 x BN tiles of the result; BN is one of
+// 64, 96, 128, 192, 256, chosen per shape.  Warp 0 (one elected lane) is the
 // producer: it moves 128 x 64 tiles of A and BN x 64 tiles of W from global memory to a
 // ring of shared-memory stages with TMA (cp.async.bulk.tensor, 128-byte swizzle; rows
 // and columns beyond the matrices are filled with zeros by the copy engine, so any M, N
 // and any K that is a multiple of 8 work).  Warp 1 (one lane) issues tcgen05.mma
 // (cta_group::1, kind::f16, M=128, N=BN, K=16, four per stage) with the accumulator in
-// tensor memory, and frees a stage with tcgen05.commit.  Warps 2..5 are the epilogue:
-// each reads its 32 lanes of the accumulator with tcgen05.ld into the (by then free)
-// stage memory, then walks its rows with a lane per 4 columns, so that the bias stays in
-// registers, the activation or the 32-bit residual sum is applied, and every store
-// instruction writes one contiguous piece of a row.
+// tensor memory, and frees a stage with tcgen05.commit.  There are two accumulators, so
+// the MMAs of the next tile run while warps 2..5, the epilogue, drain the last one: each
+// warp reads its 32 lanes with tcgen05.ld, 32 columns at a time, passes them through a
+// small shared-memory staging area so that a store instruction covers 4 rows x 32
+// consecutive columns, and applies bias, activation or the 32-bit residual sum on the way.
 //
 // The sum over K of one output element runs in the same order whatever M is (K tiles in
 // sequence, no split over K), so a row's result does not depend on the batch.
@@ -42,6 +43,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait; false when the limit was hit.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
@@ -85,7 +89,9 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Starts the load of 32 columns; the registers are valid after tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -95,7 +101,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -118,38 +123,47 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+constexpr int tmem_cols(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn <= 128 ? 128 : 256; }
+
 template <int BN> struct Cfg {
-    static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;           // a multiple of 1024 for every BN used
+    static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;       // 4 (BN=256) ... 8 (BN=64)
+    static constexpr int EPI_ROW = 36;                              // floats per staged row: 32 + 4 of padding
+    static constexpr int EPI_BYTES = 4 * 32 * EPI_ROW * 4;          // 4 epilogue warps x 32 rows
+    static constexpr int ACC_COLS = tmem_cols(BN);                  // tensor-memory columns of one accumulator
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
+// A persistent CTA: tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...; tile -> (m tile, n tile)
+// with n fastest.  Two accumulators in tensor memory let the epilogue of one tile run while
+// the next tile's MMAs are issued.
 template <int BN, typename TO>
 __global__ void __launch_bounds__(THREADS, 1)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       const float* __restrict__ bias, TO* out, long long ldo, int M, int N, int K, int act,
-                      int accumulate, int vec_ok) {
+                      int accumulate, int vec_ok, int tiles_n, int num_tiles) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(tiles + (size_t)C::STAGES * C::STAGE_BYTES);
+    float* epi = reinterpret_cast<float*>(tiles + (size_t)C::STAGES * C::STAGE_BYTES);
+    uint64_t* full = (uint64_t*)(tiles + (size_t)C::STAGES * C::STAGE_BYTES + C::EPI_BYTES);
     uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_ready = empty + C::STAGES;
-    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    uint64_t* acc_full = empty + C::STAGES;          // [2]
+    uint64_t* acc_empty = acc_full + 2;              // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* failed = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int nk = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(tmem_slot, BN);
+    if (warp == 1) tmem_alloc(tmem_slot, 2 * C::ACC_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -159,102 +173,126 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kt = 0; kt < nk; ++kt) {
-                const int s = kt % C::STAGES;
-                if (kt >= C::STAGES && !mbar_wait(&empty[s], ((kt / C::STAGES) - 1) & 1)) { *failed = 1; break; }
-                if (*failed) break;
-                uint8_t* a_dst = tiles + (size_t)s * C::STAGE_BYTES;
-                mbar_expect_tx(&full[s], C::STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, kt * BK, m0, &full[s]);
-                tma_load_2d(a_dst + C::A_BYTES, &map_w, kt * BK, n0, &full[s]);
+            int g = 0;                                           // k-steps issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < num_tiles && !*failed; tile += gridDim.x) {
+                const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+                for (int kt = 0; kt < nk; ++kt, ++g) {
+                    const int s = g % C::STAGES;
+                    if (g >= C::STAGES && !mbar_wait(&empty[s], ((g / C::STAGES) - 1) & 1)) { *failed = 1; break; }
+                    if (*failed) break;
+                    uint8_t* a_dst = tiles + (size_t)s * C::STAGE_BYTES;
+                    mbar_expect_tx(&full[s], C::STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, kt * BK, m0, &full[s]);
+                    tma_load_2d(a_dst + C::A_BYTES, &map_w, kt * BK, n0, &full[s]);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(BM, BN);
-            bool ok = true;
-            for (int kt = 0; kt < nk && ok; ++kt) {
-                const int s = kt % C::STAGES;
-                if (!mbar_wait(&full[s], (kt / C::STAGES) & 1)) { *failed = 2; ok = false; break; }
+            int g = 0, ti = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && !*failed; tile += gridDim.x, ++ti) {
+                const int buf = ti & 1;
+                if (ti >= 2 && !mbar_wait(&acc_empty[buf], ((ti >> 1) - 1) & 1)) { *failed = 4; break; }
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
-                const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + C::A_BYTES);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * C::ACC_COLS);
+                bool ok = true;
+                for (int kt = 0; kt < nk; ++kt, ++g) {
+                    const int s = g % C::STAGES;
+                    if (!mbar_wait(&full[s], (g / C::STAGES) & 1)) { *failed = 2; ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
+                    const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + C::A_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k)      // 32 bytes along K inside the swizzle atom = +2 in the address field
-                    umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kt | k) != 0);
-                umma_commit(&empty[s]);                 // the stage is free once these MMAs have read it
+                    for (int k = 0; k < BK / 16; ++k)      // 32 bytes along K inside the swizzle atom = +2 in the address field
+                        umma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kt | k) != 0);
+                    umma_commit(&empty[s]);                 // the stage is free once these MMAs have read it
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[buf]);                // the accumulator is complete once all of them are done
             }
-            if (ok) umma_commit(acc_ready);
         }
     } else {
-        const int q = warp & 3;                         // the quarter of the 128 TMEM lanes this warp may read
-        bool ok = mbar_wait(acc_ready, 0);
-        if (!ok) *failed = 3;
-        ok = __all_sync(0xffffffffu, ok && !*failed);      // tcgen05.ld is warp-wide: decide as a warp
-        tc_fence_after();
-        if (ok) {
-            // Phase A: accumulator -> shared memory (the stage ring is free: every MMA has completed).
-            // A thread holds one row; rows are padded by 4 floats so 16-byte stores spread over the banks.
-            constexpr int SROW = BN + 4;
-            float* stage = reinterpret_cast<float*>(tiles) + (size_t)(q * 32) * SROW;
+        const int q = warp & 3;                             // the quarter of the 128 TMEM lanes this warp may read
+        float* stage = epi + (size_t)q * 32 * C::EPI_ROW;
+        const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;     // phase B: 4 rows x 8 lanes of 4 columns
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti) {
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            const int buf = ti & 1;
+            bool ok = mbar_wait(&acc_full[buf], (ti >> 1) & 1);
+            if (!ok) *failed = 3;
+            ok = __all_sync(0xffffffffu, ok && !*failed);   // tcgen05.ld is warp-wide: decide as a warp
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * C::ACC_COLS);
+            // The accumulator is read 32 columns at a time; the load of the next 32 is in flight while
+            // the current ones go through shared memory to global memory.
+            constexpr int NC = BN / 32;
+            uint32_t r[32];
+            tmem_ld32_issue(t_addr, r);
+            tmem_ld_wait();
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
-                float4* dst = reinterpret_cast<float4*>(stage + (size_t)lane * SROW + c * 32);
+            for (int c = 0; c < NC; ++c) {
+                // Phase A: 32 columns of this warp's 32 rows, one row per lane, to shared memory
+                float4* dst = reinterpret_cast<float4*>(stage + (size_t)lane * C::EPI_ROW);
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                     dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                          __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-            }
-            __syncwarp();
-            // Phase B: the warp walks its 32 rows; a lane owns 4 consecutive columns per pass of 128, so the
-            // bias sits in registers and every store instruction covers one contiguous piece of a row.
-            constexpr int PASSES = (BN + 127) / 128;
-            float bv[PASSES][4];
+                if (c + 1 < NC) tmem_ld32_issue(t_addr + (uint32_t)((c + 1) * 32), r);   // r is free: refill it meanwhile
+                __syncwarp();
+                // Phase B: each store instruction covers 4 rows x 32 consecutive columns
+                const int n = n0 + c * 32 + sub_c;
+                float bv[4] = {0.f, 0.f, 0.f, 0.f};
+                if (bias) {
 #pragma unroll
-            for (int p = 0; p < PASSES; ++p)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int n = n0 + p * 128 + lane * 4 + i;
-                    bv[p][i] = (bias && p * 128 + lane * 4 + i < BN && n < N) ? __ldg(bias + n) : 0.f;
+                    for (int i = 0; i < 4; ++i) bv[i] = n + i < N ? __ldg(bias + n + i) : 0.f;
                 }
-#pragma unroll 1
-            for (int rr = 0; rr < 32; ++rr) {
-                const int row = m0 + q * 32 + rr;
-                if (row >= M) break;
-                const float* src = stage + (size_t)rr * SROW;
+                const bool vec = vec_ok && n + 4 <= N;
+                // the old values of a residual sum are fetched together, ahead of the arithmetic
+                float4 old[8];
+                if constexpr (sizeof(TO) == 4) {
+                    if (accumulate && vec) {
 #pragma unroll
-                for (int p = 0; p < PASSES; ++p) {
-                    const int col = p * 128 + lane * 4;
-                    if (col >= BN) continue;
-                    const int n = n0 + col;
-                    if (n >= N) continue;
-                    const float4 a = *reinterpret_cast<const float4*>(src + col);
-                    float v[4] = {a.x + bv[p][0], a.y + bv[p][1], a.z + bv[p][2], a.w + bv[p][3]};
+                        for (int it = 0; it < 8; ++it) {
+                            const int row = m0 + q * 32 + it * 4 + sub_r;
+                            old[it] = (row < M && n < N) ? *reinterpret_cast<const float4*>(out + (size_t)row * ldo + n)
+                                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    }
+                }
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) v[i] = apply_act(v[i], act);
+                for (int it = 0; it < 8; ++it) {
+                    const int rr = it * 4 + sub_r;
+                    const int row = m0 + q * 32 + rr;
+                    if (row >= M || n >= N) continue;
+                    const float4 a = *reinterpret_cast<const float4*>(stage + (size_t)rr * C::EPI_ROW + sub_c);
+                    float v[4] = {a.x + bv[0], a.y + bv[1], a.z + bv[2], a.w + bv[3]};
+                    if (act == MLLM_ACT_GELU_TANH) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) v[i] = sizeof(TO) == 2 ? gelu_tanh_fast(v[i]) : gelu_tanh_f(v[i]);
+                    } else if (act == MLLM_ACT_GELU_ERF) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) v[i] = gelu_erf_f(v[i]);
+                    }
                     TO* o = out + (size_t)row * ldo + n;
-                    if (vec_ok && n + 4 <= N) {
+                    if (vec) {
                         if constexpr (sizeof(TO) == 4) {
-                            float4* po = reinterpret_cast<float4*>(o);
-                            if (accumulate) {
-                                const float4 old = *po;
-                                v[0] += old.x; v[1] += old.y; v[2] += old.z; v[3] += old.w;
-                            }
-                            *po = make_float4(v[0], v[1], v[2], v[3]);
+                            if (accumulate) { v[0] += old[it].x; v[1] += old[it].y; v[2] += old[it].z; v[3] += old[it].w; }
+                            *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
                         } else {
                             uint2* po = reinterpret_cast<uint2*>(o);
                             if (accumulate) {
-                                const uint2 old = *po;
-                                const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&old);
+                                const uint2 ob = *po;
+                                const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&ob);
                                 v[0] += __low2float(oh[0]); v[1] += __high2float(oh[0]);
                                 v[2] += __low2float(oh[1]); v[3] += __high2float(oh[1]);
                             }
                             uint2 pk;
-                            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-                            h[0] = __floats2bfloat162_rn(v[0], v[1]);
-                            h[1] = __floats2bfloat162_rn(v[2], v[3]);
+                            __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&pk);
+                            hh[0] = __floats2bfloat162_rn(v[0], v[1]);
+                            hh[1] = __floats2bfloat162_rn(v[2], v[3]);
                             *po = pk;
                         }
                     } else {
@@ -267,6 +305,14 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                             }
                         }
                     }
+                }
+                if (c + 1 < NC) tmem_ld_wait();
+                if (c == NC - 2 || NC == 1) {                // the last read of this accumulator has landed (or there was one)
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                } else {
+                    __syncwarp();                            // the staging rows are free for the next 32 columns
                 }
             }
         }
@@ -281,7 +327,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, BN);
+        tmem_dealloc(tmem_base, 2 * C::ACC_COLS);
     }
 }
 
@@ -345,10 +391,21 @@ int get_map(const void* ptr, long long ld, int rows, int cols, int box_rows, CUt
     return 0;
 }
 
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
 template <int BN, typename TO>
 int launch(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo, int M, int N,
            int K, int act, int accumulate, cudaStream_t stream) {
     using C = Cfg<BN>;
+    static_assert(C::STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of swizzled tiles");
     CUtensorMap ma, mw;
     int rc = get_map(A, lda, M, K, BM, &ma);
     if (rc) return rc;
@@ -362,22 +419,40 @@ int launch(const void* A, long long lda, const void* W, const float* bias, void*
     }
     // 4 consecutive outputs per store: 16 bytes (32-bit) or 8 bytes (bfloat16); column offsets are multiples of 4
     const int vec_ok = ((uintptr_t)out % (4 * sizeof(TO)) == 0) && (ldo % 4 == 0);
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    MLLM_CUDA(mllm_launch(kern, grid, dim3(THREADS), C::SMEM, stream, true, ma, mw, bias, (TO*)out, ldo, M, N, K, act,
-                          accumulate, vec_ok));
+    const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
+    const int num_tiles = tiles_n * tiles_m;
+    const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
+    MLLM_CUDA(mllm_launch(kern, dim3(grid), dim3(THREADS), C::SMEM, stream, true, ma, mw, bias, (TO*)out, ldo, M, N, K,
+                          act, accumulate, vec_ok, tiles_n, num_tiles));
     return 0;
 }
 
 template <typename TO>
 int pick_bn(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo, int M, int N,
             int K, int act, int accumulate, cudaStream_t stream) {
-    const long long mt = (M + BM - 1) / BM;
-    // the widest tile that still gives every one of the 148 SMs a CTA; else the narrowest
-    if (mt * ((N + 255) / 256) >= 148)
-        return launch<256, TO>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
-    if (mt * ((N + 127) / 128) >= 148)
-        return launch<128, TO>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
-    return launch<64, TO>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+    // The tile width that moves the fewest bytes per SM: a CTA runs ceil(tiles / SMs) tiles one after
+    // the other and every k-step of a tile brings in (128 + BN) rows of 64 values.
+    const int widths[5] = {256, 192, 128, 96, 64};
+    const long long tiles_m = (M + BM - 1) / BM;
+    long long best_cost = -1;
+    int best = 64;
+    for (int i = 0; i < 5; ++i) {
+        const int bn = widths[i];
+        if (bn > 64 && bn >= 2 * N) continue;                       // far wider than the matrix
+        const long long tiles = tiles_m * ((N + bn - 1) / bn);
+        const long long rounds = (tiles + sm_count() - 1) / sm_count();
+        const long long cost = rounds * (BM + bn) + rounds * 24;  // + a fixed part per tile (epilogue tail)
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+#define GO(B) return launch<B, TO>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream)
+    switch (best) {
+        case 256: GO(256);
+        case 192: GO(192);
+        case 128: GO(128);
+        case 96: GO(96);
+        default: GO(64);
+    }
+#undef GO
 }
 
 }  // namespace

@@ -148,61 +148,79 @@ class ModelRunner:
         if not entries:
             raise StepError("a step needs at least one entry")
         seen = set()
+        toks: List[np.ndarray] = []
         for en in entries:
             if en.req in seen:
                 raise StepError(f"request {en.req!r} appears twice in one step")
             seen.add(en.req)
             if not cm.is_live(en.req):
                 raise StepError(f"request {en.req!r} is not live (add_request first)")
-            n = len(en.tokens)
+            arr = np.asarray(en.tokens, dtype=np.int64).reshape(-1)
+            n = arr.size
             if n == 0:
                 raise StepError(f"request {en.req!r} brings no tokens")
             start = cm.computed(en.req)
             if self.max_positions is not None and start + n > self.max_positions:
                 raise StepError(f"request {en.req!r}: {start + n} tokens exceed the model's {self.max_positions} positions")
-            for t in en.tokens:
-                if not (0 <= int(t) < self.vocab_size):
-                    raise StepError(f"request {en.req!r}: token id {t} is outside the vocabulary of {self.vocab_size}")
+            if int(arr.min()) < 0 or int(arr.max()) >= self.vocab_size:
+                bad = int(arr[(arr < 0) | (arr >= self.vocab_size)][0])
+                raise StepError(f"request {en.req!r}: token id {bad} is outside the vocabulary of {self.vocab_size}")
             for w in en.want:
                 if not (0 <= int(w) < n):
                     raise StepError(f"request {en.req!r}: wanted place {w} is outside its {n} tokens")
-        reserved = []
-        for en in entries:
-            if not cm.reserve(en.req, len(en.tokens)):
-                raise OutOfPages(f"no pages left for {len(en.tokens)} tokens of request {en.req!r} "
+            toks.append(arr)
+        for en, arr in zip(entries, toks):
+            if not cm.reserve(en.req, arr.size):
+                raise OutOfPages(f"no pages left for {arr.size} tokens of request {en.req!r} "
                                  f"({[g.allocator.num_free for g in cm.groups]} free)")
-            reserved.append(en.req)
-        token_ids: List[int] = []
-        positions: List[int] = []
-        token_seq: List[int] = []
-        logit_rows: List[int] = []
-        cu_q = [0]
-        q_start, ctx_len, slots, q_lens = [], [], [], []
+        S = len(entries)
+        ps = cm.page_size
+        q_lens = [a.size for a in toks]
+        q_start = [cm.computed(en.req) for en in entries]
+        ctx_len = [a + b for a, b in zip(q_start, q_lens)]
+        slots = [cm.slot(en.req) for en in entries]
+        cu_q = np.zeros(S + 1, dtype=np.int64)
+        np.cumsum(q_lens, out=cu_q[1:])
+        T = int(cu_q[-1])
         ng = len(cm.groups)
-        slot_maps: List[List[int]] = [[] for _ in range(ng)]
-        tables: List[List[List[int]]] = [[] for _ in range(ng)]
-        for s, en in enumerate(entries):
-            n = len(en.tokens)
-            start = cm.computed(en.req)
-            base = len(token_ids)
-            token_ids.extend(int(t) for t in en.tokens)
-            positions.extend(range(start, start + n))
-            token_seq.extend([s] * n)
-            logit_rows.extend(base + int(w) for w in en.want)
-            cu_q.append(base + n)
-            q_start.append(start)
-            ctx_len.append(start + n)
-            q_lens.append(n)
-            slots.append(cm.slot(en.req))
+        tables = [[cm.table(en.req, g) for en in entries] for g in range(ng)]
+        if T == S:                                   # a decode step: one token each, plain integers are quickest
+            token_ids = np.fromiter((a[0] for a in toks), dtype=np.int64, count=S)
+            positions = np.asarray(q_start, dtype=np.int64)
+            token_seq = np.arange(S, dtype=np.int64)
+            slot_maps = []
             for g in range(ng):
-                slot_maps[g].extend(cm.slots_for(en.req, g, start, n))
-                tables[g].append(cm.table(en.req, g))
+                sm = []
+                for tab, p in zip(tables[g], q_start):
+                    page = tab[p // ps]
+                    if page < 0:
+                        raise StepError("a position of this step lies in a page that was given back")
+                    sm.append(page * ps + p % ps)
+                slot_maps.append(sm)
+        else:
+            token_ids = np.concatenate(toks)
+            positions = np.concatenate([np.arange(a, a + n, dtype=np.int64) for a, n in zip(q_start, q_lens)])
+            token_seq = np.repeat(np.arange(S, dtype=np.int64), q_lens)
+            slot_maps = []
+            for g in range(ng):
+                parts = []
+                for tab, a, n in zip(tables[g], q_start, q_lens):
+                    pos = np.arange(a, a + n, dtype=np.int64)
+                    pages = np.asarray(tab, dtype=np.int64)[pos // ps]
+                    if pages.min() < 0:
+                        raise StepError("a position of this step lies in a page that was given back")
+                    parts.append(pages * ps + pos % ps)
+                slot_maps.append(np.concatenate(parts))
+        logit_rows: List[int] = []
+        for s, en in enumerate(entries):
+            base = int(cu_q[s])
+            logit_rows.extend(base + int(w) for w in en.want)
         max_pages = []
         for g in range(ng):
             mp = max(len(t) for t in tables[g])
             max_pages.append(max(16, (mp + 15) // 16 * 16))    # wide steps: few distinct shapes for captured graphs
-        tiles = [] if max(q_lens) == 1 else attention_tiles(q_lens)
-        layout = StepLayout.make(len(token_ids), len(entries), len(logit_rows), max_pages, len(tiles) // 3)
+        tiles = [] if T == S else attention_tiles(q_lens)
+        layout = StepLayout.make(T, S, len(logit_rows), max_pages, len(tiles) // 3)
         i, host = self._staging(layout.total)
         self._last_layout_total = layout.total
         pack_step(layout, host.numpy(), token_ids=token_ids, positions=positions, token_seq=token_seq,
