@@ -247,6 +247,40 @@ def run_prefill(model_dir, dtype, iters=5, warmup=3):
     return dict(ms=ms, tok_s=PREFILL_TOKENS / (ms / 1e3), flops=fl)
 
 
+def profile_step(kind: str, dtype: str, layers: int, batch: int) -> int:
+    """One eager prefill step (2 x 1024 tokens) or a few eager decode steps at GPT-2 small's
+    layer sizes with ``layers`` layers: a small, bounded workload to put under ncu, e.g.
+    ncu --set full --clock-control none -k regex:attention_flash -c 1 python bench.py --profile-step prefill --layers 2"""
+    import torch
+    import mini_llm_b200 as m
+    from mini_llm_b200 import ops
+    from mini_llm_b200.config.base import EngineConfig
+    from mini_llm_b200.engine.runner import ModelRunner, StepEntry
+
+    cfg = dict(SMALL, n_layer=layers)
+    with tempfile.TemporaryDirectory(prefix="mini_llm_prof_") as d:
+        m.write_random_model(cfg, 0, d, dtype=dtype)
+        n = cfg["n_positions"]
+        B = 2 if kind == "prefill" else batch
+        runner = ModelRunner(d, EngineConfig(dtype=dtype, page_size=PAGE, max_tokens=B * n, max_num_seqs=B,
+                                             max_num_batched_tokens=2048, use_cuda_graphs=False))
+        g = torch.Generator().manual_seed(7)
+        plen = n if kind == "prefill" else PROMPT_LEN
+        prompts = torch.randint(0, cfg["vocab_size"], (B, plen), generator=g).tolist()
+        for i in range(B):
+            runner.add_request(i)
+        for lo in range(0, B, 2):
+            runner.step([StepEntry(i, prompts[i], [plen - 1]) for i in range(lo, min(B, lo + 2))])
+        if kind == "decode":
+            out = torch.empty(B, dtype=torch.int32, device=runner.device)
+            for _ in range(3):
+                ops.argmax(runner.step([StepEntry(i, [11], [0]) for i in range(B)]), out)
+        torch.cuda.synchronize()
+        ops.check_device_errors()
+    print(json.dumps({"profile_step": kind, "layers": layers, "batch": B, "dtype": dtype, "launches": ops.launches}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -257,7 +291,11 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=SMALL["n_layer"], help="fewer layers than GPT-2 small's 12, if needed")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    ap.add_argument("--profile-step", choices=["prefill", "decode"],
+                    help="run one small eager step for a profiler instead of the benchmark")
     args = ap.parse_args()
+    if args.profile_step:
+        return profile_step(args.profile_step, args.dtype, args.layers, args.batch)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "taejuk/mini-llm is a CMake C++/CUDA project with no setup.py or pyproject.toml: "
