@@ -159,6 +159,9 @@ class CacheManager:
 
     def reserve(self, req, n_new: int) -> bool:
         """Pages for the next n_new tokens in every group, or none at all."""
+        total = (self._live[req].computed + n_new + self.page_size - 1) // self.page_size
+        if all(len(g.tables[req]) >= total for g in self.groups):
+            return True                              # the common decode case: the last page still has room
         miss = self.pages_missing(req, n_new)
         if not all(self.groups[gi].allocator.can_allocate(n) for gi, n in miss.items()):
             return False

@@ -137,7 +137,10 @@ class StepContext:
         for g, mp in enumerate(layout.max_pages):
             bt = dev[o[f"block_table.{g}"]:o[f"block_table.{g}"] + self.S * mp].view(self.S, mp)
             self.groups.append(GroupView(block_table=bt, slot_mapping=sec(f"slot_mapping.{g}", self.T), max_pages=mp))
-        # host-side facts (never read back from the device)
+        self.set_host_facts(q_lens, q_starts)
+
+    def set_host_facts(self, q_lens: Sequence[int], q_starts: Sequence[int]) -> None:
+        """What the host knows about the step (never read back from the device)."""
         self.q_lens = list(q_lens)
         self.q_starts = list(q_starts)
         self.max_q_len = max(self.q_lens) if self.q_lens else 0

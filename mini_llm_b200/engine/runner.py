@@ -81,6 +81,7 @@ class ModelRunner:
         self._host_events = [None, None]
         self._host_turn = 0
         self._dev: Optional[torch.Tensor] = None
+        self._ctx_cache: Dict[tuple, StepContext] = {}
         self.steps_run = 0
         # CUDA graphs of decode-only steps, by the step's shape
         self._graphs: Dict[tuple, object] = {}
@@ -155,27 +156,32 @@ class ModelRunner:
             seen.add(en.req)
             if not cm.is_live(en.req):
                 raise StepError(f"request {en.req!r} is not live (add_request first)")
-            arr = np.asarray(en.tokens, dtype=np.int64).reshape(-1)
-            n = arr.size
+            n = len(en.tokens)
             if n == 0:
                 raise StepError(f"request {en.req!r} brings no tokens")
+            if n == 1:                                   # a decoded token: no array needed to check it
+                arr = (int(en.tokens[0]),)
+                lo = hi = arr[0]
+            else:
+                arr = np.asarray(en.tokens, dtype=np.int64).reshape(-1)
+                lo, hi = int(arr.min()), int(arr.max())
             start = cm.computed(en.req)
             if self.max_positions is not None and start + n > self.max_positions:
                 raise StepError(f"request {en.req!r}: {start + n} tokens exceed the model's {self.max_positions} positions")
-            if int(arr.min()) < 0 or int(arr.max()) >= self.vocab_size:
-                bad = int(arr[(arr < 0) | (arr >= self.vocab_size)][0])
+            if lo < 0 or hi >= self.vocab_size:
+                bad = next(int(t) for t in en.tokens if not (0 <= int(t) < self.vocab_size))
                 raise StepError(f"request {en.req!r}: token id {bad} is outside the vocabulary of {self.vocab_size}")
             for w in en.want:
                 if not (0 <= int(w) < n):
                     raise StepError(f"request {en.req!r}: wanted place {w} is outside its {n} tokens")
             toks.append(arr)
         for en, arr in zip(entries, toks):
-            if not cm.reserve(en.req, arr.size):
-                raise OutOfPages(f"no pages left for {arr.size} tokens of request {en.req!r} "
+            if not cm.reserve(en.req, len(arr)):
+                raise OutOfPages(f"no pages left for {len(arr)} tokens of request {en.req!r} "
                                  f"({[g.allocator.num_free for g in cm.groups]} free)")
         S = len(entries)
         ps = cm.page_size
-        q_lens = [a.size for a in toks]
+        q_lens = [len(a) for a in toks]
         q_start = [cm.computed(en.req) for en in entries]
         ctx_len = [a + b for a, b in zip(q_start, q_lens)]
         slots = [cm.slot(en.req) for en in entries]
@@ -198,7 +204,7 @@ class ModelRunner:
                     sm.append(page * ps + p % ps)
                 slot_maps.append(sm)
         else:
-            token_ids = np.concatenate(toks)
+            token_ids = np.concatenate([np.asarray(a, dtype=np.int64) for a in toks])
             positions = np.concatenate([np.arange(a, a + n, dtype=np.int64) for a, n in zip(q_start, q_lens)])
             token_seq = np.repeat(np.arange(S, dtype=np.int64), q_lens)
             slot_maps = []
@@ -228,7 +234,17 @@ class ModelRunner:
                   slot_mappings=slot_maps, block_tables=tables, attn_tiles=tiles)
         self._dev[:layout.total].copy_(host[:layout.total], non_blocking=True)
         self._host_events[i].record()
-        return StepContext(layout, self._dev, self.ws, q_lens=q_lens, q_starts=q_start)
+        # the device views of a layout are always the same tensors: keep them, refresh the host-side facts
+        key = (layout.key(), self._dev.data_ptr())
+        ctx = self._ctx_cache.get(key)
+        if ctx is None:
+            if len(self._ctx_cache) > 256:
+                self._ctx_cache.clear()
+            ctx = StepContext(layout, self._dev, self.ws, q_lens=q_lens, q_starts=q_start)
+            self._ctx_cache[key] = ctx
+        else:
+            ctx.set_host_facts(q_lens, q_start)
+        return ctx
 
     def step(self, entries: Sequence[StepEntry], commit: bool = True) -> Optional[torch.Tensor]:
         """Run one batch; returns 32-bit logits [number of wanted places, vocab] in the
