@@ -1,11 +1,15 @@
 // Causal attention of prompt portions over the paged cache on tensor cores:
 // tiles of 64 queries against tiles of 64 keys, online softmax in 32-bit registers.
 //
-// A CTA (4 warps, 16 query rows each) takes one tile of up to 64 consecutive new tokens
-// of one request (the host cuts every request's portion into such tiles) and one head.
-// Keys and values come from the request's pages: tile j always covers the absolute
-// positions [64j, 64j+64), so the order of the additions for a query does not depend on
-// how the prompt was cut or what else is in the batch.  K and V tiles are brought in
+// A CTA takes one tile of up to 64 consecutive new tokens of one request (the host cuts
+// every request's portion into such tiles) and one head.  It has two groups of 4 warps (16
+// query rows per warp): group 0 walks the even key tiles, group 1 the odd ones, each with
+// its own online-softmax state, and the two states are merged (even, then odd) at the
+// end, which halves the walk of the longest rows.  Keys and values come from the
+// request's pages: tile j always covers the absolute positions [64j, 64j+64) and belongs
+// to group j mod 2, so the order of the additions for a query does not depend on how the
+// prompt was cut or what else is in the batch.  Heavy tiles (late positions) are launched
+// first.  K and V tiles are brought in
 // with cp.async (16-byte pieces, two stages), S = Q.K^T and O += P.V run on
 // mma.sync.m16n8k16 (bf16 in, 32-bit accumulate); the recurrence
 // m' = max(m, s), alpha = exp(m - m'), p = exp(s - m'), o = o*alpha + p*v, l = l*alpha + p
@@ -19,7 +23,7 @@
 
 namespace {
 
-constexpr int BQ = 64, BKV = 64, WARPS = 4;
+constexpr int BQ = 64, BKV = 64, WARPS = 4, GROUPS = 2;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -48,7 +52,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int DH>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(GROUPS * WARPS * 32, DH <= 64 ? 2 : 1)
 attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
                        const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                        const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tiles,
@@ -57,11 +61,12 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     constexpr int ROW = DH + 8;                       // padded row (elements): ldmatrix rows hit distinct banks
     constexpr int CH = DH / 8;                        // 16-byte pieces per row
     extern __shared__ __align__(16) uint8_t smem[];
+    const int group = threadIdx.x / (WARPS * 32), gtid = threadIdx.x % (WARPS * 32);
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);
-    __nv_bfloat16* sK = sQ + BQ * ROW;                // [2][BKV][ROW]
-    __nv_bfloat16* sV = sK + 2 * BKV * ROW;           // [2][BKV][ROW]
+    __nv_bfloat16* sK = sQ + BQ * ROW + group * (4 * BKV * ROW);      // this group's [2][BKV][ROW]
+    __nv_bfloat16* sV = sK + 2 * BKV * ROW;                           // and its [2][BKV][ROW]
 
-    const int tile = blockIdx.x, h = blockIdx.y;
+    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;      // late (long) tiles first
     pdl_wait();
     pdl_launch();
     const int seq = tiles[tile * 3], tok0 = tiles[tile * 3 + 1], rows = tiles[tile * 3 + 2];
@@ -69,15 +74,18 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     const int pos_max = pos0 + rows - 1;
     const int hk = h / (H / Hkv);
     const int* bt = block_table + (size_t)seq * bt_stride;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = gtid >> 5, lane = gtid & 31;                   // warp inside its group
     const int g = lane >> 2, t = lane & 3;
 
     int first_key = 0;
     if (window > 0 && pos0 - window + 1 > 0) first_key = pos0 - window + 1;
-    const int j_lo = first_key / BKV, j_hi = pos_max / BKV;
+    const int j_first = first_key / BKV, j_hi = pos_max / BKV;
+    // this group's tiles: j = j_lo, j_lo + 2, ... with j mod 2 == group
+    const int j_lo = j_first + ((j_first & 1) != group ? 1 : 0);
+    const int rounds = (j_hi - j_first) / 2 + 1;                        // both groups take part in every round
 
     // Q tile -> shared memory (rows beyond the tile are zeros)
-    for (int i = threadIdx.x; i < BQ * CH; i += WARPS * 32) {
+    for (int i = threadIdx.x; i < BQ * CH; i += GROUPS * WARPS * 32) {
         const int r = i / CH, c = i % CH;
         cp_async16(sQ + r * ROW + c * 8, q + (size_t)(tok0 + (r < rows ? r : 0)) * q_stride + (size_t)h * DH + c * 8,
                    r < rows);
@@ -85,7 +93,7 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     auto load_kv = [&](int j, int stage) {
         __nv_bfloat16* dK = sK + stage * BKV * ROW;
         __nv_bfloat16* dV = sV + stage * BKV * ROW;
-        for (int i = threadIdx.x; i < BKV * CH; i += WARPS * 32) {
+        for (int i = gtid; i < BKV * CH; i += WARPS * 32) {
             const int r = i / CH, c = i % CH;
             const int kp = j * BKV + r;
             const bool ok = kp <= pos_max && kp >= first_key;
@@ -98,7 +106,7 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
             cp_async16(dV + r * ROW + c * 8, v_pages + off, ok);
         }
     };
-    load_kv(j_lo, 0);
+    if (j_lo <= j_hi) load_kv(j_lo, 0);
     cp_commit();
 
     float o[DH / 8][4];
@@ -111,17 +119,19 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     uint32_t qa[DH / 16][4];
     const int qrow0 = pos0 + warp * 16 + g;           // absolute position of this thread's first row; second is +8
 
-    for (int j = j_lo; j <= j_hi; ++j) {
-        const int stage = (j - j_lo) & 1;
-        if (j < j_hi) load_kv(j + 1, stage ^ 1);
+    for (int rd = 0; rd < rounds; ++rd) {
+        const int j = j_lo + 2 * rd;
+        const int stage = rd & 1;
+        if (j + 2 <= j_hi) load_kv(j + 2, stage ^ 1);
         cp_commit();
         cp_wait<1>();
         __syncthreads();
-        if (j == j_lo) {
+        if (rd == 0) {
 #pragma unroll
             for (int ks = 0; ks < DH / 16; ++ks)
                 ldsm_x4(qa[ks], sQ + (warp * 16 + (lane & 15)) * ROW + ks * 16 + (lane >> 4) * 8);
         }
+        if (j > j_hi) { __syncthreads(); continue; }          // this group has no tile in the last round
         const __nv_bfloat16* tK = sK + stage * BKV * ROW;
         const __nv_bfloat16* tV = sV + stage * BKV * ROW;
         // S = Q K^T : 16 rows x 64 keys per warp
@@ -212,6 +222,31 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
         __syncthreads();                                   // the stage may be overwritten by the next load
     }
     cp_wait<0>();
+    // merge the two groups' states: the odd-tile group hands (m, l, o) over through shared memory
+    float* xch = reinterpret_cast<float*>(smem) + (size_t)(warp * 32 + lane) * (DH / 2 + 4);   // the K/V stages are free
+    __syncthreads();
+    if (group == 1) {
+        xch[0] = m_run[0]; xch[1] = m_run[1]; xch[2] = l_run[0]; xch[3] = l_run[1];
+#pragma unroll
+        for (int i = 0; i < DH / 8; ++i)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) xch[4 + i * 4 + k] = o[i][k];
+    }
+    __syncthreads();
+    if (group == 1) return;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const float m1 = xch[r], l1 = xch[2 + r];
+        const float mm = fmaxf(m_run[r], m1);
+        const float muse2 = mm == -INFINITY ? 0.f : mm;
+        const float a0 = exp2f(m_run[r] - muse2), a1 = exp2f(m1 - muse2);
+        l_run[r] = l_run[r] * a0 + l1 * a1;
+#pragma unroll
+        for (int i = 0; i < DH / 8; ++i) {
+            o[i][2 * r] = o[i][2 * r] * a0 + xch[4 + i * 4 + 2 * r] * a1;
+            o[i][2 * r + 1] = o[i][2 * r + 1] * a0 + xch[4 + i * 4 + 2 * r + 1] * a1;
+        }
+    }
     // write O / l
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -231,7 +266,7 @@ template <int DH>
 int launch(const void* q, long long q_stride, const void* k_pages, const void* v_pages, const int* block_table,
            int bt_stride, const int* tiles, int n_tiles, const int* positions, void* out, long long out_stride,
            int H, int Hkv, int page_size, float scale, int window, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)(BQ + 4 * BKV) * (DH + 8) * sizeof(__nv_bfloat16);
+    constexpr size_t smem = (size_t)(BQ + GROUPS * 4 * BKV) * (DH + 8) * sizeof(__nv_bfloat16);
     auto kern = attention_flash_kernel<DH>;
     static bool set = false;
     if (!set && smem > 48 * 1024) {
@@ -239,7 +274,7 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
         set = true;
     }
     using bf = __nv_bfloat16;
-    MLLM_CUDA(mllm_launch(kern, dim3(n_tiles, H), dim3(WARPS * 32), smem, stream, true, (const bf*)q, q_stride,
+    MLLM_CUDA(mllm_launch(kern, dim3(n_tiles, H), dim3(GROUPS * WARPS * 32), smem, stream, true, (const bf*)q, q_stride,
                           (const bf*)k_pages, (const bf*)v_pages, block_table, bt_stride, tiles, positions, (bf*)out,
                           out_stride, H, Hkv, page_size, scale, window));
     return 0;

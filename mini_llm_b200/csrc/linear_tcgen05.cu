@@ -9,8 +9,9 @@
 // and any K that is a multiple of 8 work).  Warp 1 (one lane) issues tcgen05.mma
 // (cta_group::1, kind::f16, M=128, N=BN, K=16, four per stage) with the accumulator in
 // tensor memory, and frees a stage with tcgen05.commit.  There are two accumulators, so
-// the MMAs of the next tile run while warps 2..5, the epilogue, drain the last one: each
-// warp reads its 32 lanes with tcgen05.ld, 32 columns at a time, passes them through a
+// the MMAs of the next tile run while warps 2..9, the epilogue, drain the last one: two
+// warps share a quarter of the lanes and take 32-column chunks in turn; a warp reads its
+// 32 lanes with tcgen05.ld, passes them through a
 // small shared-memory staging area so that a store instruction covers 4 rows x 32
 // consecutive columns, and applies bias, activation or the 32-bit residual sum on the way.
 //
@@ -30,7 +31,8 @@
 namespace {
 
 constexpr int BM = 128, BK = 64;
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 8;                  // two per quarter of the tensor-memory lanes
+constexpr int THREADS = (2 + EPI_WARPS) * 32;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;     // two seconds, then the wait gives up
 
 __device__ int g_tc_error = 0;          // first error code seen by any tcgen05 kernel
@@ -128,9 +130,9 @@ constexpr int tmem_cols(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn <= 1
 template <int BN> struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;           // a multiple of 1024 for every BN used
-    static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;       // 4 (BN=256) ... 8 (BN=64)
     static constexpr int EPI_ROW = 36;                              // floats per staged row: 32 + 4 of padding
-    static constexpr int EPI_BYTES = 4 * 32 * EPI_ROW * 4;          // 4 epilogue warps x 32 rows
+    static constexpr int EPI_BYTES = EPI_WARPS * 32 * EPI_ROW * 4;  // every epilogue warp stages 32 rows
+    static constexpr int STAGES = (227 * 1024 - EPI_BYTES - 2304) / STAGE_BYTES;   // 3 (BN=256) ... 7 (BN=64)
     static constexpr int ACC_COLS = tmem_cols(BN);                  // tensor-memory columns of one accumulator
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 };
@@ -159,7 +161,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], EPI_WARPS); }
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -214,7 +216,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
     } else {
         const int q = warp & 3;                             // the quarter of the 128 TMEM lanes this warp may read
-        float* stage = epi + (size_t)q * 32 * C::EPI_ROW;
+        const int half = (warp - 2) >> 2;                   // the two warps of a quarter take the 32-column chunks in turn
+        float* stage = epi + (size_t)(warp - 2) * 32 * C::EPI_ROW;
         const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;     // phase B: 4 rows x 8 lanes of 4 columns
         int ti = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti) {
@@ -230,17 +233,24 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             // the current ones go through shared memory to global memory.
             constexpr int NC = BN / 32;
             uint32_t r[32];
-            tmem_ld32_issue(t_addr, r);
-            tmem_ld_wait();
+            if (half < NC) {
+                tmem_ld32_issue(t_addr + (uint32_t)(half * 32), r);
+                tmem_ld_wait();
+            }
+            if (half + 2 >= NC) {                            // that was this warp's only read (or it has none)
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            }
 #pragma unroll 1
-            for (int c = 0; c < NC; ++c) {
+            for (int c = half; c < NC; c += 2) {
                 // Phase A: 32 columns of this warp's 32 rows, one row per lane, to shared memory
                 float4* dst = reinterpret_cast<float4*>(stage + (size_t)lane * C::EPI_ROW);
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                     dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                          __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                if (c + 1 < NC) tmem_ld32_issue(t_addr + (uint32_t)((c + 1) * 32), r);   // r is free: refill it meanwhile
+                if (c + 2 < NC) tmem_ld32_issue(t_addr + (uint32_t)((c + 2) * 32), r);   // r is free: refill it meanwhile
                 __syncwarp();
                 // Phase B: each store instruction covers 4 rows x 32 consecutive columns
                 const int n = n0 + c * 32 + sub_c;
@@ -306,8 +316,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                         }
                     }
                 }
-                if (c + 1 < NC) tmem_ld_wait();
-                if (c == NC - 2 || NC == 1) {                // the last read of this accumulator has landed (or there was one)
+                if (c + 2 < NC) tmem_ld_wait();
+                if (c + 2 < NC && c + 4 >= NC) {             // this warp's last read of the accumulator has landed
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
