@@ -63,20 +63,28 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int MT, int RT, typename TO, bool LN, bool KVW>
+template <int MT, int RT_, typename TO, bool LN, bool KVW>
 __global__ void __launch_bounds__(WARPS * 32)
 linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ W,
                      const float* __restrict__ bias, TO* out, long long ldo, int M, int N, int K, int act,
                      int accumulate, NormArgs ln, KvArgs kv) {
-    extern __shared__ float red[];                 // [WARPS][16*RT][8*MT]
+    // RT_ == 0 stands for half a row tile: 8 weight rows per CTA (the upper half of the MMA's 16 rows
+    // stays zero), which doubles the number of CTAs for narrow matrices.
+    constexpr bool HALF = RT_ == 0;
+    constexpr int RT = HALF ? 1 : RT_;
+    extern __shared__ float red[];                 // [WARPS][ROWS][8*MT], then the normed rows (LN)
     __shared__ float s_mean[LN ? 64 : 1], s_rstd[LN ? 64 : 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * (16 * RT);
+    constexpr int U = HALF ? 8 : (RT == 1 ? 4 : (RT == 2 ? 2 : 1));
+    constexpr int ROWS = HALF ? 8 : 16 * RT, COLS = 8 * MT;
+    const int n0 = blockIdx.x * ROWS;
     const int nchunks = (K + 31) / 32;
-    constexpr int U = RT == 1 ? 4 : (RT == 2 ? 2 : 1);
-    constexpr int ROWS = 16 * RT, COLS = 8 * MT;
     const uint4 zero = make_uint4(0, 0, 0, 0);
+    // normed rows in shared memory (bfloat16, rows padded by 8 so that 16-byte reads of 8 rows do not collide)
+    const int xs_stride = K + 8;
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(red + WARPS * ROWS * COLS);
+    const bool ln_smem = LN && K <= 1024;
 
     // The weight loads of the first round go out before anything else: they come from HBM and
     // nothing they need depends on the norm statistics or on the epilogue's operands.
@@ -90,7 +98,7 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
             for (int r = 0; r < RT; ++r) {
                 const int ra = n0 + r * 16 + g, rb = ra + 8;
                 da[u][r] = (kok && ra < N) ? ldg16(W + (size_t)ra * K + k) : zero;
-                db[u][r] = (kok && rb < N) ? ldg16(W + (size_t)rb * K + k) : zero;
+                db[u][r] = (!HALF && kok && rb < N) ? ldg16(W + (size_t)rb * K + k) : zero;
             }
         }
     };
@@ -149,7 +157,23 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
                 }
             }
             const float var = warp_sum(q) / (float)K;
-            if (lane == 0) { s_mean[m] = mean; s_rstd[m] = rsqrtf(var + ln.eps); }
+            const float rstd = rsqrtf(var + ln.eps);
+            if (lane == 0) { s_mean[m] = mean; s_rstd[m] = rstd; }
+            if (fits) {
+                // the normed row, rounded to bfloat16 as a separate norm kernel would store it
+#pragma unroll
+                for (int i = 0; i < KEEP; ++i) {
+                    const int k = lane * 4 + i * 128;
+                    if (k < K) {
+                        const float4 ga = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
+                        const float4 be = __ldg(reinterpret_cast<const float4*>(ln.beta + k));
+                        uint2 pk;
+                        pk.x = pack2((keep[i].x - mean) * rstd * ga.x + be.x, (keep[i].y - mean) * rstd * ga.y + be.y);
+                        pk.y = pack2((keep[i].z - mean) * rstd * ga.z + be.z, (keep[i].w - mean) * rstd * ga.w + be.w);
+                        *reinterpret_cast<uint2*>(xs + (size_t)m * xs_stride + k) = pk;
+                    }
+                }
+            }
         }
         __syncthreads();
     }
@@ -175,7 +199,9 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
                 const int row = m * 8 + g;
                 xv[m] = zero;
                 if (kok && row < M) {
-                    if constexpr (LN) {
+                    if (ln_smem) {
+                        xv[m] = *reinterpret_cast<const uint4*>(xs + (size_t)row * xs_stride + k);
+                    } else if constexpr (LN) {
                         const float* xr = ln.x + (size_t)(ln.rows ? ln.rows[row] : row) * ldx + k;
                         const float4 a = *reinterpret_cast<const float4*>(xr), b = *reinterpret_cast<const float4*>(xr + 4);
                         const float4 ga = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
@@ -216,8 +242,10 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
             const int row = r * 16 + g, col = m * 8 + 2 * t;
             mine[row * COLS + col] = acc[r][m][0];
             mine[row * COLS + col + 1] = acc[r][m][1];
-            mine[(row + 8) * COLS + col] = acc[r][m][2];
-            mine[(row + 8) * COLS + col + 1] = acc[r][m][3];
+            if constexpr (!HALF) {
+                mine[(row + 8) * COLS + col] = acc[r][m][2];
+                mine[(row + 8) * COLS + col + 1] = acc[r][m][3];
+            }
         }
     __syncthreads();
     // consecutive threads take consecutive weight rows (n) of one token, so stores run along n
@@ -260,16 +288,18 @@ struct Call {
 
 template <int MT, int RT, typename TO, bool LN, bool KVW>
 int launch_k(const Call& c) {
-    const size_t smem = (size_t)WARPS * 16 * RT * 8 * MT * sizeof(float);
+    constexpr int ROWS = RT == 0 ? 8 : 16 * RT;
+    size_t smem = (size_t)WARPS * ROWS * 8 * MT * sizeof(float);
+    if (LN && c.K <= 1024) smem += (size_t)c.M * (c.K + 8) * sizeof(__nv_bfloat16);   // the normed rows
     auto kern = linear_smallm_kernel<MT, RT, TO, LN, KVW>;
     if (smem > 48 * 1024) {
-        static bool set = false;                   // per instantiation
-        if (!set) {
+        static size_t set = 0;                     // per instantiation: the largest size asked for so far
+        if (smem > set) {
             MLLM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            set = true;
+            set = smem;
         }
     }
-    const int grid = (c.N + 16 * RT - 1) / (16 * RT);
+    const int grid = (c.N + ROWS - 1) / ROWS;
     MLLM_CUDA(mllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, c.stream, true, (const __nv_bfloat16*)c.x, c.ldx,
                           (const __nv_bfloat16*)c.W, c.bias, (TO*)c.out, c.ldo, c.M, c.N, c.K, c.act, c.accumulate,
                           c.ln ? *c.ln : NormArgs{}, c.kv ? *c.kv : KvArgs{}));
@@ -294,6 +324,7 @@ template <int MT, typename TO>
 int pick_rt(int rt, const Call& c) {
     if (rt == 4) return pick_fusion<MT, 4, TO>(c);
     if (rt == 2) return pick_fusion<MT, 2, TO>(c);
+    if (rt == 0) return pick_fusion<MT, 0, TO>(c);
     return pick_fusion<MT, 1, TO>(c);
 }
 
@@ -324,6 +355,7 @@ int dispatch(const Call& c, int out_dtype) {
     int rt = 1;
     if (c.N >= 16 * 4 * 296) rt = 4;
     else if (c.N >= 16 * 2 * 296) rt = 2;
+    else if (c.N < 16 * 100 && c.M <= 16) rt = 0;   // narrow, few rows: 8 weight rows per CTA
     if (out_dtype == MLLM_BF16) return pick_mt<__nv_bfloat16>(rt, c);
     if (out_dtype == MLLM_F32) return pick_mt<float>(rt, c);
     return mllm_fail(1, "linear_smallm: unknown dtype code %d", out_dtype);
