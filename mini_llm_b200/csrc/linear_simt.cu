@@ -102,11 +102,98 @@ linear_simt_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict
     }
 }
 
+// The same product with 128 x 128 tiles and 8 x 8 outputs per thread (as 2 x 2 blocks of 4 x 4),
+// for many rows: four times the arithmetic per byte read from shared memory, and the next K tile
+// is fetched into registers while the current one is multiplied.  Same order of the sum over K.
+constexpr int LBM = 128, LBN = 128, LBK = 16, LTHREADS = 256;
+
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(LTHREADS)
+linear_simt_large_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ W,
+                         const float* __restrict__ bias, TO* out, long long ldo, int M, int N, int K, int act,
+                         int accumulate, int vecA, int vecW) {
+    __shared__ float As[2][LBK][LBM + 4];
+    __shared__ float Ws[2][LBK][LBN + 4];
+    pdl_wait();
+    const int tid = threadIdx.x;
+    const int tx = tid % 16, ty = tid / 16;
+    const int m0 = blockIdx.y * LBM, n0 = blockIdx.x * LBN;
+    const int lrow = tid / 2, lk = (tid % 2) * 8;       // 128 rows x 16 k: 8 consecutive k per thread
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    float a0[4], a1[4], w0[4], w1[4];
+    auto fetch = [&](int k0) {
+        load4<TA>(A, lda, m0 + lrow, M, k0 + lk, K, vecA != 0, a0);
+        load4<TA>(A, lda, m0 + lrow, M, k0 + lk + 4, K, vecA != 0, a1);
+        load4<TW>(W, (long long)K, n0 + lrow, N, k0 + lk, K, vecW != 0, w0);
+        load4<TW>(W, (long long)K, n0 + lrow, N, k0 + lk + 4, K, vecW != 0, w1);
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            As[buf][lk + i][lrow] = a0[i];
+            As[buf][lk + 4 + i][lrow] = a1[i];
+            Ws[buf][lk + i][lrow] = w0[i];
+            Ws[buf][lk + 4 + i][lrow] = w1[i];
+        }
+    };
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    int buf = 0;
+    for (int k0 = 0; k0 < K; k0 += LBK) {
+        const bool more = k0 + LBK < K;
+        if (more) fetch(k0 + LBK);
+#pragma unroll
+        for (int k = 0; k < LBK; ++k) {
+            const float4 al = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
+            const float4 ah = *reinterpret_cast<const float4*>(&As[buf][k][64 + ty * 4]);
+            const float4 wl = *reinterpret_cast<const float4*>(&Ws[buf][k][tx * 4]);
+            const float4 wh = *reinterpret_cast<const float4*>(&Ws[buf][k][64 + tx * 4]);
+            const float ar[8] = {al.x, al.y, al.z, al.w, ah.x, ah.y, ah.z, ah.w};
+            const float wr[8] = {wl.x, wl.y, wl.z, wl.w, wh.x, wh.y, wh.z, wh.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(ar[i], wr[j], acc[i][j]);
+        }
+        if (more) stash(buf ^ 1);
+        __syncthreads();
+        buf ^= 1;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (bias) v += bias[n];
+            v = apply_act(v, act);
+            TO* o = out + (size_t)m * ldo + n;
+            if (accumulate) v += to_f32(*o);
+            *o = from_f32<TO>(v);
+        }
+    }
+}
+
 template <typename TA, typename TW, typename TO>
 int launch(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo, int M, int N,
            int K, int act, int accumulate, cudaStream_t stream) {
     const bool vecA = ((uintptr_t)A % (4 * sizeof(TA)) == 0) && (lda % 4 == 0);
     const bool vecW = ((uintptr_t)W % (4 * sizeof(TW)) == 0) && (K % 4 == 0);
+    if (M > 128 && N >= 128 && (M + LBM - 1) / LBM <= 65535) {
+        dim3 lgrid((N + LBN - 1) / LBN, (M + LBM - 1) / LBM);
+        linear_simt_large_kernel<TA, TW, TO><<<lgrid, LTHREADS, 0, stream>>>(
+            (const TA*)A, lda, (const TW*)W, bias, (TO*)out, ldo, M, N, K, act, accumulate, vecA, vecW);
+        MLLM_CHECK_LAUNCH("linear_simt_large");
+        return 0;
+    }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     linear_simt_kernel<TA, TW, TO><<<grid, THREADS, 0, stream>>>(
         (const TA*)A, lda, (const TW*)W, bias, (TO*)out, ldo, M, N, K, act, accumulate, vecA, vecW);

@@ -17,6 +17,7 @@ from .csrc import build as _build
 
 F32, BF16 = 0, 1
 SMALL_M = 64                 # rows up to which the weight-streaming product is used
+SMALL_M_F32 = 16             # the same for the float32 weight-streaming product
 DECODE_SPLIT = 128           # keys per split of the decode attention (csrc/attention_decode.cu)
 _FLASH_HEAD_DIMS = (16, 32, 64, 128)
 _DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16, 32, 64, 128)}
@@ -49,6 +50,8 @@ def _signatures(lib):
         "mllm_linear_smallm_fused": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int,
                                      c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_linear_smallm_f32": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
+                                   c_void_p],
         "mllm_linear_tcgen05": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p],
         "mllm_tcgen05_error": [c_void_p],
@@ -332,6 +335,14 @@ def linear(x, weight, bias, out, act: Optional[str] = None, accumulate: bool = F
         if x.dtype == torch.bfloat16 and K % 8 == 0 and lda % 8 == 0 \
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
             impl = "smallm" if M <= SMALL_M else "tcgen05"
+        elif x.dtype == torch.float32 and out.dtype == torch.float32 and M <= SMALL_M_F32 and K % 4 == 0 \
+                and lda % 4 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
+            impl = "smallm_f32"
+    if impl == "smallm_f32":
+        _call("mllm_linear_smallm_f32", x.data_ptr(), lda, weight.data_ptr(),
+              bias.data_ptr() if bias is not None else None, out.data_ptr(), ldo, M, N, K, _ACT[act],
+              int(accumulate), _stream())
+        return out
     if impl in ("smallm", "tcgen05"):
         _call("mllm_linear_" + impl, x.data_ptr(), lda, weight.data_ptr(),
               bias.data_ptr() if bias is not None else None, out.data_ptr(), ldo, M, N, K, _ACT[act],

@@ -55,7 +55,8 @@ def test_layernorm(ops, out_dtype, R, D, eps):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("M,N,K", [(1, 50, 33), (67, 79, 37), (130, 200, 96), (5, 1003, 768), (64, 64, 16)])
+@pytest.mark.parametrize("M,N,K", [(1, 50, 33), (67, 79, 37), (130, 200, 96), (5, 1003, 768), (64, 64, 16),
+                                   (300, 260, 72), (2048, 768, 96), (257, 1003, 40)])
 def test_linear_and_epilogues(ops, dtype, M, N, K):
     x, w, b = rnd(M, K, seed=7, dtype=dtype), rnd(N, K, seed=8, scale=K ** -0.5, dtype=dtype), rnd(N, seed=9)
     ref = x.double() @ w.double().t()
@@ -231,13 +232,43 @@ def test_linear_small_m_rows_do_not_depend_on_the_batch(ops):
         assert torch.equal(part, full[lo:hi])
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 768, 768), (8, 2304, 768), (3, 50, 40), (16, 1003, 96), (5, 320, 3072), (13, 50257, 64)])
+def test_linear_small_m_float32(ops, M, N, K):
+    """The 32-bit weight-streaming product beside the plain kernel and float64."""
+    x, w, b = rnd(M, K, seed=1), rnd(N, K, seed=2, scale=K ** -0.5), rnd(N, seed=3)
+    ref = x.double() @ w.double().t() + b.double()
+    for act in (None, "gelu_tanh", "gelu_erf"):
+        out = torch.full((M, N), 7.0, device=DEV)
+        ops.linear(x, w, b, out=out, act=act, impl="smallm_f32")
+        want = ref if act is None else torch.nn.functional.gelu(ref, approximate="tanh" if act == "gelu_tanh" else "none")
+        assert (out.double() - want).abs().max() < 2e-5 * max(1.0, want.abs().max().item())
+    acc = rnd(M, N, seed=4)
+    acc0 = acc.clone()
+    wide = rnd(M, K + 8, seed=5)
+    ops.linear(wide[:, 4:4 + K], w, None, out=acc, accumulate=True, impl="smallm_f32")
+    assert (acc.double() - (acc0.double() + wide[:, 4:4 + K].double() @ w.double().t())).abs().max() < 1e-4
+    full = torch.empty(M, N, device=DEV)
+    ops.linear(x, w, None, out=full, impl="smallm_f32")
+    one = torch.empty(1, N, device=DEV)
+    ops.linear(x[M - 1:M], w, None, out=one, impl="smallm_f32")
+    assert torch.equal(one, full[M - 1:M])                     # a row does not depend on the batch
+
+
 def test_linear_rows_do_not_depend_on_the_batch(ops):
     x, w = rnd(200, 96, seed=1), rnd(130, 96, seed=2)
     full = torch.empty(200, 130, device=DEV)
-    ops.linear(x, w, None, out=full)
+    ops.linear(x, w, None, out=full, impl="simt")
     for lo, hi in ((0, 1), (63, 65), (199, 200), (17, 150)):
         part = torch.empty(hi - lo, 130, device=DEV)
-        ops.linear(x[lo:hi], w, None, out=part)
+        ops.linear(x[lo:hi], w, None, out=part, impl="simt")
+        assert torch.equal(part, full[lo:hi])
+    # the wide tiles used for many rows: same property
+    x, w = rnd(700, 96, seed=3), rnd(260, 96, seed=4)
+    full = torch.empty(700, 260, device=DEV)
+    ops.linear(x, w, None, out=full, impl="simt")
+    for lo, hi in ((0, 300), (129, 640), (400, 700)):
+        part = torch.empty(hi - lo, 260, device=DEV)
+        ops.linear(x[lo:hi], w, None, out=part, impl="simt")
         assert torch.equal(part, full[lo:hi])
 
 
