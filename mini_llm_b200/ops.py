@@ -60,6 +60,8 @@ def _signatures(lib):
                                   c_int, c_int, c_int, c_int, c_void_p],
         "mllm_attention_flash": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                  c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "mllm_attention_tiled": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                 c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "mllm_argmax": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
         "mllm_argmax_sliced": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mllm_sample": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -403,6 +405,14 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
         elif q.dtype == torch.bfloat16 and head_dim in _FLASH_HEAD_DIMS and getattr(ctx, "n_tiles", 0) > 0 \
                 and ldq % 8 == 0 and q.data_ptr() % 16 == 0 and ldo % 2 == 0:
             impl = "flash"
+        elif getattr(ctx, "n_tiles", 0) > 0:
+            impl = "tiled"          # float32, or a head size the tensor-core kernel does not take
+    if impl == "tiled":
+        _call("mllm_attention_tiled", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(),
+              block_table.data_ptr(), bt_stride, ctx.attn_tiles.data_ptr(), int(ctx.n_tiles),
+              ctx.positions.data_ptr(), out.data_ptr(), ldo, num_heads, num_kv_heads, head_dim, ps, float(scale),
+              int(window or 0), _dt(q), _stream())
+        return
     if impl == "flash":
         if q.dtype != torch.bfloat16 or head_dim not in _FLASH_HEAD_DIMS:
             raise KernelError(f"paged_attention: the tensor-core kernel takes bfloat16 and head sizes "

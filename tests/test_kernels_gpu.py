@@ -437,6 +437,54 @@ def test_flash_attention_mixed_batch(ops, H, Hkv, dh, page, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,dh,page,window", [(4, 4, 16, 16, None), (3, 3, 32, 8, None), (12, 12, 64, 16, None),
+                                                  (5, 1, 48, 4, None), (2, 2, 128, 32, 100), (2, 1, 256, 16, None),
+                                                  (4, 2, 80, 16, 37)])
+def test_tiled_attention_mixed_batch(ops, dtype, H, Hkv, dh, page, window):
+    """The CUDA-core tiled kernel (the 32-bit path's prefill attention, and head sizes such as 48 or
+    80 on either path): prompt portions of many lengths beside single tokens, against float64 and
+    the plain kernel; the same queries cut differently give the same bits."""
+    from mini_llm_b200.engine.context import attention_tiles
+    seqs = [(1, 1), (70, 1), (33, 33), (100, 7), (16, 2), (129, 129), (64, 64), (65, 65), (200, 63), (300, 130),
+            (128, 64), (191, 2)]
+    case = _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages=1400 // page + 40, seed=H + dh + page)
+    ctx = _ctx_for(case)
+    ctx.decode_only = False
+    tiles = attention_tiles([ql for _, ql in seqs])
+    ctx.attn_tiles, ctx.n_tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV), len(tiles) // 3
+    q = case["q"].to(dtype).to(DEV)
+    kp, vp, bt = case["k_pages"].to(dtype).to(DEV), case["v_pages"].to(dtype).to(DEV), case["bt"].to(DEV)
+    scale = dh ** -0.5
+    kw = dict(num_heads=H, num_kv_heads=Hkv, head_dim=dh, scale=scale, window=window)
+    out, plain = torch.empty_like(q), torch.empty_like(q)
+    ops.paged_attention(q, kp, vp, bt, ctx, out, impl="tiled", **kw)
+    ops.paged_attention(q, kp, vp, bt, ctx, plain, impl="simt", **kw)
+    want = _attention_reference(case, H, Hkv, dh, scale, window, dtype)
+    mag = want.abs().clamp(min=1.0)
+    tol = 2e-5 if dtype == torch.float32 else 2 ** -8
+    assert ((out.double().cpu() - want).abs() / mag).max() < tol
+    assert ((out.double() - plain.double()).abs().cpu() / mag).max() < (2e-5 if dtype == torch.float32 else 2 ** -7 * 1.05)
+    c2 = _paged_case(dtype, [(129, 129)], H, Hkv, dh, page, num_pages=1400 // page + 40, seed=99)
+    ctxa = _ctx_for(c2)
+    ctxa.decode_only = False
+    ta = attention_tiles([129])
+    ctxa.attn_tiles, ctxa.n_tiles = torch.tensor(ta, dtype=torch.int32, device=DEV), len(ta) // 3
+    q2 = c2["q"].to(dtype).to(DEV)
+    args2 = (c2["k_pages"].to(dtype).to(DEV), c2["v_pages"].to(dtype).to(DEV), c2["bt"].to(DEV))
+    whole = torch.empty_like(q2)
+    ops.paged_attention(q2, *args2, ctxa, whole, impl="tiled", **kw)
+    for lo, hi in ((0, 5), (5, 70), (70, 129), (100, 101)):
+        cb = _Ctx()
+        cb.token_seq = torch.zeros(hi - lo, dtype=torch.int32, device=DEV)
+        cb.positions = torch.arange(lo, hi, dtype=torch.int32, device=DEV)
+        tb = attention_tiles([hi - lo])
+        cb.attn_tiles, cb.n_tiles, cb.decode_only = torch.tensor(tb, dtype=torch.int32, device=DEV), len(tb) // 3, False
+        part = torch.empty_like(q2[lo:hi])
+        ops.paged_attention(q2[lo:hi], *args2, cb, part, impl="tiled", **kw)
+        assert torch.equal(part, whole[lo:hi]), (lo, hi)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_paged_attention_finds_one_far_key_among_hundreds(ops, dtype):
     """Random keys give near-uniform weights that would hide a skipped key; here one key
     far back carries almost all the weight, once at a page's first slot, once at its last."""
