@@ -86,6 +86,7 @@ class ModelRunner:
         # CUDA graphs of decode-only steps, by the step's shape
         self._graphs: Dict[tuple, object] = {}
         self._graph_seen: Dict[tuple, int] = {}
+        self._graph_families = set()
         self._graph_version = -1
         self.graph_replays = 0
         self.graph_kernels: Dict[tuple, int] = {}
@@ -224,7 +225,7 @@ class ModelRunner:
         max_pages = []
         for g in range(ng):
             mp = max(len(t) for t in tables[g])
-            max_pages.append(max(16, (mp + 15) // 16 * 16))    # wide steps: few distinct shapes for captured graphs
+            max_pages.append(max(16, 1 << (mp - 1).bit_length()))   # powers of two: few distinct shapes for captured graphs
         tiles = [] if T == S else attention_tiles(q_lens)
         layout = StepLayout.make(T, S, len(logit_rows), max_pages, len(tiles) // 3)
         i, host = self._staging(layout.total)
@@ -274,8 +275,9 @@ class ModelRunner:
         if self._graph_version != self.ws.version:
             self._graphs.clear()
             self._graph_seen.clear()
+            self._graph_families.clear()
             self._graph_version = self.ws.version
-        key = (ctx.layout.key(), -(-ctx.max_ctx_len // ops.DECODE_SPLIT) if ctx.decode_only else 0)
+        key = (ctx.layout.key(), ops.decode_splits(ctx.max_ctx_len) if ctx.decode_only else 0)
         g = self._graphs.get(key)
         if g is not None:
             g[0].replay()
@@ -286,7 +288,10 @@ class ModelRunner:
         if len(self._graph_seen) > 4096:
             self._graph_seen.clear()
         self._graph_seen[key] = seen + 1
-        if seen == 0:
+        # A shape that differs from a captured one only in the width of the block tables or the number of
+        # key splits (a context that grew) needs no new buffers: capture it at first sight.
+        family = key[0][:3] + key[0][4:]
+        if seen == 0 and family not in self._graph_families:
             with ops.stream_scope():
                 return self.model.forward(ctx)         # first time: eager, buffers get allocated
         version = self.ws.version
@@ -306,6 +311,7 @@ class ModelRunner:
             self._graphs.pop(old)
             self.graph_kernels.pop(old, None)
         self._graphs[key] = (graph, logits)
+        self._graph_families.add(family)
         self.graph_kernels[key] = kernels
         ops.launches = n0 + kernels
         graph.replay()

@@ -227,6 +227,12 @@ class NormedInput:
         return self._out
 
 
+def decode_splits(max_ctx_len: int) -> int:
+    """Key splits the decode attention is launched with: just enough for the longest context
+    (launching more costs: the splits of a request form a cluster that is scheduled as a whole)."""
+    return max(1, -(-int(max_ctx_len) // DECODE_SPLIT))
+
+
 def _fusable(weight, M, K) -> bool:
     return weight.dtype == torch.bfloat16 and M <= SMALL_M and K % 8 == 0 and weight.data_ptr() % 16 == 0
 
@@ -427,7 +433,7 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
             raise KernelError(f"paged_attention: the split-key kernel takes head sizes {_DECODE_HEAD_DIMS[q.dtype]} "
                               f"for {q.dtype}, not {head_dim}")
         # splits cover the longest context of the step, rounded up so that captured graphs keep their grid
-        max_splits = max(1, -(-int(ctx.max_ctx_len) // DECODE_SPLIT))
+        max_splits = decode_splits(ctx.max_ctx_len)
         part_o = ctx.ws.buf("attn_part_o", T * num_heads * max_splits, head_dim, torch.float32)
         part_ml = ctx.ws.buf("attn_part_ml", T * num_heads * max_splits, 2, torch.float32)
         counters = ctx.ws.zeroed("attn_counters", T * num_heads)     # the kernel leaves them zero

@@ -52,7 +52,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one(dtype, dcode):
     stream = torch.cuda.current_stream().cuda_stream
     for call, (seed, T) in enumerate([(1, 8), (2, 5)]):         # two calls in a row
         q, kp, vpg, bt, token_seq, positions, max_ctx = _case(seed, T, H, dh, page, dtype)
-        max_splits = -(-max_ctx // ops.DECODE_SPLIT)
+        max_splits = ops.decode_splits(max_ctx)
         got = torch.empty_like(q)
         rc = fn(q.data_ptr(), q.stride(0), kp.data_ptr(), vpg.data_ptr(), bt.data_ptr(), bt.stride(0),
                 token_seq.data_ptr(), positions.data_ptr(), got.data_ptr(), got.stride(0), T, H, H, dh, page,
