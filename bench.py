@@ -281,6 +281,58 @@ def profile_step(kind: str, dtype: str, layers: int, batch: int) -> int:
     return 0
 
 
+MEDIUM = dict(SMALL, n_layer=24, n_embd=1024, n_head=16, n_inner=4096)
+XL = dict(SMALL, n_layer=48, n_embd=1600, n_head=25, n_inner=6400)
+
+
+def run_workload(kind: str, dtype: str, layers: int) -> int:
+    """The two serving workloads of the larger GPT-2 sizes, through the Python entry point.
+
+    medium: 64 requests, prompt lengths uniform in [32, 1024), output lengths uniform in [16, 256),
+            continuous batching with prompts cut into portions of 512 tokens.
+    xl:     64 requests with 128-token prompts generating 896 tokens each; the cache pool holds 24
+            full contexts, so admission defers requests and running ones are preempted by recompute.
+    Prints one JSON line with tokens per second and the scheduler's counters."""
+    import torch
+    import mini_llm_b200 as m
+
+    cfg = dict(MEDIUM if kind == "medium" else XL)
+    full_layers = cfg["n_layer"]
+    if layers and layers < full_layers:
+        cfg["n_layer"] = layers
+    g = torch.Generator().manual_seed(2024)
+    n = cfg["n_positions"]
+    if kind == "medium":
+        plens = torch.randint(32, 1024, (64,), generator=g).tolist()
+        olens = [min(o, n - p + 1) for p, o in zip(plens, torch.randint(16, 256, (64,), generator=g).tolist())]
+        eng = dict(max_tokens=64 * n, max_num_seqs=64, max_num_batched_tokens=1024, prefill_chunk=512)
+    else:
+        plens, olens = [128] * 64, [896] * 64
+        eng = dict(max_tokens=24 * n, max_num_seqs=64, max_num_batched_tokens=2048, prefill_chunk=512)
+    prompts = [torch.randint(0, cfg["vocab_size"], (p,), generator=g).tolist() for p in plens]
+    with tempfile.TemporaryDirectory(prefix="mini_llm_work_") as d:
+        m.write_random_model(cfg, 0, d, dtype=dtype)
+        llm = m.LLM(d, dtype=dtype, page_size=PAGE, **eng)
+        params = [m.SamplingParams(max_new_tokens=o, ignore_eos=True) for o in olens]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs = llm.generate(prompts, params)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        st = llm.scheduler.stats
+        assert [len(o) for o in outs] == olens, "a request produced the wrong number of tokens"
+        llm.runner.cache.check()
+        print(json.dumps({"workload": kind, "dtype": dtype, "n_layer": cfg["n_layer"], "n_layer_full": full_layers,
+                          "n_embd": cfg["n_embd"], "n_head": cfg["n_head"], "requests": 64,
+                          "prompt_tokens": sum(plens), "output_tokens": sum(olens), "seconds": round(dt, 3),
+                          "output_tok_s": round(sum(olens) / dt, 1), "total_tok_s": round((sum(plens) + sum(olens)) / dt, 1),
+                          "steps": st.steps, "deferred_decode": st.deferred_decode,
+                          "deferred_prefill": st.deferred_prefill, "preempted": st.preempted,
+                          "peak_pages": st.peak_pages, "num_pages": llm.runner.num_pages,
+                          "graph_replays": llm.runner.graph_replays}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -293,9 +345,13 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--profile-step", choices=["prefill", "decode"],
                     help="run one small eager step for a profiler instead of the benchmark")
+    ap.add_argument("--workload", choices=["medium", "xl"],
+                    help="run a continuous-batching workload of GPT-2 medium or XL instead of the benchmark")
     args = ap.parse_args()
     if args.profile_step:
         return profile_step(args.profile_step, args.dtype, args.layers, args.batch)
+    if args.workload:
+        return run_workload(args.workload, args.dtype, args.layers if args.layers != SMALL["n_layer"] else 0)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "taejuk/mini-llm is a CMake C++/CUDA project with no setup.py or pyproject.toml: "
