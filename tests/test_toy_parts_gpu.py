@@ -175,3 +175,118 @@ def test_toy_architecture_with_a_state_mixer(tmp_path):
         assert (torch.cat(got[r]) - want[r]).abs().max() < 2e-4 * want[r].abs().max(), r
     runner.cache.check()
     assert runner.cache.num_live == 0
+
+
+def _register_window():
+    import mini_llm_b200 as m
+    from mini_llm_b200.config.base import ModelConfig
+    from mini_llm_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, WeightRef
+
+    @dataclass
+    class WinConfig(ModelConfig):
+        hidden: int = 0
+        vocab: int = 0
+        heads: int = 0
+        kv_heads: int = 0
+        window: int = 0
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(hidden=d["hidden"], vocab=d["vocab"], heads=d["heads"], kv_heads=d["kv_heads"], window=d["window"])
+
+        def to_dict(self):
+            return dict(architectures=["ToyWindowLM"], hidden=self.hidden, vocab=self.vocab, heads=self.heads,
+                        kv_heads=self.kv_heads, window=self.window)
+
+    def build(cfg):
+        D, H, Hkv = cfg.hidden, cfg.heads, cfg.kv_heads
+        dh = D // H
+
+        def norm(name):
+            return PartSpec("layernorm", dict(hidden_size=D, eps=1e-5),
+                            {"weight": WeightRef((name + ".g",), init=("ones",)), "bias": WeightRef((name + ".b",), init=("zeros",))})
+
+        def layer(i, window, kvh):
+            att = PartSpec("attention", dict(hidden_size=D, num_heads=H, num_kv_heads=kvh, head_dim=dh, scale=dh ** -0.5,
+                                             window=window, bias=True),
+                           {"qkv_weight": WeightRef((f"l{i}.qkv",), init=("normal", 0.4)),
+                            "qkv_bias": WeightRef((f"l{i}.qkv_b",), init=("normal", 0.1)),
+                            "out_weight": WeightRef((f"l{i}.o",), init=("normal", 0.3)),
+                            "out_bias": WeightRef((f"l{i}.o_b",), init=("normal", 0.1))})
+            ff = PartSpec("mlp", dict(hidden_size=D, inner_size=2 * D, activation="gelu_tanh", bias=True),
+                          {"fc_weight": WeightRef((f"l{i}.up",), init=("normal", 0.2)), "fc_bias": WeightRef((f"l{i}.up_b",), init=("zeros",)),
+                           "proj_weight": WeightRef((f"l{i}.down",), init=("normal", 0.2)), "proj_bias": WeightRef((f"l{i}.down_b",), init=("zeros",))})
+            return LayerSpec(mixer=att, ff=ff, mixer_norm=norm(f"l{i}.n1"), ff_norm=norm(f"l{i}.n2"))
+
+        # layer 0: a window of `window` keys and grouped key/value heads; layer 1: all keys, one k/v head per head
+        return ModelSpec(hidden_size=D, vocab_size=cfg.vocab,
+                         embedding=PartSpec("token", dict(hidden_size=D, vocab_size=cfg.vocab), {"table": WeightRef(("emb",), init=("normal", 1.0))}),
+                         positions=PartSpec("learned", dict(hidden_size=D, max_positions=512), {"table": WeightRef(("pos",), init=("normal", 0.5))}),
+                         layers=[layer(0, cfg.window, Hkv), layer(1, None, H)], final_norm=norm("nf"),
+                         head=PartSpec("tied", dict(hidden_size=D, vocab_size=cfg.vocab)), max_positions=512)
+
+    m.register_architecture("ToyWindowLM", WinConfig, build, replace=True)
+    return dict(architectures=["ToyWindowLM"], hidden=64, vocab=120, heads=4, kv_heads=2, window=20)
+
+
+def _window_reference(folder, ids, store=lambda t: t):
+    """Whole-sequence float64 statement; ``store`` rounds the values an engine keeps in bfloat16
+    between kernels (normed rows, Q|K|V, attention output, the MLP's hidden row)."""
+    from safetensors.torch import load_file
+    w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    cfg = json.load(open(os.path.join(folder, "config.json")))
+    D, H, T = cfg["hidden"], cfg["heads"], len(ids)
+    dh = D // H
+
+    def ln(x, n):
+        return torch.nn.functional.layer_norm(x, (D,), w[n + ".g"], w[n + ".b"], 1e-5)
+
+    x = w["emb"][torch.tensor(ids)] + w["pos"][:T]
+    idx = torch.arange(T)
+    for i, (window, kvh) in enumerate(((cfg["window"], cfg["kv_heads"]), (None, H))):
+        qkv = store(store(ln(x, f"l{i}.n1")) @ w[f"l{i}.qkv"].t() + w[f"l{i}.qkv_b"])
+        q, k, v = qkv[:, :D], qkv[:, D:D + kvh * dh], qkv[:, D + kvh * dh:]
+        vis = idx[None, :] <= idx[:, None]
+        if window:
+            vis &= idx[None, :] > idx[:, None] - window
+        att = torch.zeros(T, D, dtype=torch.float64)
+        for hh in range(H):
+            hk = hh // (H // kvh)
+            s = (q[:, hh * dh:(hh + 1) * dh] @ k[:, hk * dh:(hk + 1) * dh].t()) * dh ** -0.5
+            att[:, hh * dh:(hh + 1) * dh] = torch.softmax(s.masked_fill(~vis, float("-inf")), -1) @ v[:, hk * dh:(hk + 1) * dh]
+        x = x + store(att) @ w[f"l{i}.o"].t() + w[f"l{i}.o_b"]
+        h = store(torch.nn.functional.gelu(store(ln(x, f"l{i}.n2")) @ w[f"l{i}.up"].t() + w[f"l{i}.up_b"], approximate="tanh"))
+        x = x + h @ w[f"l{i}.down"].t() + w[f"l{i}.down_b"]
+    return store(ln(x, "nf")) @ w["emb"].t()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_a_window_and_grouped_heads(tmp_path, dtype):
+    """Two cache groups in one model: a layer with a 20-key window and 2 key/value heads beside a
+    layer that sees everything.  Whole, in portions and token by token; the windowed group gives
+    pages back while the request runs, and the logits stay right."""
+    import mini_llm_b200 as m
+    from mini_llm_b200.config.base import EngineConfig
+    from mini_llm_b200.engine.runner import ModelRunner, StepEntry
+
+    cfg = _register_window()
+    folder = m.write_random_model(cfg, 5, str(tmp_path / "win"), dtype=dtype)
+    runner = ModelRunner(folder, EngineConfig(dtype=dtype, page_size=8, num_pages=40, max_num_seqs=2))
+    assert len(runner.cache.groups) == 2
+    windowed = next(g for g in runner.cache.groups if g.need.window == 20)
+    assert windowed.need.kv_heads == 2
+    from helpers import assert_close, oracle_store
+    ids = torch.randint(0, cfg["vocab"], (150,), generator=torch.Generator().manual_seed(3)).tolist()
+    want = _window_reference(folder, ids, oracle_store(dtype))
+    for plan in ([150], [70, 1, 1, 1, 40, 37], [3] + [1] * 40 + [107]):
+        runner.add_request("r")
+        got, pos = [], 0
+        for n in plan:
+            got.append(runner.step([StepEntry("r", ids[pos:pos + n], list(range(n)))]).double().cpu())
+            pos += n
+            held = sum(p >= 0 for p in runner.cache.table("r", windowed.index))
+            assert held <= (20 + 8 - 2) // 8 + 2 + (n + 7) // 8       # only the window's pages (and this step's) are kept
+        assert_close(torch.cat(got).numpy(), want.numpy(), dtype, f"window model, portions {plan[:3]}")
+        runner.finish_request("r")
+    runner.cache.check()
+    assert all(g.allocator.num_free == 40 for g in runner.cache.groups)
