@@ -52,6 +52,7 @@ class EngineConfig:
     memory_fraction: float = 0.5       # of free device memory, when sizes are not given
     use_cuda_graphs: bool = True
     use_pdl: bool = True               # programmatic dependent launch between the kernels of a step
+    async_scheduling: bool = True      # while only decodes run, launch a step before the last one's tokens are read
     device: str = "cuda:0"
 
     def __post_init__(self):

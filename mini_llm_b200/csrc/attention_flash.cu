@@ -8,9 +8,11 @@
 // end, which halves the walk of the longest rows.  Keys and values come from the
 // request's pages: tile j always covers the absolute positions [64j, 64j+64) and belongs
 // to group j mod 2, so the order of the additions for a query does not depend on how the
-// prompt was cut or what else is in the batch.  Heavy tiles (late positions) are launched
-// first.  K and V tiles are brought in
-// with cp.async (16-byte pieces, two stages), S = Q.K^T and O += P.V run on
+// prompt was cut or what else is in the batch.  The host lists heavy tiles (late positions)
+// first; heads are the fast grid dimension.  The two groups run on barriers of their own.
+// K and V tiles are brought in with cp.async (16-byte pieces, two stages; the page numbers
+// of a tile are fetched one round before its loads are issued, so no warp waits on the
+// block table), S = Q.K^T and O += P.V run on
 // mma.sync.m16n8k16 (bf16 in, 32-bit accumulate); the recurrence
 // m' = max(m, s), alpha = exp(m - m'), p = exp(s - m'), o = o*alpha + p*v, l = l*alpha + p
 // and the final o/l are the reference's (src/kernels/prefill/flashattention.cu:129-168),
@@ -46,6 +48,9 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void group_barrier(int group) {         // the 4 warps of one group
+    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(WARPS * 32) : "memory");
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -66,7 +71,7 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     __nv_bfloat16* sK = sQ + BQ * ROW + group * (4 * BKV * ROW);      // this group's [2][BKV][ROW]
     __nv_bfloat16* sV = sK + 2 * BKV * ROW;                           // and its [2][BKV][ROW]
 
-    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;      // late (long) tiles first
+    const int tile = blockIdx.y, h = blockIdx.x;
     pdl_wait();
     pdl_launch();
     const int seq = tiles[tile * 3], tok0 = tiles[tile * 3 + 1], rows = tiles[tile * 3 + 2];
@@ -82,7 +87,6 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     const int j_first = first_key / BKV, j_hi = pos_max / BKV;
     // this group's tiles: j = j_lo, j_lo + 2, ... with j mod 2 == group
     const int j_lo = j_first + ((j_first & 1) != group ? 1 : 0);
-    const int rounds = (j_hi - j_first) / 2 + 1;                        // both groups take part in every round
 
     // Q tile -> shared memory (rows beyond the tile are zeros)
     for (int i = threadIdx.x; i < BQ * CH; i += GROUPS * WARPS * 32) {
@@ -90,24 +94,38 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
         cp_async16(sQ + r * ROW + c * 8, q + (size_t)(tok0 + (r < rows ? r : 0)) * q_stride + (size_t)h * DH + c * 8,
                    r < rows);
     }
-    auto load_kv = [&](int j, int stage) {
+    cp_commit();
+    // a thread moves the same pieces of every tile: piece i = gtid + it * 128 of BKV * CH
+    constexpr int ITER = (BKV * CH + WARPS * 32 - 1) / (WARPS * 32);
+    int pg[ITER];                                        // page of each piece's key, -1: not visible to any row
+    auto fetch_pages = [&](int j) {
+#pragma unroll
+        for (int it = 0; it < ITER; ++it) {
+            const int i = gtid + it * WARPS * 32;
+            const int kp = j * BKV + i / CH;
+            const bool ok = i < BKV * CH && j <= j_hi && kp <= pos_max && kp >= first_key;
+            pg[it] = ok ? bt[kp / page_size] : -1;
+        }
+    };
+    auto load_kv = [&](int j, int stage) {               // with the pages that fetch_pages(j) brought
         __nv_bfloat16* dK = sK + stage * BKV * ROW;
         __nv_bfloat16* dV = sV + stage * BKV * ROW;
-        for (int i = gtid; i < BKV * CH; i += WARPS * 32) {
+#pragma unroll
+        for (int it = 0; it < ITER; ++it) {
+            const int i = gtid + it * WARPS * 32;
+            if (i >= BKV * CH) break;
             const int r = i / CH, c = i % CH;
             const int kp = j * BKV + r;
-            const bool ok = kp <= pos_max && kp >= first_key;
-            size_t off = 0;
-            if (ok) {
-                const int page = bt[kp / page_size];
-                off = (((size_t)page * Hkv + hk) * page_size + kp % page_size) * DH + c * 8;
-            }
+            const bool ok = pg[it] >= 0;
+            const size_t off = ok ? (((size_t)pg[it] * Hkv + hk) * page_size + kp % page_size) * DH + c * 8 : 0;
             cp_async16(dK + r * ROW + c * 8, k_pages + off, ok);
             cp_async16(dV + r * ROW + c * 8, v_pages + off, ok);
         }
     };
+    fetch_pages(j_lo);
     if (j_lo <= j_hi) load_kv(j_lo, 0);
     cp_commit();
+    fetch_pages(j_lo + 2);
 
     float o[DH / 8][4];
 #pragma unroll
@@ -118,20 +136,19 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     const float sl2 = scale * LOG2E;
     uint32_t qa[DH / 16][4];
     const int qrow0 = pos0 + warp * 16 + g;           // absolute position of this thread's first row; second is +8
+    cp_wait<1>();                                      // the queries are in (the first key tile may still fly)
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < DH / 16; ++ks)
+        ldsm_x4(qa[ks], sQ + (warp * 16 + (lane & 15)) * ROW + ks * 16 + (lane >> 4) * 8);
 
-    for (int rd = 0; rd < rounds; ++rd) {
-        const int j = j_lo + 2 * rd;
-        const int stage = rd & 1;
+    int stage = 0;
+    for (int j = j_lo; j <= j_hi; j += 2, stage ^= 1) {
         if (j + 2 <= j_hi) load_kv(j + 2, stage ^ 1);
         cp_commit();
+        fetch_pages(j + 4);                                // used by the next round's loads
         cp_wait<1>();
-        __syncthreads();
-        if (rd == 0) {
-#pragma unroll
-            for (int ks = 0; ks < DH / 16; ++ks)
-                ldsm_x4(qa[ks], sQ + (warp * 16 + (lane & 15)) * ROW + ks * 16 + (lane >> 4) * 8);
-        }
-        if (j > j_hi) { __syncthreads(); continue; }          // this group has no tile in the last round
+        group_barrier(group);
         const __nv_bfloat16* tK = sK + stage * BKV * ROW;
         const __nv_bfloat16* tV = sV + stage * BKV * ROW;
         // S = Q K^T : 16 rows x 64 keys per warp
@@ -209,17 +226,24 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
         // O += P V
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
+            // all value fragments of these 16 keys first, then the hi products of every output tile, then the lo
+            // ones: consecutive MMAs never wait on each other's accumulator
+            uint32_t b[DH / 16][4];
+#pragma unroll
+            for (int dp = 0; dp < DH / 16; ++dp)
+                ldsm_x4_trans(b[dp], tV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ROW + dp * 16 + (lane >> 4) * 8);
 #pragma unroll
             for (int dp = 0; dp < DH / 16; ++dp) {
-                uint32_t b[4];
-                ldsm_x4_trans(b, tV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ROW + dp * 16 + (lane >> 4) * 8);
-                mma16816(o[2 * dp], pa[kk], b[0], b[1]);
-                mma16816(o[2 * dp + 1], pa[kk], b[2], b[3]);
-                mma16816(o[2 * dp], pb[kk], b[0], b[1]);
-                mma16816(o[2 * dp + 1], pb[kk], b[2], b[3]);
+                mma16816(o[2 * dp], pa[kk], b[dp][0], b[dp][1]);
+                mma16816(o[2 * dp + 1], pa[kk], b[dp][2], b[dp][3]);
+            }
+#pragma unroll
+            for (int dp = 0; dp < DH / 16; ++dp) {
+                mma16816(o[2 * dp], pb[kk], b[dp][0], b[dp][1]);
+                mma16816(o[2 * dp + 1], pb[kk], b[dp][2], b[dp][3]);
             }
         }
-        __syncthreads();                                   // the stage may be overwritten by the next load
+        group_barrier(group);                              // the stage may be overwritten by the next load
     }
     cp_wait<0>();
     // merge the two groups' states: the odd-tile group hands (m, l, o) over through shared memory
@@ -274,7 +298,7 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
         set = true;
     }
     using bf = __nv_bfloat16;
-    MLLM_CUDA(mllm_launch(kern, dim3(n_tiles, H), dim3(GROUPS * WARPS * 32), smem, stream, true, (const bf*)q, q_stride,
+    MLLM_CUDA(mllm_launch(kern, dim3(H, n_tiles), dim3(GROUPS * WARPS * 32), smem, stream, true, (const bf*)q, q_stride,
                           (const bf*)k_pages, (const bf*)v_pages, block_table, bt_stride, tiles, positions, (bf*)out,
                           out_stride, H, Hkv, page_size, scale, window));
     return 0;
@@ -292,7 +316,7 @@ MLLM_EXPORT int mllm_attention_flash(const void* q, long long q_stride, const vo
                                      int page_size, float scale, int window, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (Hkv <= 0 || H % Hkv != 0) return mllm_fail(1, "attention_flash: %d heads over %d key/value heads", H, Hkv);
-    if (H > 65535) return mllm_fail(1, "attention_flash: too many heads for the grid");
+    if (n_tiles > 65535) return mllm_fail(1, "attention_flash: %d query tiles are more than one launch takes", n_tiles);
     if (q_stride % 8 || (uintptr_t)q % 16 || out_stride % 2 || (uintptr_t)out % 4)
         return mllm_fail(1, "attention_flash: queries must be 16-byte aligned, outputs 4-byte aligned");
 #define GO(D) return launch<D>(q, q_stride, k_pages, v_pages, block_table, bt_stride, tiles, n_tiles, positions, out, \

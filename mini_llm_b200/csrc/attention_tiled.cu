@@ -31,7 +31,7 @@ attention_tiled_kernel(const T* __restrict__ q, long long q_stride, const T* __r
     float* Ps = Vs + BK * dh;               // [BQ][BK+1]
     pdl_wait();
     pdl_launch();
-    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;      // late (long) tiles first
+    const int tile = blockIdx.y, h = blockIdx.x;                      // the host lists long tiles first
     const int seq = tiles[tile * 3], tok0 = tiles[tile * 3 + 1], rows = tiles[tile * 3 + 2];
     const int pos0 = positions[tok0], pos_max = pos0 + rows - 1;
     const int hk = h / (H / Hkv);
@@ -191,7 +191,7 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
         MLLM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         set = smem;
     }
-    MLLM_CUDA(mllm_launch(kern, dim3(n_tiles, H), dim3(THREADS), smem, stream, true, (const T*)q, q_stride,
+    MLLM_CUDA(mllm_launch(kern, dim3(H, n_tiles), dim3(THREADS), smem, stream, true, (const T*)q, q_stride,
                           (const T*)k_pages, (const T*)v_pages, block_table, bt_stride, tiles, positions, (T*)out,
                           out_stride, H, Hkv, dh, page_size, scale, window));
     return 0;
@@ -209,7 +209,7 @@ MLLM_EXPORT int mllm_attention_tiled(const void* q, long long q_stride, const vo
     if (dh <= 0 || dh % 16 != 0 || dh > 256)
         return mllm_fail(1, "attention_tiled: head size %d is not a multiple of 16 in 16..256", dh);
     if (Hkv <= 0 || H % Hkv != 0) return mllm_fail(1, "attention_tiled: %d heads over %d key/value heads", H, Hkv);
-    if (H > 65535) return mllm_fail(1, "attention_tiled: too many heads for the grid");
+    if (n_tiles > 65535) return mllm_fail(1, "attention_tiled: %d query tiles are more than one launch takes", n_tiles);
     if (dtype == MLLM_F32)
         return launch<float>(q, q_stride, k_pages, v_pages, block_table, bt_stride, tiles, n_tiles, positions, out,
                              out_stride, H, Hkv, dh, page_size, scale, window, stream);

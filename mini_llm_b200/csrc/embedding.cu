@@ -35,3 +35,23 @@ MLLM_EXPORT int mllm_embed(const int* ids, const int* pos, const void* table, co
     MLLM_CHECK_LAUNCH("embed");
     return 0;
 }
+
+// ids[t] < 0 stands for "the token that the last sampling launch wrote to row -ids[t]-1 of
+// its output": the step that consumes a token can be queued before the host has read it.
+__global__ void resolve_tokens_kernel(int* __restrict__ ids, int T, const int* __restrict__ sampled, int rows) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    const int v = ids[t];
+    if (v < 0) {
+        const int r = -v - 1;
+        ids[t] = r < rows ? sampled[r] : 0;
+    }
+}
+
+MLLM_EXPORT int mllm_resolve_tokens(int* ids, int T, const int* sampled, int rows, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (rows <= 0) return mllm_fail(1, "resolve_tokens: no sampled rows to read from");
+    resolve_tokens_kernel<<<(T + 255) / 256, 256, 0, stream>>>(ids, T, sampled, rows);
+    MLLM_CHECK_LAUNCH("resolve_tokens");
+    return 0;
+}

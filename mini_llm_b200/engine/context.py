@@ -151,15 +151,24 @@ class StepContext:
 ATTN_TILE = 64      # query rows per tile of csrc/attention_flash.cu
 
 
-def attention_tiles(q_lens: Sequence[int]) -> List[int]:
-    """Cut every request's new tokens into tiles of at most ATTN_TILE rows; longest
-    contexts first would balance better, but the order is kept simple and fixed."""
-    out: List[int] = []
+def attention_tiles(q_lens: Sequence[int], q_starts: Optional[Sequence[int]] = None) -> List[int]:
+    """Cut every request's new tokens into tiles of at most ATTN_TILE rows: triples of
+    (request index in the batch, flat index of the tile's first token, rows).  With the
+    positions at which the portions start, the tiles that see the most keys come first,
+    so that the longest walks of the attention kernel start earliest."""
+    tiles = []
     base = 0
     for s, n in enumerate(q_lens):
+        start = 0 if q_starts is None else int(q_starts[s])
         for q0 in range(0, n, ATTN_TILE):
-            out += [s, base + q0, min(ATTN_TILE, n - q0)]
+            rows = min(ATTN_TILE, n - q0)
+            tiles.append((start + q0 + rows, s, base + q0, rows))
         base += n
+    if q_starts is not None:
+        tiles.sort(key=lambda t: -t[0])          # stable: equal lengths keep the batch order
+    out: List[int] = []
+    for _, s, t0, rows in tiles:
+        out += [s, t0, rows]
     return out
 
 

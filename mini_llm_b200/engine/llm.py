@@ -14,7 +14,7 @@ from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .request import Request, Response
 from .runner import ModelRunner, StepEntry
-from .scheduler import Scheduler
+from .scheduler import PENDING, Scheduler
 
 
 class LLM:
@@ -30,6 +30,7 @@ class LLM:
         self.scheduler = Scheduler(self.runner.cache, engine, self.runner.max_positions, self.runner.spec.eos_token_id)
         self.sampler = Sampler(self.runner.device, engine.max_num_seqs)
         self._next_id = 0
+        self._inflight = None          # (advanced step, sampler ticket, request id -> row) of a step whose tokens are not read yet
 
     # ------------------------------------------------------------------ low level
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -44,19 +45,51 @@ class LLM:
         return request_id
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self._inflight is not None
 
     def step(self) -> List[Response]:
-        """Schedule, run and sample one step; returns the tokens it produced."""
+        """Schedule, launch and sample one step; returns the tokens that became known.
+
+        While only decoding requests are running (``Scheduler.can_run_ahead``) the steps
+        overlap: a step is scheduled and launched before the tokens of the one before it
+        have been read back, its input tokens are taken from the sampler's device buffer,
+        and the host work of a step hides behind the GPU work of the step before.  The
+        tokens a call returns are then those of the step launched by the call before.  In
+        every other situation (prompts waiting or running, pages short) the tokens are read
+        first and a call returns the tokens of its own step, as with
+        ``async_scheduling=False``."""
+        out: List[Response] = []
+        ahead = self.engine_config.async_scheduling and self.scheduler.can_run_ahead()
+        if self._inflight is not None and not ahead:
+            out += self._finalize()
         sched = self.scheduler.schedule()
-        if not sched.entries:
-            return []
-        entries = [StepEntry(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.wants_logits else [])
-                   for e in sched.entries]
-        logits = self.runner.step(entries, commit=False)
-        wanting = [e.request for e in sched.entries if e.wants_logits]
-        sampled = self.sampler.sample(logits, wanting) if wanting else []
-        return self.scheduler.update(sched, sampled)
+        launched = None
+        if sched.entries:
+            rows = self._inflight[2] if self._inflight is not None else {}
+            entries = []
+            for e in sched.entries:
+                toks = e.tokens
+                if e.is_decode and toks[0] == PENDING:
+                    toks = [-(rows[e.request.request_id] + 1)]       # still on the device
+                entries.append(StepEntry(e.request.request_id, toks, [len(toks) - 1] if e.wants_logits else []))
+            logits = self.runner.step(entries, commit=False,
+                                      sampled=self.sampler.dev_out if self._inflight is not None else None)
+            wanting = [e.request for e in sched.entries if e.wants_logits]
+            ticket = self.sampler.launch(logits, wanting) if wanting else None
+            adv = self.scheduler.advance(sched)
+            launched = (adv, ticket, {r.request_id: i for i, r in enumerate(wanting)})
+        if self._inflight is not None:
+            out += self._finalize()                # the step before, now that the GPU has the next one queued
+        self._inflight = launched
+        if launched is not None and not ahead:
+            out += self._finalize()
+        return out
+
+    def _finalize(self) -> List[Response]:
+        adv, ticket, _ = self._inflight
+        self._inflight = None
+        sampled = self.sampler.fetch(ticket) if ticket is not None else []
+        return self.scheduler.resolve(adv, sampled)
 
     # ------------------------------------------------------------------ generate
     def generate(self, prompts: Sequence[Sequence[int]],
@@ -70,7 +103,7 @@ class LLM:
             raise ValueError("one SamplingParams per prompt")
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
         out: Dict[Hashable, List[int]] = {i: [] for i in ids}
-        while self.scheduler.has_unfinished():
+        while self.has_unfinished():
             for resp in self.step():
                 if resp.request_id in out:
                     out[resp.request_id].append(resp.token)

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import enum
 from dataclasses import dataclass, field
-from typing import Hashable, List
+from typing import Hashable, List, Optional
 
 from ..sampling.params import SamplingParams
 
@@ -30,6 +30,7 @@ class Request:
     num_computed: int = 0                   # tokens whose keys/values are in the cache
     num_preemptions: int = 0
     arrival: int = 0
+    ended_at: Optional[int] = None          # index of the end-of-sequence token, once one was sampled
 
     def __post_init__(self):
         self.tokens = [int(t) for t in self.tokens]

@@ -144,9 +144,12 @@ class ModelRunner:
         return self.cache.computed(req)
 
     # ------------------------------------------------------------------ the step
-    def prepare_step(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Reserve pages, pack the step's integers, start their copy to the device."""
+    def prepare_step(self, entries: Sequence[StepEntry], sampled: Optional[torch.Tensor] = None) -> StepContext:
+        """Reserve pages, pack the step's integers, start their copy to the device.  With
+        ``sampled`` (the device buffer of the last sampling launch) a token may be given as
+        -(row + 1): the value that launch wrote to that row, filled in on the device."""
         cm = self.cache
+        pending = False
         if not entries:
             raise StepError("a step needs at least one entry")
         seen = set()
@@ -169,6 +172,9 @@ class ModelRunner:
             start = cm.computed(en.req)
             if self.max_positions is not None and start + n > self.max_positions:
                 raise StepError(f"request {en.req!r}: {start + n} tokens exceed the model's {self.max_positions} positions")
+            if lo < 0 and sampled is not None and lo >= -int(sampled.numel()):
+                pending = True
+                lo = 0
             if lo < 0 or hi >= self.vocab_size:
                 bad = next(int(t) for t in en.tokens if not (0 <= int(t) < self.vocab_size))
                 raise StepError(f"request {en.req!r}: token id {bad} is outside the vocabulary of {self.vocab_size}")
@@ -226,7 +232,7 @@ class ModelRunner:
         for g in range(ng):
             mp = max(len(t) for t in tables[g])
             max_pages.append(max(16, 1 << (mp - 1).bit_length()))   # powers of two: few distinct shapes for captured graphs
-        tiles = [] if T == S else attention_tiles(q_lens)
+        tiles = [] if T == S else attention_tiles(q_lens, q_start)
         layout = StepLayout.make(T, S, len(logit_rows), max_pages, len(tiles) // 3)
         i, host = self._staging(layout.total)
         self._last_layout_total = layout.total
@@ -235,6 +241,7 @@ class ModelRunner:
                   slot_mappings=slot_maps, block_tables=tables, attn_tiles=tiles)
         self._dev[:layout.total].copy_(host[:layout.total], non_blocking=True)
         self._host_events[i].record()
+        self._pending_ids = pending
         # the device views of a layout are always the same tensors: keep them, refresh the host-side facts
         key = (layout.key(), self._dev.data_ptr())
         ctx = self._ctx_cache.get(key)
@@ -247,12 +254,15 @@ class ModelRunner:
             ctx.set_host_facts(q_lens, q_start)
         return ctx
 
-    def step(self, entries: Sequence[StepEntry], commit: bool = True) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], commit: bool = True,
+             sampled: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one batch; returns 32-bit logits [number of wanted places, vocab] in the
         order of the entries and of each entry's ``want`` (a view that the next step
         overwrites), or None if nothing was wanted.  ``commit=False`` leaves it to the
         caller (the scheduler) to tell the cache manager that the tokens are in."""
-        ctx = self.prepare_step(entries)
+        ctx = self.prepare_step(entries, sampled)
+        if self._pending_ids:
+            ops.resolve_tokens(ctx.token_ids, sampled)
         logits = self._forward(ctx)
         if commit:
             for en in entries:

@@ -38,6 +38,9 @@ class SchedulerError(RuntimeError):
     pass
 
 
+PENDING = -1      # a generated token whose value has not been read back yet
+
+
 @dataclass
 class ScheduledEntry:
     request: Request
@@ -54,6 +57,14 @@ class ScheduledStep:
     @property
     def num_tokens(self) -> int:
         return sum(len(e.tokens) for e in self.entries)
+
+
+@dataclass
+class AdvancedStep:
+    """A launched step: for every entry that wanted logits, (request, index of the new
+    token in request.tokens, finished by count)."""
+    step: ScheduledStep
+    places: List[Tuple[Request, int, bool]] = field(default_factory=list)
 
 
 @dataclass
@@ -222,12 +233,15 @@ class Scheduler:
         return victim
 
     # ------------------------------------------------------------------ after the model ran
-    def update(self, step: ScheduledStep, sampled: List[int]) -> List[Response]:
-        """``sampled``: one token for every entry that wanted logits, in order.  Marks
-        the step's tokens as held by the cache, appends the new tokens, finishes
-        and frees."""
-        out: List[Response] = []
-        it = iter(sampled)
+    def advance(self, step: ScheduledStep) -> "AdvancedStep":
+        """The step has been launched: its tokens are held by the cache, and every entry that
+        wanted logits gets a place for its new token (``PENDING`` until ``resolve`` fills it
+        in).  What depends on the count of tokens alone is decided here: a request that has
+        reached max_new_tokens or the model's last position finishes and frees its pages,
+        although the value of its last token is not known yet.  The next step can be
+        scheduled on this state; a token that turns out to end its request is found by
+        ``resolve``."""
+        adv = AdvancedStep(step)
         self.stats.steps += 1
         self.stats.tokens += step.num_tokens
         for en in step.entries:
@@ -236,28 +250,67 @@ class Scheduler:
             req.num_computed += len(en.tokens)
             if not en.wants_logits:
                 continue
-            tok = int(next(it))
-            req.tokens.append(tok)
+            index = len(req.tokens)
+            req.tokens.append(PENDING)
             finished = req.isfinish()
-            if not req.params.ignore_eos and self.eos_token_id is not None and tok == self.eos_token_id:
-                finished = True
             if self.max_positions is not None and len(req.tokens) >= self.max_positions + 1:
                 finished = True             # the new token has no position left to be fed at
-            out.append(Response(req.request_id, tok, finished))
+            adv.places.append((req, index, finished))
             if not en.is_decode:
                 self.prefill.remove(req)
             if finished:
                 if en.is_decode:
                     self.decode.remove(req)
-                self.cache.release(req.request_id)
-                req.state = RequestState.Finished
-                self.finished.append(req)
-                self.stats.finished += 1
-                self.admission_paused = False
+                self._finish(req)
             else:
                 req.state = RequestState.DecodeReady
                 if not en.is_decode:
                     self.decode.append(req)
         for g in self.cache.groups:
             self.stats.peak_pages = max(self.stats.peak_pages, g.allocator.peak_in_use)
+        return adv
+
+    def resolve(self, adv: "AdvancedStep", sampled: List[int]) -> List[Response]:
+        """``sampled``: one token for every entry of the step that wanted logits, in order.
+        Fills them in; a request whose token is the end-of-sequence token finishes here, and
+        what a later step (launched before this was known) computed for it is dropped."""
+        out: List[Response] = []
+        if len(sampled) != len(adv.places):
+            raise SchedulerError(f"{len(adv.places)} tokens expected, {len(sampled)} given")
+        for (req, index, finished), tok in zip(adv.places, sampled):
+            if req.ended_at is not None and index > req.ended_at:
+                continue                        # computed after the request's last token: dropped
+            tok = int(tok)
+            req.tokens[index] = tok
+            if not req.params.ignore_eos and self.eos_token_id is not None and tok == self.eos_token_id:
+                req.ended_at = index
+                del req.tokens[index + 1:]
+                if req.state != RequestState.Finished:
+                    if req in self.decode:
+                        self.decode.remove(req)
+                    if req in self.deferred_decode:
+                        self.deferred_decode.remove(req)
+                    self._finish(req)
+                finished = True
+            out.append(Response(req.request_id, tok, finished))
         return out
+
+    def update(self, step: ScheduledStep, sampled: List[int]) -> List[Response]:
+        """advance and resolve in one call, for a caller that has the tokens at hand."""
+        return self.resolve(self.advance(step), sampled)
+
+    def _finish(self, req: Request) -> None:
+        self.cache.release(req.request_id)
+        req.state = RequestState.Finished
+        self.finished.append(req)
+        self.stats.finished += 1
+        self.admission_paused = False
+
+    def can_run_ahead(self) -> bool:
+        """True when the next step can be scheduled before the last one's tokens are known:
+        only decoding requests, and a free page in every group for each of them, so that
+        nothing is admitted, cut, deferred or preempted on a token that is still pending."""
+        if self.waiting or self.deferred_prefill or self.prefill or self.deferred_decode:
+            return False
+        n = len(self.decode)
+        return all(g.allocator.num_free >= n for g in self.cache.groups)

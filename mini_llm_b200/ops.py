@@ -38,6 +38,7 @@ def _signatures(lib):
     lib.mllm_set_pdl.restype = c_int
     sig = {
         "mllm_embed": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mllm_resolve_tokens": [c_void_p, c_int, c_void_p, c_int, c_void_p],
         "mllm_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
         "mllm_kv_write": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                           c_void_p],
@@ -186,6 +187,14 @@ def embed(ids, positions, table, pos_table, out) -> None:
         pp = pos_table.data_ptr()
     _call("mllm_embed", ids.data_ptr(), positions.data_ptr() if pos_table is not None else None,
           table.data_ptr(), pp, out.data_ptr(), T, D, _dt(table), _stream())
+
+
+def resolve_tokens(ids, sampled) -> None:
+    """In place: ids[t] = sampled[-ids[t] - 1] wherever ids[t] is negative (a token that the
+    last sampling launch left on the device and the host has not read yet)."""
+    _cuda("ids", ids, torch.int32)
+    _cuda("sampled", sampled, torch.int32)
+    _call("mllm_resolve_tokens", ids.data_ptr(), ids.numel(), sampled.data_ptr(), sampled.numel(), _stream())
 
 
 # --------------------------------------------------------------------------- norm

@@ -135,6 +135,46 @@ def test_small_pool_defers_and_preempts_but_tokens_stay_the_same(setup):
     assert tight.runner.cache.num_live == 0 and tight.runner.cache.num_free_pages() == tight.runner.num_pages
 
 
+def test_running_ahead_gives_the_same_tokens_as_reading_every_step(setup):
+    """async_scheduling launches a decode step before the tokens of the one before it are
+    read; tokens, finish flags and the cache's state must be those of the step-by-step
+    loop, also where an end token arrives while the next step is already running."""
+    import mini_llm_b200 as m
+    cfg, dtype, page = setup["cfg"], setup["dtype"], setup["page"]
+    prompts = [random_ids(n, cfg["vocab_size"], 900 + n) for n in (9, 21, 4, 30)]
+
+    def run(async_on, eos, temperature):
+        llm = m.LLM(setup["dir"], dtype=dtype, page_size=page, max_tokens=1024, max_num_seqs=4,
+                    async_scheduling=async_on)
+        llm.scheduler.eos_token_id = eos
+        ids = [llm.add_request(p, m.SamplingParams(temperature=temperature, seed=5, max_new_tokens=14,
+                                                   ignore_eos=eos is None)) for p in prompts]
+        out = {i: [] for i in ids}
+        calls = 0
+        while llm.has_unfinished():
+            calls += 1
+            for r in llm.step():
+                assert not (out[r.request_id] and out[r.request_id][-1][1]), "a token after the last one"
+                out[r.request_id].append((r.token, r.finished))
+        assert llm.runner.cache.num_live == 0
+        llm.runner.cache.check()
+        assert llm.runner.cache.num_free_pages() == llm.runner.num_pages
+        return [out[i] for i in ids], calls
+
+    for temperature in (0.0, 0.7):
+        base, _ = run(False, None, temperature)
+        ahead, _ = run(True, None, temperature)
+        assert ahead == base
+        # make the 6th token of the second request the end token
+        eos = base[1][5][0]
+        base_e, _ = run(False, eos, temperature)
+        ahead_e, _ = run(True, eos, temperature)
+        assert ahead_e == base_e
+        assert base_e[1][-1] == (eos, True) and len(base_e[1]) <= 6
+        for o in base_e:
+            assert o[-1][1] and all(not f for _, f in o[:-1])
+
+
 def test_command_line(setup, tmp_path):
     cfg, dtype = setup["cfg"], setup["dtype"]
     p1, p2 = random_ids(6, cfg["vocab_size"], 1), random_ids(11, cfg["vocab_size"], 2)

@@ -202,3 +202,85 @@ def test_random_workloads_under_pressure(seed):
         room = 48 - len(p) + 1
         assert out[i] == want[:max(1, min(n, room))]
     assert cm.num_free_pages() == 14 and cm.num_live == 0
+
+
+# ---------------------------------------------------------------------------------- running ahead
+def run_ahead(sched, cm, token_of, max_steps=1000):
+    """Drive advance/resolve the way the entry point does while it runs ahead: a step is
+    scheduled and advanced before the tokens of the step before it are resolved."""
+    from mini_llm_b200.engine.scheduler import PENDING
+    out, inflight, steps = {}, None, 0
+
+    def finalize():
+        nonlocal inflight
+        adv, toks = inflight
+        inflight = None
+        for resp in sched.resolve(adv, toks):
+            out.setdefault(resp.request_id, []).append((resp.token, resp.finished))
+
+    while sched.has_unfinished() or inflight is not None:
+        steps += 1
+        assert steps < max_steps
+        ahead = sched.can_run_ahead()
+        if inflight is not None and not ahead:
+            finalize()
+        st = sched.schedule()
+        launched = None
+        if st.entries:
+            for e in st.entries:
+                if not e.is_decode:
+                    assert PENDING not in e.tokens          # a prompt portion never holds an unread token
+            # the "device" knows every token: what the model would sample for each entry
+            toks = [token_of(e.request) for e in st.entries if e.wants_logits]
+            launched = (sched.advance(st), toks)
+        if inflight is not None:
+            finalize()
+        inflight = launched
+        if launched is not None and not ahead:
+            finalize()
+        cm.check()
+    return out, steps
+
+
+def test_running_ahead_gives_the_same_tokens_and_drops_what_follows_an_end_token():
+    """Request 1 samples the end token as its 3rd token; the step launched before that was
+    known computed a 4th one, which is dropped; the others are unaffected."""
+    from mini_llm_b200.engine.scheduler import PENDING
+    cm, s = make(num_pages=64, budget=64, chunk=64)
+    truth = {}                                   # request id -> tokens the "device" has produced
+
+    def token_of(req):
+        hist = truth.setdefault(req.request_id, [])
+        tok = EOS if (req.request_id == 1 and len(hist) == 2) else 1000 + 10 * req.request_id + len(hist)
+        hist.append(tok)
+        return tok
+
+    for i, n in enumerate((5, 9, 3)):
+        s.add(Request(i, list(range(20, 20 + n)), SamplingParams(max_new_tokens=6)))
+    out, steps = run_ahead(s, cm, token_of)
+    assert [t for t, _ in out[0]] == [1000 + k for k in range(6)]
+    assert [t for t, _ in out[2]] == [1020 + k for k in range(6)]
+    assert [t for t, _ in out[1]] == [1010, 1011, EOS]
+    assert [f for _, f in out[1]] == [False, False, True]
+    assert [f for _, f in out[0]] == [False] * 5 + [True]
+    assert len(truth[1]) == 4                    # one token was computed past the end and dropped
+    for r in s.finished:
+        assert PENDING not in r.tokens
+    assert {r.request_id: r.tokens[r.prompts_len:] for r in s.finished}[1] == [1010, 1011, EOS]
+    assert cm.num_live == 0 and s.stats.finished == 3
+    assert steps <= 1 + 6 + 1                    # the prompts in one step, then one step per token, one to drain
+
+
+def test_running_ahead_stops_while_pages_are_short_or_prompts_wait():
+    cm, s = make(num_pages=6, page=4, seqs=4, budget=16, chunk=8)
+    s.add(Request(0, list(range(10, 18)), SamplingParams(max_new_tokens=12, ignore_eos=True)))
+    assert not s.can_run_ahead()                 # a prompt is waiting
+    st = s.schedule()
+    s.update(st, [1000])
+    assert s.can_run_ahead()
+    s.add(Request(1, list(range(30, 38)), SamplingParams(max_new_tokens=12, ignore_eos=True)))
+    assert not s.can_run_ahead()
+    out, _ = run_ahead(s, cm, lambda r: 1000 + len(r.tokens))
+    assert len(out[0]) == 11 and len(out[1]) == 12      # request 0 had one token before
+    assert cm.num_live == 0
+    cm.check()
