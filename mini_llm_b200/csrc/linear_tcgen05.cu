@@ -74,6 +74,18 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, const void* smem_src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(smem_u32(smem_src)) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, const void* smem_src) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(smem_u32(smem_src)) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
@@ -128,13 +140,16 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
 constexpr int tmem_cols(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn <= 128 ? 128 : 256; }
 
 template <int BN> struct Cfg {
+    static constexpr int KB = BN <= 96 ? 2 : 1;                     // 64-wide k-blocks per stage: narrow tiles wait less often
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;           // a multiple of 1024 for every BN used
+    static constexpr int BLOCK_BYTES = A_BYTES + B_BYTES;           // one k-block of A and of W
+    static constexpr int STAGE_BYTES = KB * BLOCK_BYTES;            // a multiple of 1024 for every BN used
     static constexpr int EPI_ROW = 36;                              // floats per staged row: 32 + 4 of padding
     static constexpr int EPI_BYTES = EPI_WARPS * 32 * EPI_ROW * 4;  // every epilogue warp stages 32 rows
-    static constexpr int STAGES = (227 * 1024 - EPI_BYTES - 2304) / STAGE_BYTES;   // 3 (BN=256) ... 7 (BN=64)
+    static constexpr int BIAS_BYTES = EPI_WARPS * 128 * 4;          // every epilogue warp keeps the bias of its (up to 4) chunks
+    static constexpr int STAGES = (227 * 1024 - EPI_BYTES - BIAS_BYTES - 2304) / STAGE_BYTES;   // 3 (BN=256, 96) ... 4 (BN=192, 64)
     static constexpr int ACC_COLS = tmem_cols(BN);                  // tensor-memory columns of one accumulator
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + EPI_BYTES + BIAS_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
 // A persistent CTA: tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...; tile -> (m tile, n tile)
@@ -143,13 +158,15 @@ template <int BN> struct Cfg {
 template <int BN, typename TO>
 __global__ void __launch_bounds__(THREADS, 1)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                      const float* __restrict__ bias, TO* out, long long ldo, int M, int N, int K, int act,
-                      int accumulate, int vec_ok, int tiles_n, int num_tiles) {
+                      const __grid_constant__ CUtensorMap map_o, const float* __restrict__ bias, TO* out, long long ldo,
+                      int M, int N, int K, int act, int accumulate, int vec_ok, int tma_out, int tiles_n,
+                      int num_tiles) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    float* epi = reinterpret_cast<float*>(tiles + (size_t)C::STAGES * C::STAGE_BYTES);
-    uint64_t* full = (uint64_t*)(tiles + (size_t)C::STAGES * C::STAGE_BYTES + C::EPI_BYTES);
+    float* epi = reinterpret_cast<float*>(tiles + (size_t)C::STAGES * C::STAGE_BYTES);       // 1024-byte aligned
+    float* sbias = reinterpret_cast<float*>(tiles + (size_t)C::STAGES * C::STAGE_BYTES + C::EPI_BYTES);   // [EPI_WARPS][128]
+    uint64_t* full = (uint64_t*)(tiles + (size_t)C::STAGES * C::STAGE_BYTES + C::EPI_BYTES + C::BIAS_BYTES);
     uint64_t* empty = full + C::STAGES;
     uint64_t* acc_full = empty + C::STAGES;          // [2]
     uint64_t* acc_empty = acc_full + 2;              // [2]
@@ -157,7 +174,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     volatile int* failed = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nk = (K + BK - 1) / BK;
+    const int nk = (K + C::KB * BK - 1) / (C::KB * BK);       // stages per tile; k-blocks beyond K are zeros
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -184,8 +201,11 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     if (*failed) break;
                     uint8_t* a_dst = tiles + (size_t)s * C::STAGE_BYTES;
                     mbar_expect_tx(&full[s], C::STAGE_BYTES);
-                    tma_load_2d(a_dst, &map_a, kt * BK, m0, &full[s]);
-                    tma_load_2d(a_dst + C::A_BYTES, &map_w, kt * BK, n0, &full[s]);
+#pragma unroll
+                    for (int b = 0; b < C::KB; ++b) {
+                        tma_load_2d(a_dst + b * C::BLOCK_BYTES, &map_a, (kt * C::KB + b) * BK, m0, &full[s]);
+                        tma_load_2d(a_dst + b * C::BLOCK_BYTES + C::A_BYTES, &map_w, (kt * C::KB + b) * BK, n0, &full[s]);
+                    }
                 }
             }
         }
@@ -204,10 +224,14 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     if (!mbar_wait(&full[s], (g / C::STAGES) & 1)) { *failed = 2; ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
-                    const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + C::A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)      // 32 bytes along K inside the swizzle atom = +2 in the address field
-                        umma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kt | k) != 0);
+                    for (int b = 0; b < C::KB; ++b) {
+                        const uint64_t a_desc = make_smem_desc(a_addr + b * C::BLOCK_BYTES);
+                        const uint64_t b_desc = make_smem_desc(a_addr + b * C::BLOCK_BYTES + C::A_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)      // 32 bytes along K inside the swizzle atom = +2 in the address field
+                            umma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kt | b | k) != 0);
+                    }
                     umma_commit(&empty[s]);                 // the stage is free once these MMAs have read it
                 }
                 if (!ok) break;
@@ -223,6 +247,16 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti) {
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
             const int buf = ti & 1;
+            float* wb = sbias + (warp - 2) * 128;            // this warp's bias values: 32 per chunk it will take
+            if (tma_out) {
+                // fetched while the MMAs still run; nobody else reads or writes this warp's copy
+#pragma unroll
+                for (int k = 0; k < (BN / 32 + 1) / 2; ++k) {
+                    const int n = n0 + (half + 2 * k) * 32 + lane;
+                    wb[k * 32 + lane] = (bias && half + 2 * k < BN / 32 && n < N) ? __ldg(bias + n) : 0.f;
+                }
+                __syncwarp();
+            }
             bool ok = mbar_wait(&acc_full[buf], (ti >> 1) & 1);
             if (!ok) *failed = 3;
             ok = __all_sync(0xffffffffu, ok && !*failed);   // tcgen05.ld is warp-wide: decide as a warp
@@ -233,6 +267,76 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             // the current ones go through shared memory to global memory.
             constexpr int NC = BN / 32;
             uint32_t r[32];
+            if (tma_out) {
+                // the block of 32 rows x 32 columns goes out through the copy engine
+                constexpr int ES = (int)sizeof(TO);
+                uint8_t* sblk = reinterpret_cast<uint8_t*>(epi) + (size_t)(warp - 2) * 4096;    // 1024-byte aligned
+                const int row0 = m0 + q * 32;
+                if (half < NC) {
+                    tmem_ld32_issue(t_addr + (uint32_t)(half * 32), r);
+                    tmem_ld_wait();
+                }
+                if (half + 2 >= NC) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                }
+#pragma unroll 1
+                for (int c = half; c < NC; c += 2) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(wb + (c >> 1) * 32 + 4 * j);   // same address in all lanes
+                        v[4 * j] = __uint_as_float(r[4 * j]) + b4.x;
+                        v[4 * j + 1] = __uint_as_float(r[4 * j + 1]) + b4.y;
+                        v[4 * j + 2] = __uint_as_float(r[4 * j + 2]) + b4.z;
+                        v[4 * j + 3] = __uint_as_float(r[4 * j + 3]) + b4.w;
+                    }
+                    if (c + 2 < NC) tmem_ld32_issue(t_addr + (uint32_t)((c + 2) * 32), r);   // r is free: refill it meanwhile
+                    if (act == MLLM_ACT_GELU_TANH) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = ES == 2 ? gelu_tanh_fast(v[j]) : gelu_tanh_f(v[j]);
+                    } else if (act == MLLM_ACT_GELU_ERF) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = gelu_erf_f(v[j]);
+                    }
+                    if (lane == 0) bulk_wait_read();         // the copy engine has read the last block out of the buffer
+                    __syncwarp();
+                    // lane = row; 16-byte pieces are swizzled the way the tensor map expects (128-byte rows:
+                    // piece ^ (row & 7); 64-byte rows: piece ^ ((row >> 1) & 3)), which also spreads the banks
+                    if constexpr (ES == 4) {
+                        uint8_t* rowp = sblk + lane * 128;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            *reinterpret_cast<float4*>(rowp + ((j ^ (lane & 7)) << 4)) =
+                                make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    } else {
+                        uint8_t* rowp = sblk + lane * 64;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint4 pk;
+                            __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) hh[i] = __floats2bfloat162_rn(v[8 * j + 2 * i], v[8 * j + 2 * i + 1]);
+                            *reinterpret_cast<uint4*>(rowp + ((j ^ ((lane >> 1) & 3)) << 4)) = pk;
+                        }
+                    }
+                    fence_async_smem();                      // the writes above become visible to the copy engine
+                    __syncwarp();
+                    if (lane == 0 && row0 < M && n0 + c * 32 < N) {
+                        if (accumulate) tma_reduce_add_2d(&map_o, n0 + c * 32, row0, sblk);
+                        else tma_store_2d(&map_o, n0 + c * 32, row0, sblk);
+                        bulk_commit();
+                    }
+                    if (c + 2 < NC) tmem_ld_wait();
+                    if (c + 2 < NC && c + 4 >= NC) {         // this warp's last read of the accumulator has landed
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    }
+                }
+                continue;
+            }
             if (half < NC) {
                 tmem_ld32_issue(t_addr + (uint32_t)(half * 32), r);
                 tmem_ld_wait();
@@ -327,6 +431,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             }
         }
     }
+    if (warp >= 2 && lane == 0 && tma_out) bulk_wait_all();     // this thread's stores have been written
     tc_fence_before();
     __syncthreads();
     if (*failed) {
@@ -360,9 +465,9 @@ EncodeTiledFn encode_fn() {
 }
 
 struct MapKey {
-    const void* ptr; long long ld; int rows, cols, box_rows;
+    const void* ptr; long long ld; int rows, cols, box_rows, kind;
     bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && ld == o.ld && rows == o.rows && cols == o.cols && box_rows == o.box_rows;
+        return ptr == o.ptr && ld == o.ld && rows == o.rows && cols == o.cols && box_rows == o.box_rows && kind == o.kind;
     }
 };
 struct MapKeyHash {
@@ -371,29 +476,36 @@ struct MapKeyHash {
         h = h * 1000003u ^ (size_t)k.ld;
         h = h * 1000003u ^ (size_t)k.rows;
         h = h * 1000003u ^ (size_t)k.cols;
-        h = h * 1000003u ^ (size_t)k.box_rows;
+        h = h * 1000003u ^ (size_t)(k.box_rows * 4 + k.kind);
         return h;
     }
 };
 
-// A [rows, cols] bf16 matrix with row stride ld (elements), boxes of box_rows x 64, 128-byte swizzle.
-int get_map(const void* ptr, long long ld, int rows, int cols, int box_rows, CUtensorMap* out) {
+// Kinds of tensor maps over a row-major [rows, cols] matrix with row stride ld (elements):
+//   MAP_OPERAND  bfloat16, boxes of box_rows x 64 (128 bytes), 128-byte swizzle: the MMA operands
+//   MAP_OUT_F32  32-bit,   boxes of 32 x 32 (128 bytes),       128-byte swizzle: the epilogue's blocks
+//   MAP_OUT_BF16 bfloat16, boxes of 32 x 32 (64 bytes),        64-byte swizzle
+enum { MAP_OPERAND = 0, MAP_OUT_F32 = 1, MAP_OUT_BF16 = 2 };
+
+int get_map(const void* ptr, long long ld, int rows, int cols, int box_rows, int kind, CUtensorMap* out) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     static std::mutex mu;
-    MapKey key{ptr, ld, rows, cols, box_rows};
+    MapKey key{ptr, ld, rows, cols, box_rows, kind};
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) { *out = it->second; return 0; }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return mllm_fail(3, "linear_tcgen05: cuTensorMapEncodeTiled is not available from the driver");
+    const int es = kind == MAP_OUT_F32 ? 4 : 2;
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * es};
+    cuuint32_t box[2] = {(cuuint32_t)(kind == MAP_OPERAND ? BK : 32), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUtensorMap m;
-    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = fn(&m, kind == MAP_OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    kind == MAP_OUT_BF16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return mllm_fail(3, "linear_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
     if (cache.size() > 4096) cache.clear();
     cache.emplace(key, m);
@@ -416,11 +528,21 @@ int launch(const void* A, long long lda, const void* W, const float* bias, void*
            int K, int act, int accumulate, cudaStream_t stream) {
     using C = Cfg<BN>;
     static_assert(C::STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of swizzled tiles");
-    CUtensorMap ma, mw;
-    int rc = get_map(A, lda, M, K, BM, &ma);
+    CUtensorMap ma, mw, mo;
+    int rc = get_map(A, lda, M, K, BM, MAP_OPERAND, &ma);
     if (rc) return rc;
-    rc = get_map(W, K, N, K, BN, &mw);
+    rc = get_map(W, K, N, K, BN, MAP_OPERAND, &mw);
     if (rc) return rc;
+    // The copy engine writes the result when its rows are 16-byte aligned; a residual sum goes through
+    // it only in 32-bit (its bfloat16 addition would round the new term before adding).
+    const int tma_out = (uintptr_t)out % 16 == 0 && (ldo * (long long)sizeof(TO)) % 16 == 0 &&
+                        !(accumulate && sizeof(TO) == 2);
+    if (tma_out) {
+        rc = get_map(out, ldo, M, N, 32, sizeof(TO) == 4 ? MAP_OUT_F32 : MAP_OUT_BF16, &mo);
+        if (rc) return rc;
+    } else {
+        mo = ma;                                       // not used by the kernel
+    }
     auto kern = linear_tcgen05_kernel<BN, TO>;
     static bool set = false;
     if (!set) {
@@ -432,8 +554,8 @@ int launch(const void* A, long long lda, const void* W, const float* bias, void*
     const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
     const int num_tiles = tiles_n * tiles_m;
     const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
-    MLLM_CUDA(mllm_launch(kern, dim3(grid), dim3(THREADS), C::SMEM, stream, true, ma, mw, bias, (TO*)out, ldo, M, N, K,
-                          act, accumulate, vec_ok, tiles_n, num_tiles));
+    MLLM_CUDA(mllm_launch(kern, dim3(grid), dim3(THREADS), C::SMEM, stream, true, ma, mw, mo, bias, (TO*)out, ldo, M, N,
+                          K, act, accumulate, vec_ok, tma_out, tiles_n, num_tiles));
     return 0;
 }
 

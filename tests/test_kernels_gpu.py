@@ -139,6 +139,16 @@ def test_linear_tcgen05_against_the_plain_kernel(ops, out_dtype, M, N, K):
     ops.linear(x, w, b, out=pad[:, :N], impl="tcgen05")
     assert (pad[:, :N].double() - ref).abs().max() < tol * max(1.0, ref.abs().max().item())
     assert torch.all(pad[:, N:] == 0)
+    # rows 16-byte aligned but wider than N, and more rows than M: the copy engine's stores stop at the edges
+    big = torch.full((M + 5, N + 8), 3.0, device=DEV, dtype=out_dtype)
+    ops.linear(x, w, b, out=big[:M, :N], impl="tcgen05")
+    assert (big[:M, :N].double() - ref).abs().max() < tol * max(1.0, ref.abs().max().item())
+    assert torch.all(big[:, N:] == 3.0) and torch.all(big[M:] == 3.0)
+    if out_dtype == torch.float32:
+        big[:M, :N] = acc0
+        ops.linear(wide[:, 8:8 + K], w, b, out=big[:M, :N], accumulate=True, impl="tcgen05")
+        assert (big[:M, :N].double() - want).abs().max() < 1e-4 * max(1.0, want.abs().max().item())
+        assert torch.all(big[:, N:] == 3.0) and torch.all(big[M:] == 3.0)
     ops.check_device_errors()
 
 
