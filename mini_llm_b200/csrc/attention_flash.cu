@@ -51,6 +51,13 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ void group_barrier(int group) {         // the 4 warps of one group
     asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(WARPS * 32) : "memory");
 }
+// 2^x for x <= 0 (and -inf): one MUFU instruction; results below 2^-126 are flushed to zero, which a
+// softmax weight that small may be.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -167,42 +174,45 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
                 mma16816(s[2 * np + 1], qa[ks], b[2], b[3]);
             }
         }
-        // mask and online softmax (two rows per thread: g and g+8)
+        // mask and online softmax (two rows per thread: g and g+8).  The scores stay unscaled; the scale
+        // (times log2 e, positive) enters with the subtraction of the maximum as one multiply-add.
         const int kbase = j * BKV + 2 * t;
         const bool need_mask = (j * BKV + BKV - 1 > pos0 + warp * 16) || (window > 0);
         float mx[2] = {-INFINITY, -INFINITY};
+        if (need_mask) {
 #pragma unroll
-        for (int nt = 0; nt < BKV / 8; ++nt) {
+            for (int nt = 0; nt < BKV / 8; ++nt) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int r = k >> 1;
-                float v = s[nt][k] * sl2;
-                if (need_mask) {
+                for (int k = 0; k < 4; ++k) {
                     const int kp = kbase + nt * 8 + (k & 1);
-                    const int qp = qrow0 + r * 8;
+                    const int qp = qrow0 + (k >> 1) * 8;
                     const bool vis = kp <= qp && (window <= 0 || kp > qp - window);
-                    v = vis ? v : -INFINITY;
+                    s[nt][k] = vis ? s[nt][k] : -INFINITY;
                 }
-                s[nt][k] = v;
-                mx[r] = fmaxf(mx[r], v);
             }
         }
-        float alpha[2], muse[2];
+#pragma unroll
+        for (int nt = 0; nt < BKV / 8; ++nt) {
+            mx[0] = fmaxf(mx[0], fmaxf(s[nt][0], s[nt][1]));
+            mx[1] = fmaxf(mx[1], fmaxf(s[nt][2], s[nt][3]));
+        }
+        float alpha[2], mneg[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(m_run[r], mx[r]);
-            muse[r] = m_new == -INFINITY ? 0.f : m_new;
-            alpha[r] = exp2f(m_run[r] - muse[r]);           // exp2(-inf) = 0 while nothing was seen
+            const float m_new = fmaxf(m_run[r], mx[r] * sl2);      // running maximum of the scaled scores
+            const float muse = m_new == -INFINITY ? 0.f : m_new;
+            alpha[r] = fast_exp2(m_run[r] - muse);              // 2^(-inf) = 0 while nothing was seen
             m_run[r] = m_new;
+            mneg[r] = -muse;
         }
         float rs[2] = {0.f, 0.f};
         uint32_t pa[BKV / 16][4], pb[BKV / 16][4];
 #pragma unroll
         for (int nt = 0; nt < BKV / 8; ++nt) {
-            const float p0 = exp2f(s[nt][0] - muse[0]), p1 = exp2f(s[nt][1] - muse[0]);
-            const float p2 = exp2f(s[nt][2] - muse[1]), p3 = exp2f(s[nt][3] - muse[1]);
+            const float p0 = fast_exp2(fmaf(s[nt][0], sl2, mneg[0])), p1 = fast_exp2(fmaf(s[nt][1], sl2, mneg[0]));
+            const float p2 = fast_exp2(fmaf(s[nt][2], sl2, mneg[1])), p3 = fast_exp2(fmaf(s[nt][3], sl2, mneg[1]));
             rs[0] += p0 + p1;
             rs[1] += p2 + p3;
             const uint32_t h01 = pack_bf16(p0, p1), h23 = pack_bf16(p2, p3);
@@ -218,10 +228,12 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
             rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
             l_run[r] = l_run[r] * alpha[r] + rs[r];
         }
+        if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {     // the maximum moved for some row of the warp
 #pragma unroll
-        for (int i = 0; i < DH / 8; ++i) {
-            o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-            o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+            for (int i = 0; i < DH / 8; ++i) {
+                o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+                o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+            }
         }
         // O += P V
 #pragma unroll
@@ -263,7 +275,7 @@ attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
         const float m1 = xch[r], l1 = xch[2 + r];
         const float mm = fmaxf(m_run[r], m1);
         const float muse2 = mm == -INFINITY ? 0.f : mm;
-        const float a0 = exp2f(m_run[r] - muse2), a1 = exp2f(m1 - muse2);
+        const float a0 = fast_exp2(m_run[r] - muse2), a1 = fast_exp2(m1 - muse2);
         l_run[r] = l_run[r] * a0 + l1 * a1;
 #pragma unroll
         for (int i = 0; i < DH / 8; ++i) {
@@ -317,6 +329,7 @@ MLLM_EXPORT int mllm_attention_flash(const void* q, long long q_stride, const vo
     if (n_tiles <= 0) return 0;
     if (Hkv <= 0 || H % Hkv != 0) return mllm_fail(1, "attention_flash: %d heads over %d key/value heads", H, Hkv);
     if (n_tiles > 65535) return mllm_fail(1, "attention_flash: %d query tiles are more than one launch takes", n_tiles);
+    if (!(scale > 0.f)) return mllm_fail(1, "attention_flash: the score scale must be positive, got %g", (double)scale);
     if (q_stride % 8 || (uintptr_t)q % 16 || out_stride % 2 || (uintptr_t)out % 4)
         return mllm_fail(1, "attention_flash: queries must be 16-byte aligned, outputs 4-byte aligned");
 #define GO(D) return launch<D>(q, q_stride, k_pages, v_pages, block_table, bt_stride, tiles, n_tiles, positions, out, \
