@@ -40,13 +40,17 @@ class PageAllocator:
             raise ValueError("cannot allocate a negative number of pages")
         if n > len(self._free):
             raise PageError(f"asked for {n} pages, {len(self._free)} free")
-        out = []
-        for _ in range(n):
-            p = self._free.pop()
-            if self._in_use[p]:
+        if n == 0:
+            return []
+        out = self._free[-n:]
+        out.reverse()                       # the order in which single pops would have handed them out
+        in_use = self._in_use
+        for p in out:
+            if in_use[p]:
                 raise PageError(f"page {p} was on the free list while in use")
-            self._in_use[p] = 1
-            out.append(p)
+        del self._free[-n:]
+        for p in out:
+            in_use[p] = 1
         self.peak_in_use = max(self.peak_in_use, self.num_in_use)
         return out
 

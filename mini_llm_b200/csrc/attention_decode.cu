@@ -18,11 +18,15 @@
 // keys with one thread per key and one thread per output element
 // (src/kernels/decode/paged_attention.cu:60-120).
 //
-// When a request's splits fit a thread-block cluster (up to 8, i.e. contexts up to 1024),
-// the splits of a (token, head) are launched as one cluster and meet in distributed shared
-// memory: every CTA leaves its (m, l, o) in its own shared memory, the first CTA with work
-// reads them over the SM-to-SM network in split order and writes the result; no scratch in
-// global memory, no fence, no counter.  Longer contexts use the scratch path.
+// When the CTAs of a (token, head) fit a thread-block cluster (up to 8) they are launched as
+// one cluster and meet in distributed shared memory: every CTA leaves the (m, l, o) of its
+// splits in its own shared memory, the CTA with the first split reads them over the
+// SM-to-SM network in split order and writes the result; no scratch in global memory, no
+// fence, no counter.  With few (token, head) pairs every split gets a CTA of its own; with
+// many, a CTA walks up to 8 splits one after the other (the other resident CTAs hide its
+// waits), down to one CTA per pair, which then needs no cluster at all.  The partial
+// results and the order of their merge are the same in every arrangement, so a token's
+// result does not depend on the size of the batch.  Longer contexts use the scratch path.
 #include "common.cuh"
 #include <cooperative_groups.h>
 
@@ -54,35 +58,48 @@ template <> struct Vec16<__nv_bfloat16> {
     }
 };
 
-template <typename T, int LPK, bool CLUSTER>
+// How the splits of one (token, head) meet.
+enum { MODE_SCRATCH = 0,     // partial results in global scratch; the CTA that arrives last merges them
+       MODE_CLUSTER = 1,     // the CTAs of a (token, head) form a cluster and meet in distributed shared memory
+       MODE_LOCAL = 2 };     // one CTA walks all the splits and merges them from its own shared memory
+
+constexpr int MAX_SPC = 8;   // splits that one CTA may take, one after the other
+
+template <typename T, int LPK, int MODE, bool ONE>        // ONE: every CTA takes exactly one split
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
                    const T* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
                    const int* __restrict__ token_seq, const int* __restrict__ positions, T* __restrict__ out,
                    long long out_stride, float* __restrict__ part_o, float* __restrict__ part_ml,
                    unsigned int* __restrict__ counters, int H, int Hkv, int page_size, float scale, int window,
-                   int max_splits) {
+                   int max_splits, int spc_arg) {
+    const int spc = ONE ? 1 : spc_arg;
     constexpr int VEC = Vec16<T>::N;
     constexpr int DH = LPK * VEC;
     constexpr int NG = THREADS / LPK;                 // key groups per CTA
     constexpr int KPG = SPLIT / NG;                   // keys per group in a split
     constexpr int UNR = KPG < 8 ? KPG : 8;            // keys in flight per group
+    constexpr int RES = DH + 2;                       // a split's (o, m, l)
     __shared__ float sm_m[NG], sm_l[NG];
     __shared__ float sm_o[NG * DH];
-    __shared__ float sm_res[DH + 2];                          // this split's (o, m, l) for the cluster merge
+    __shared__ float sm_res[(MODE == MODE_SCRATCH || ONE ? 1 : MAX_SPC) * RES];
     __shared__ int s_last;
-    const int split = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
+    const int cx = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
     pdl_wait();
     pdl_launch();
     const int p = positions[t];
     const int seq = token_seq[t];
     int first = 0;
     if (window > 0 && p - window + 1 > 0) first = p - window + 1;
-    const int k_lo = split * SPLIT, k_hi = min(k_lo + SPLIT, p + 1);
     const int s_lo = first / SPLIT, s_hi = p / SPLIT;         // splits that have work, inclusive
-    if (k_lo > p || k_lo + SPLIT <= first) {                  // nothing visible in this split
-        if constexpr (CLUSTER) {
-            if (s_lo != s_hi) {                               // the others still meet at the cluster's barriers
+    // this CTA takes the splits cx*spc .. cx*spc+spc-1, one after the other
+    const int my_lo = max(cx * spc, s_lo), my_hi = min(cx * spc + spc - 1, s_hi);
+    const bool single = s_lo == s_hi;                         // the only split: its result is the output
+    const int c_lo = spc == 1 ? s_lo : s_lo / spc, c_hi = spc == 1 ? s_hi : s_hi / spc;   // CTAs with work
+    const bool several = c_lo != c_hi;                        // more than one (the same answer in all of them)
+    if (my_lo > my_hi) {                                      // nothing visible for this CTA
+        if constexpr (MODE == MODE_CLUSTER) {
+            if (several) {                                    // the others still meet at the cluster's barriers
                 cg::cluster_group cluster = cg::this_cluster();
                 cluster.sync();
                 cluster.sync();
@@ -95,128 +112,160 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
     const int gi = threadIdx.x / LPK, li = threadIdx.x % LPK;
 
     const uint4 qraw = *reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)h * DH + li * VEC);
-    float m = -INFINITY, l = 0.f, o[VEC];
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) o[i] = 0.f;
     float qv[VEC];
     Vec16<T>::unpack(qraw, qv);
 #pragma unroll
     for (int i = 0; i < VEC; ++i) qv[i] *= scale;
+    const size_t pair = (size_t)t * H + h;
 
 #pragma unroll 1
-    for (int kb = k_lo + gi; kb < k_lo + SPLIT; kb += NG * UNR) {   // same trip count for every lane
-        int page[UNR];
-        bool ok[UNR];
+    for (int split = my_lo; split <= my_hi; ++split) {
+        const int k_lo = split * SPLIT, k_hi = min(k_lo + SPLIT, p + 1);
+        float m = -INFINITY, l = 0.f, o[VEC];
 #pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            const int kp = kb + u * NG;
-            ok[u] = kp < k_hi && kp >= first;
-            page[u] = ok[u] ? bt[kp / page_size] : 0;
-        }
-        uint4 kr[UNR], vr[UNR];
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            const int kp = kb + u * NG;
-            kr[u] = make_uint4(0, 0, 0, 0);
-            vr[u] = make_uint4(0, 0, 0, 0);
-            if (ok[u]) {
-                const size_t off = (((size_t)page[u] * Hkv + hk) * page_size + kp % page_size) * DH + li * VEC;
-                kr[u] = *reinterpret_cast<const uint4*>(k_pages + off);
-                vr[u] = *reinterpret_cast<const uint4*>(v_pages + off);
-            }
-        }
-        float s[UNR];
-        float mx = m;
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            float kv[VEC];
-            Vec16<T>::unpack(kr[u], kv);
-            float d = 0.f;
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) d = fmaf(qv[i], kv[i], d);
-#pragma unroll
-            for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-            s[u] = ok[u] ? d : -INFINITY;
-            mx = fmaxf(mx, s[u]);
-        }
-        if (mx != -INFINITY) {                               // uniform within the group; no shuffles inside
-            const float alpha = expf(m - mx);
-            l *= alpha;
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) o[i] *= alpha;
+        for (int i = 0; i < VEC; ++i) o[i] = 0.f;
+#pragma unroll 1
+        for (int kb = k_lo + gi; kb < k_lo + SPLIT; kb += NG * UNR) {   // same trip count for every lane
+            int page[UNR];
+            bool ok[UNR];
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
-                const float pr = ok[u] ? expf(s[u] - mx) : 0.f;
-                float vv[VEC];
-                Vec16<T>::unpack(vr[u], vv);
-                l += pr;
-#pragma unroll
-                for (int i = 0; i < VEC; ++i) o[i] = fmaf(pr, vv[i], o[i]);
+                const int kp = kb + u * NG;
+                ok[u] = kp < k_hi && kp >= first;
+                page[u] = ok[u] ? bt[kp / page_size] : 0;
             }
-            m = mx;
-        }
-    }
-    if (li == 0) { sm_m[gi] = m; sm_l[gi] = l; }
+            uint4 kr[UNR], vr[UNR];
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) sm_o[gi * DH + li * VEC + i] = o[i];
-    __syncthreads();
-    float M = -INFINITY;
-    for (int g = 0; g < NG; ++g) M = fmaxf(M, sm_m[g]);
-    const size_t pair = (size_t)t * H + h;
-    const size_t slot = pair * max_splits + split;
-    const bool single = s_lo == s_hi;                        // the only split: write the result directly
-    float L = 0.f;
-    for (int g = 0; g < NG; ++g) {
-        const float w = sm_m[g] == -INFINITY ? 0.f : expf(sm_m[g] - M);
-        L = fmaf(w, sm_l[g], L);
-    }
-    for (int d = threadIdx.x; d < DH; d += THREADS) {
-        float acc = 0.f;
+            for (int u = 0; u < UNR; ++u) {
+                const int kp = kb + u * NG;
+                kr[u] = make_uint4(0, 0, 0, 0);
+                vr[u] = make_uint4(0, 0, 0, 0);
+                if (ok[u]) {
+                    const size_t off = (((size_t)page[u] * Hkv + hk) * page_size + kp % page_size) * DH + li * VEC;
+                    kr[u] = *reinterpret_cast<const uint4*>(k_pages + off);
+                    vr[u] = *reinterpret_cast<const uint4*>(v_pages + off);
+                }
+            }
+            float s[UNR];
+            float mx = m;
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                float kv[VEC];
+                Vec16<T>::unpack(kr[u], kv);
+                float d = 0.f;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) d = fmaf(qv[i], kv[i], d);
+#pragma unroll
+                for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+                s[u] = ok[u] ? d : -INFINITY;
+                mx = fmaxf(mx, s[u]);
+            }
+            if (mx != -INFINITY) {                               // uniform within the group; no shuffles inside
+                const float alpha = expf(m - mx);
+                l *= alpha;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) o[i] *= alpha;
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    const float pr = ok[u] ? expf(s[u] - mx) : 0.f;
+                    float vv[VEC];
+                    Vec16<T>::unpack(vr[u], vv);
+                    l += pr;
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) o[i] = fmaf(pr, vv[i], o[i]);
+                }
+                m = mx;
+            }
+        }
+        // the groups of the CTA are merged in group order
+        if (li == 0) { sm_m[gi] = m; sm_l[gi] = l; }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) sm_o[gi * DH + li * VEC + i] = o[i];
+        __syncthreads();
+        float M = -INFINITY;
+        for (int g = 0; g < NG; ++g) M = fmaxf(M, sm_m[g]);
+        float L = 0.f;
         for (int g = 0; g < NG; ++g) {
             const float w = sm_m[g] == -INFINITY ? 0.f : expf(sm_m[g] - M);
-            acc = fmaf(w, sm_o[g * DH + d], acc);
+            L = fmaf(w, sm_l[g], L);
         }
-        if (single) out[(size_t)t * out_stride + (size_t)h * DH + d] = from_f32<T>(acc / L);
-        else if (CLUSTER) sm_res[d] = acc;
-        else part_o[slot * DH + d] = acc;
+        const size_t slot = pair * max_splits + split;
+        float* res = sm_res + (MODE == MODE_SCRATCH ? 0 : (split - cx * spc) * RES);
+        for (int d = threadIdx.x; d < DH; d += THREADS) {
+            float acc = 0.f;
+            for (int g = 0; g < NG; ++g) {
+                const float w = sm_m[g] == -INFINITY ? 0.f : expf(sm_m[g] - M);
+                acc = fmaf(w, sm_o[g * DH + d], acc);
+            }
+            if (single) out[(size_t)t * out_stride + (size_t)h * DH + d] = from_f32<T>(acc / L);
+            else if (MODE == MODE_SCRATCH) part_o[slot * DH + d] = acc;
+            else res[d] = acc;
+        }
+        if (!single && threadIdx.x == 0) {
+            if (MODE == MODE_SCRATCH) { part_ml[slot * 2] = M; part_ml[slot * 2 + 1] = L; }
+            else { res[DH] = M; res[DH + 1] = L; }
+        }
+        if (split < my_hi) __syncthreads();                   // the group buffers are free for the next split
     }
-    if (CLUSTER && !single && threadIdx.x == 0) { sm_res[DH] = M; sm_res[DH + 1] = L; }
     if (single) return;
-    if constexpr (CLUSTER) {
-        // (o, m, l) of this split stay in shared memory; the cluster's first CTA collects them
-        // (the loop above wrote o to part_o only on the scratch path: redo it into sm_res)
+
+    if constexpr (MODE != MODE_SCRATCH) {
+        // every split's (o, m, l) stays in the shared memory of the CTA that computed it; the CTA with the
+        // first split collects them in split order - over the SM-to-SM network where another CTA holds them
         cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();                                       // every split's result is in place
-        if (split == s_lo) {                                  // the first split with work collects (rank == split)
+        const bool remote = MODE == MODE_CLUSTER && several;
+        if (remote) cluster.sync();                           // every split's result is in place
+        else __syncthreads();
+        if (cx == c_lo) {
+            // walks the splits s_lo..s_hi: CTA c holds the splits c*spc .. c*spc+spc-1 in that order
+            auto held_by = [&](int c) -> const float* {
+                return (remote && c <= c_hi) ? cluster.map_shared_rank(sm_res, c) : sm_res;
+            };
+            const int i_lo = s_lo - c_lo * spc;               // index of the first split inside its CTA
+#define MLLM_NEXT_SPLIT(r, c, i)                                  \
+    do {                                                          \
+        if (++i == spc) { i = 0; ++c; r = held_by(c); }           \
+        else r += RES;                                            \
+    } while (0)
             float MM = -INFINITY;
-            for (int s = s_lo; s <= s_hi; ++s) MM = fmaxf(MM, cluster.map_shared_rank(sm_res, s)[DH]);
+            {
+                int c = c_lo, i = i_lo;
+                const float* r = held_by(c) + i * RES;
+                for (int s = s_lo; s <= s_hi; ++s) {
+                    MM = fmaxf(MM, r[DH]);
+                    MLLM_NEXT_SPLIT(r, c, i);
+                }
+            }
             float LL = 0.f;
-            for (int s = s_lo; s <= s_hi; ++s) {
-                const float* r = cluster.map_shared_rank(sm_res, s);
-                LL = fmaf(expf(r[DH] - MM), r[DH + 1], LL);
+            {
+                int c = c_lo, i = i_lo;
+                const float* r = held_by(c) + i * RES;
+                for (int s = s_lo; s <= s_hi; ++s) {
+                    LL = fmaf(expf(r[DH] - MM), r[DH + 1], LL);
+                    MLLM_NEXT_SPLIT(r, c, i);
+                }
             }
             const float inv = 1.f / LL;
             for (int d = threadIdx.x; d < DH; d += THREADS) {
                 float acc = 0.f;
+                int c = c_lo, i = i_lo;
+                const float* r = held_by(c) + i * RES;
                 for (int s = s_lo; s <= s_hi; ++s) {
-                    const float* r = cluster.map_shared_rank(sm_res, s);
                     acc = fmaf(expf(r[DH] - MM), r[d], acc);
+                    MLLM_NEXT_SPLIT(r, c, i);
                 }
                 out[(size_t)t * out_stride + (size_t)h * DH + d] = from_f32<T>(acc * inv);
             }
+#undef MLLM_NEXT_SPLIT
         }
-        cluster.sync();                                       // nobody leaves while its memory may be read
+        if (remote) cluster.sync();                           // nobody leaves while its memory may be read
         return;
-    }
-    if (threadIdx.x == 0) {
-        part_ml[slot * 2] = M;
-        part_ml[slot * 2 + 1] = L;
     }
     // the CTA that arrives last merges the splits of this (token, head)
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned int n = (unsigned int)(s_hi - s_lo + 1);
+        const unsigned int n = (unsigned int)(c_hi - c_lo + 1);
         const unsigned int old = atomicAdd(&counters[pair], 1u);
         s_last = (old == n - 1);
         if (s_last) counters[pair] = 0;                      // ready for the next launch
@@ -239,36 +288,61 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
     }
 }
 
+int decode_sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
 template <typename T, int LPK>
 int launch(const void* q, long long q_stride, const void* k_pages, const void* v_pages, const int* block_table,
            int bt_stride, const int* token_seq, const int* positions, void* out, long long out_stride,
            float* part_o, float* part_ml, unsigned int* counters, int T_tokens, int H, int Hkv, int page_size,
            float scale, int window, int max_splits, bool scratch_path, cudaStream_t stream) {
-    dim3 grid(max_splits, H, T_tokens);
-    if (!scratch_path && max_splits <= MAX_CLUSTER) {
+    // CTAs per (token, head): few requests get one CTA per split, so that the chain position -> block table ->
+    // rows is as short as it can be; many requests let a CTA walk several splits, which keeps the number of
+    // CTAs near four per SM-slot instead of growing with the batch.  Which keys are added together, and in
+    // which order, is the same either way.
+    const long long pairs = (long long)T_tokens * H;
+    long long want = (4LL * decode_sm_count() + pairs - 1) / pairs;
+    int ctas = (int)(want < 1 ? 1 : (want > max_splits ? max_splits : want));
+    int spc = (max_splits + ctas - 1) / ctas;
+    if (spc > MAX_SPC) spc = MAX_SPC;
+    ctas = (max_splits + spc - 1) / spc;
+    dim3 grid(ctas, H, T_tokens);
+#define ARGS (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table, bt_stride, token_seq, positions, \
+             (T*)out, out_stride, part_o, part_ml, counters, H, Hkv, page_size, scale, window, max_splits, spc
+    if (!scratch_path && ctas == 1) {
+        MLLM_CUDA(mllm_launch(attn_decode_kernel<T, LPK, MODE_LOCAL, false>, grid, dim3(THREADS), 0, stream, true, ARGS));
+        return 0;
+    }
+    if (!scratch_path && ctas <= MAX_CLUSTER) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(THREADS);
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = max_splits;
+        attr[0].val.clusterDim.x = ctas;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
         attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = g_mllm_pdl ? 2 : 1;
-        MLLM_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel<T, LPK, true>, (const T*)q, q_stride, (const T*)k_pages,
-                                     (const T*)v_pages, block_table, bt_stride, token_seq, positions, (T*)out,
-                                     out_stride, part_o, part_ml, counters, H, Hkv, page_size, scale, window,
-                                     max_splits));
+        if (spc == 1) MLLM_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel<T, LPK, MODE_CLUSTER, true>, ARGS));
+        else MLLM_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel<T, LPK, MODE_CLUSTER, false>, ARGS));
         return 0;
     }
-    MLLM_CUDA(mllm_launch(attn_decode_kernel<T, LPK, false>, grid, dim3(THREADS), 0, stream, true, (const T*)q,
-                          q_stride, (const T*)k_pages, (const T*)v_pages, block_table, bt_stride, token_seq, positions,
-                          (T*)out, out_stride, part_o, part_ml, counters, H, Hkv, page_size, scale, window,
-                          max_splits));
+    if (spc == 1)
+        MLLM_CUDA(mllm_launch(attn_decode_kernel<T, LPK, MODE_SCRATCH, true>, grid, dim3(THREADS), 0, stream, true, ARGS));
+    else
+        MLLM_CUDA(mllm_launch(attn_decode_kernel<T, LPK, MODE_SCRATCH, false>, grid, dim3(THREADS), 0, stream, true, ARGS));
+#undef ARGS
     return 0;
 }
 

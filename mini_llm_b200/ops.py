@@ -242,6 +242,19 @@ def decode_splits(max_ctx_len: int) -> int:
     return max(1, -(-int(max_ctx_len) // DECODE_SPLIT))
 
 
+def _small_m_wins(M: int, N: int, K: int) -> bool:
+    """Whether the weight-streaming kernel (mma.sync, K split over warps) beats the tensor-memory
+    kernel for M rows.  Measured on GPT-2 small's shapes in a replayed graph: the streaming
+    kernel's time grows with M*N while the other stays near its fixed cost of about 6 us per 768
+    of K; with a long K the streaming kernel keeps winning up to its limit of 64 rows, and a
+    matrix as tall as a vocabulary is streamed faster by the tensor-memory kernel from 9 rows on."""
+    if M > SMALL_M:
+        return False
+    if N >= 16384:
+        return M <= 8
+    return K > 2048 or M * N <= 80_000
+
+
 def _fusable(weight, M, K) -> bool:
     return weight.dtype == torch.bfloat16 and M <= SMALL_M and K % 8 == 0 and weight.data_ptr() % 16 == 0
 
@@ -321,6 +334,7 @@ def linear(x, weight, bias, out, act: Optional[str] = None, accumulate: bool = F
     """
     if isinstance(x, NormedInput):
         if impl in (None, "smallm") and _fusable(weight, x.shape[0], weight.shape[1]) and _norm_ok(x) \
+                and (impl == "smallm" or _small_m_wins(x.shape[0], weight.shape[0], weight.shape[1])) \
                 and x.shape[1] == weight.shape[1] and tuple(out.shape) == (x.shape[0], weight.shape[0]):
             _cuda("out", out, contiguous=False)
             if bias is not None:
@@ -351,7 +365,7 @@ def linear(x, weight, bias, out, act: Optional[str] = None, accumulate: bool = F
         impl = "simt"
         if x.dtype == torch.bfloat16 and K % 8 == 0 and lda % 8 == 0 \
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
-            impl = "smallm" if M <= SMALL_M else "tcgen05"
+            impl = "smallm" if _small_m_wins(M, N, K) else "tcgen05"
         elif x.dtype == torch.float32 and out.dtype == torch.float32 and M <= SMALL_M_F32 and K % 4 == 0 \
                 and lda % 4 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
             impl = "smallm_f32"

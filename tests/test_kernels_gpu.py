@@ -371,6 +371,18 @@ def test_decode_attention_split_keys(ops, dtype, H, Hkv, dh, page, window):
         o1 = torch.empty_like(q[t:t + 1])
         ops.paged_attention(q[t:t + 1], kp, vp, bt, c1, o1, impl="decode", **kw)
         assert torch.equal(o1, out[t:t + 1])
+    # nor on the size of the batch: with many tokens a CTA walks several splits (down to one CTA per token
+    # and head), with few every split has its own CTA; the bits stay the same
+    for reps in (4, 20):
+        cb = _Ctx()
+        cb.token_seq, cb.positions = ctx.token_seq.repeat(reps), ctx.positions.repeat(reps)
+        cb.ws, cb.max_ctx_len, cb.decode_only = ctx.ws, ctx.max_ctx_len, True
+        qb = q.repeat(reps, 1)
+        ob = torch.empty_like(qb)
+        ops.paged_attention(qb, kp, vp, bt, cb, ob, impl="decode", **kw)
+        assert torch.equal(ob, out.repeat(reps, 1))
+        ops.paged_attention(qb, kp, vp, bt, cb, ob.zero_(), impl="decode_scratch", **kw)
+        assert torch.equal(ob, out.repeat(reps, 1))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
