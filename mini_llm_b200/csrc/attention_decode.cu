@@ -65,6 +65,22 @@ enum { MODE_SCRATCH = 0,     // partial results in global scratch; the CTA that 
 
 constexpr int MAX_SPC = 8;   // splits that one CTA may take, one after the other
 
+// e^x for the softmax.  The 32-bit path keeps expf; with a bfloat16 cache the scores are kept in base 2
+// (the query is scaled by log2 e as well) and one ex2.approx instruction, good to 2^-22, does it.
+template <typename T> struct Exp;
+template <> struct Exp<float> {
+    static constexpr float QSCALE = 1.f;
+    static __device__ __forceinline__ float of(float x) { return expf(x); }
+};
+template <> struct Exp<__nv_bfloat16> {
+    static constexpr float QSCALE = 1.4426950408889634f;
+    static __device__ __forceinline__ float of(float x) {
+        float y;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+        return y;
+    }
+};
+
 template <typename T, int LPK, int MODE, bool ONE>        // ONE: every CTA takes exactly one split
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
@@ -80,9 +96,12 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
     constexpr int KPG = SPLIT / NG;                   // keys per group in a split
     constexpr int UNR = KPG < 8 ? KPG : 8;            // keys in flight per group
     constexpr int RES = DH + 2;                       // a split's (o, m, l)
-    __shared__ float sm_m[NG], sm_l[NG];
+    // One split per CTA in a cluster: every CTA writes its (o, m, l) straight into the shared memory of the
+    // CTA that merges, so the merge reads local memory only and the others may leave after one barrier.
+    constexpr bool PUSH = MODE == MODE_CLUSTER && ONE;
+    __shared__ float sm_m[NG], sm_l[NG], sm_w[NG];
     __shared__ float sm_o[NG * DH];
-    __shared__ float sm_res[(MODE == MODE_SCRATCH || ONE ? 1 : MAX_SPC) * RES];
+    __shared__ float sm_res[(PUSH ? MAX_CLUSTER : MODE == MODE_SCRATCH || ONE ? 1 : MAX_SPC) * RES];
     __shared__ int s_last;
     const int cx = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
     pdl_wait();
@@ -107,16 +126,43 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
         }
         return;
     }
+    if constexpr (PUSH) {
+        // first barrier, arrival only: once it completes every CTA of the cluster runs and its shared memory
+        // may be written; it is waited for just before the results go out, long after it has completed
+        if (several) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    }
     const int hk = h / (H / Hkv);
     const int* bt = block_table + (size_t)seq * bt_stride;
     const int gi = threadIdx.x / LPK, li = threadIdx.x % LPK;
+    // page sizes are powers of two in practice: a shift and a mask instead of two divisions per key
+    const bool pow2 = (page_size & (page_size - 1)) == 0;
+    const int pshift = __ffs(page_size) - 1, pmask = page_size - 1;
+    auto page_index = [&](int kp) { return pow2 ? kp >> pshift : kp / page_size; };
+    auto page_offset = [&](int kp) { return pow2 ? kp & pmask : kp % page_size; };
 
     const uint4 qraw = *reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)h * DH + li * VEC);
     float qv[VEC];
     Vec16<T>::unpack(qraw, qv);
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) qv[i] *= scale;
+    for (int i = 0; i < VEC; ++i) qv[i] *= scale * Exp<T>::QSCALE;
     const size_t pair = (size_t)t * H + h;
+
+    if constexpr (!ONE) {
+        // A CTA that walks several splits asks for the rows of its later splits right away (into L2), one
+        // key per thread, so that HBM streams them while the first splits are computed.
+        const int k_end = min((my_hi + 1) * SPLIT, p + 1);
+        constexpr int ROW_BYTES = DH * (int)sizeof(T);
+#pragma unroll 4
+        for (int kp = (my_lo + 1) * SPLIT + (int)threadIdx.x; kp < k_end; kp += THREADS) {
+            if (kp < first) continue;
+            const size_t off = (((size_t)bt[page_index(kp)] * Hkv + hk) * page_size + page_offset(kp)) * DH;
+#pragma unroll
+            for (int b = 0; b < ROW_BYTES; b += 128) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(k_pages + off) + b));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(v_pages + off) + b));
+            }
+        }
+    }
 
 #pragma unroll 1
     for (int split = my_lo; split <= my_hi; ++split) {
@@ -132,7 +178,7 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
             for (int u = 0; u < UNR; ++u) {
                 const int kp = kb + u * NG;
                 ok[u] = kp < k_hi && kp >= first;
-                page[u] = ok[u] ? bt[kp / page_size] : 0;
+                page[u] = ok[u] ? bt[page_index(kp)] : 0;
             }
             uint4 kr[UNR], vr[UNR];
 #pragma unroll
@@ -141,7 +187,7 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
                 kr[u] = make_uint4(0, 0, 0, 0);
                 vr[u] = make_uint4(0, 0, 0, 0);
                 if (ok[u]) {
-                    const size_t off = (((size_t)page[u] * Hkv + hk) * page_size + kp % page_size) * DH + li * VEC;
+                    const size_t off = (((size_t)page[u] * Hkv + hk) * page_size + page_offset(kp)) * DH + li * VEC;
                     kr[u] = *reinterpret_cast<const uint4*>(k_pages + off);
                     vr[u] = *reinterpret_cast<const uint4*>(v_pages + off);
                 }
@@ -161,13 +207,13 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
                 mx = fmaxf(mx, s[u]);
             }
             if (mx != -INFINITY) {                               // uniform within the group; no shuffles inside
-                const float alpha = expf(m - mx);
+                const float alpha = Exp<T>::of(m - mx);
                 l *= alpha;
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) o[i] *= alpha;
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) {
-                    const float pr = ok[u] ? expf(s[u] - mx) : 0.f;
+                    const float pr = ok[u] ? Exp<T>::of(s[u] - mx) : 0.f;
                     float vv[VEC];
                     Vec16<T>::unpack(vr[u], vv);
                     l += pr;
@@ -184,19 +230,22 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
         __syncthreads();
         float M = -INFINITY;
         for (int g = 0; g < NG; ++g) M = fmaxf(M, sm_m[g]);
+        if (threadIdx.x < NG)                                 // every group's weight in the merge, computed once
+            sm_w[threadIdx.x] = sm_m[threadIdx.x] == -INFINITY ? 0.f : Exp<T>::of(sm_m[threadIdx.x] - M);
+        __syncthreads();
         float L = 0.f;
-        for (int g = 0; g < NG; ++g) {
-            const float w = sm_m[g] == -INFINITY ? 0.f : expf(sm_m[g] - M);
-            L = fmaf(w, sm_l[g], L);
-        }
+        for (int g = 0; g < NG; ++g) L = fmaf(sm_w[g], sm_l[g], L);
         const size_t slot = pair * max_splits + split;
         float* res = sm_res + (MODE == MODE_SCRATCH ? 0 : (split - cx * spc) * RES);
+        if constexpr (PUSH) {
+            if (several) {
+                asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+                res = cg::this_cluster().map_shared_rank(sm_res, c_lo) + cx * RES;      // slot `split` of the merging CTA
+            }
+        }
         for (int d = threadIdx.x; d < DH; d += THREADS) {
             float acc = 0.f;
-            for (int g = 0; g < NG; ++g) {
-                const float w = sm_m[g] == -INFINITY ? 0.f : expf(sm_m[g] - M);
-                acc = fmaf(w, sm_o[g * DH + d], acc);
-            }
+            for (int g = 0; g < NG; ++g) acc = fmaf(sm_w[g], sm_o[g * DH + d], acc);
             if (single) out[(size_t)t * out_stride + (size_t)h * DH + d] = from_f32<T>(acc / L);
             else if (MODE == MODE_SCRATCH) part_o[slot * DH + d] = acc;
             else res[d] = acc;
@@ -213,12 +262,19 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
         // every split's (o, m, l) stays in the shared memory of the CTA that computed it; the CTA with the
         // first split collects them in split order - over the SM-to-SM network where another CTA holds them
         cg::cluster_group cluster = cg::this_cluster();
-        const bool remote = MODE == MODE_CLUSTER && several;
-        if (remote) cluster.sync();                           // every split's result is in place
-        else __syncthreads();
+        const bool remote = MODE == MODE_CLUSTER && several && !PUSH;
+        if (PUSH) {
+            cluster.sync();                                   // second barrier: every split's result has arrived
+            if (cx != c_lo) return;
+        } else if (remote) {
+            cluster.sync();                                   // every split's result is in place
+        } else {
+            __syncthreads();
+        }
         if (cx == c_lo) {
             // walks the splits s_lo..s_hi: CTA c holds the splits c*spc .. c*spc+spc-1 in that order
             auto held_by = [&](int c) -> const float* {
+                if (PUSH) return sm_res + c * RES;            // pushed here, one slot per CTA
                 return (remote && c <= c_hi) ? cluster.map_shared_rank(sm_res, c) : sm_res;
             };
             const int i_lo = s_lo - c_lo * spc;               // index of the first split inside its CTA
@@ -241,7 +297,7 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
                 int c = c_lo, i = i_lo;
                 const float* r = held_by(c) + i * RES;
                 for (int s = s_lo; s <= s_hi; ++s) {
-                    LL = fmaf(expf(r[DH] - MM), r[DH + 1], LL);
+                    LL = fmaf(Exp<T>::of(r[DH] - MM), r[DH + 1], LL);
                     MLLM_NEXT_SPLIT(r, c, i);
                 }
             }
@@ -251,7 +307,7 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
                 int c = c_lo, i = i_lo;
                 const float* r = held_by(c) + i * RES;
                 for (int s = s_lo; s <= s_hi; ++s) {
-                    acc = fmaf(expf(r[DH] - MM), r[d], acc);
+                    acc = fmaf(Exp<T>::of(r[DH] - MM), r[d], acc);
                     MLLM_NEXT_SPLIT(r, c, i);
                 }
                 out[(size_t)t * out_stride + (size_t)h * DH + d] = from_f32<T>(acc * inv);
@@ -278,12 +334,12 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
     for (int s = s_lo; s <= s_hi; ++s) MM = fmaxf(MM, __ldcg(&part_ml[(base + s) * 2]));
     float LL = 0.f;
     for (int s = s_lo; s <= s_hi; ++s)
-        LL = fmaf(expf(__ldcg(&part_ml[(base + s) * 2]) - MM), __ldcg(&part_ml[(base + s) * 2 + 1]), LL);
+        LL = fmaf(Exp<T>::of(__ldcg(&part_ml[(base + s) * 2]) - MM), __ldcg(&part_ml[(base + s) * 2 + 1]), LL);
     const float inv = 1.f / LL;
     for (int d = threadIdx.x; d < DH; d += THREADS) {
         float acc = 0.f;
         for (int s = s_lo; s <= s_hi; ++s)
-            acc = fmaf(expf(__ldcg(&part_ml[(base + s) * 2]) - MM), __ldcg(&part_o[(base + s) * DH + d]), acc);
+            acc = fmaf(Exp<T>::of(__ldcg(&part_ml[(base + s) * 2]) - MM), __ldcg(&part_o[(base + s) * DH + d]), acc);
         out[(size_t)t * out_stride + (size_t)h * DH + d] = from_f32<T>(acc * inv);
     }
 }
@@ -310,6 +366,8 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
     const long long pairs = (long long)T_tokens * H;
     long long want = (4LL * decode_sm_count() + pairs - 1) / pairs;
     int ctas = (int)(want < 1 ? 1 : (want > max_splits ? max_splits : want));
+    // measured: one split per CTA stays ahead until the grid reaches about 24 CTAs per SM
+    if (max_splits <= MAX_CLUSTER && pairs * max_splits <= 24LL * decode_sm_count()) ctas = max_splits;
     int spc = (max_splits + ctas - 1) / ctas;
     if (spc > MAX_SPC) spc = MAX_SPC;
     ctas = (max_splits + spc - 1) / spc;
