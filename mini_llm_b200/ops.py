@@ -311,7 +311,7 @@ def linear_qkv_cache(x, weight, bias, q_out, k_pages, v_pages, slot_mapping, ws)
     norm = x if isinstance(x, NormedInput) else None
     if norm is not None and not _norm_ok(norm):
         x, norm = norm.materialize(), None
-    if q_out.dtype == torch.bfloat16 and _fusable(weight, M, K) and (
+    if q_out.dtype == torch.bfloat16 and _fusable(weight, M, K) and _small_m_wins(M, N, K) and (
             _norm_ok(norm) if norm is not None else
             (x.is_cuda and x.dtype == torch.bfloat16 and _rows("x", x) % 8 == 0 and x.data_ptr() % 16 == 0)):
         if bias is not None:
