@@ -23,119 +23,17 @@
 //
 // The reference multiplies with FP32 SIMT tiles (src/kernels/gemm.cu:238-580), or cuBLAS
 // SGEMM when MINI_LLM_USE_CUBLAS is set (:119-156); it has no tensor-core path.
-#include "common.cuh"
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
+#include "tcgen05.cuh"
 
 namespace {
+
+using namespace tc;
 
 constexpr int BM = 128, BK = 64;
 constexpr int EPI_WARPS = 8;                  // two per quarter of the tensor-memory lanes
 constexpr int THREADS = (2 + EPI_WARPS) * 32;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;     // two seconds, then the wait gives up
 
 __device__ int g_tc_error = 0;          // first error code seen by any tcgen05 kernel
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait; false when the limit was hit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    unsigned long long t0 = 0;
-    for (uint32_t i = 0;; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-        if ((i & 63) == 63) {
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_NS) return false;
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, const void* smem_src) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                 ::"l"(map), "r"(x), "r"(y), "r"(smem_u32(smem_src)) : "memory");
-}
-__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, const void* smem_src) {
-    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
-                 ::"l"(map), "r"(x), "r"(y), "r"(smem_u32(smem_src)) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols));
-}
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// Starts the load of 32 columns; the registers are valid after tmem_ld_wait().
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 64
-// bf16 (128 bytes), groups of 8 rows 1024 bytes apart; version 1 (Blackwell), layout
-// type 2 (SWIZZLE_128B), leading offset 1 (unused for swizzled K-major).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-// Instruction descriptor: D=F32 (bits 4-5 = 1), A=B=BF16 (bits 7-9, 10-12 = 1), both
-// K-major (bits 15, 16 = 0), N>>3 at bit 17, M>>4 at bit 24.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
 
 constexpr int tmem_cols(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn <= 128 ? 128 : 256; }
 
@@ -446,73 +344,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
 }
 
-// ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; long long ld; int rows, cols, box_rows, kind;
-    bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && ld == o.ld && rows == o.rows && cols == o.cols && box_rows == o.box_rows && kind == o.kind;
-    }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        size_t h = (size_t)k.ptr;
-        h = h * 1000003u ^ (size_t)k.ld;
-        h = h * 1000003u ^ (size_t)k.rows;
-        h = h * 1000003u ^ (size_t)k.cols;
-        h = h * 1000003u ^ (size_t)(k.box_rows * 4 + k.kind);
-        return h;
-    }
-};
-
-// Kinds of tensor maps over a row-major [rows, cols] matrix with row stride ld (elements):
-//   MAP_OPERAND  bfloat16, boxes of box_rows x 64 (128 bytes), 128-byte swizzle: the MMA operands
-//   MAP_OUT_F32  32-bit,   boxes of 32 x 32 (128 bytes),       128-byte swizzle: the epilogue's blocks
-//   MAP_OUT_BF16 bfloat16, boxes of 32 x 32 (64 bytes),        64-byte swizzle
-enum { MAP_OPERAND = 0, MAP_OUT_F32 = 1, MAP_OUT_BF16 = 2 };
-
-int get_map(const void* ptr, long long ld, int rows, int cols, int box_rows, int kind, CUtensorMap* out) {
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    static std::mutex mu;
-    MapKey key{ptr, ld, rows, cols, box_rows, kind};
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return 0; }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return mllm_fail(3, "linear_tcgen05: cuTensorMapEncodeTiled is not available from the driver");
-    const int es = kind == MAP_OUT_F32 ? 4 : 2;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * es};
-    cuuint32_t box[2] = {(cuuint32_t)(kind == MAP_OPERAND ? BK : 32), (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUtensorMap m;
-    CUresult r = fn(&m, kind == MAP_OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    kind == MAP_OUT_BF16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return mllm_fail(3, "linear_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
-    if (cache.size() > 4096) cache.clear();
-    cache.emplace(key, m);
-    *out = m;
-    return 0;
-}
-
 int sm_count() {
     static int n = 0;
     if (!n) {
@@ -529,16 +360,16 @@ int launch(const void* A, long long lda, const void* W, const float* bias, void*
     using C = Cfg<BN>;
     static_assert(C::STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of swizzled tiles");
     CUtensorMap ma, mw, mo;
-    int rc = get_map(A, lda, M, K, BM, MAP_OPERAND, &ma);
+    int rc = get_map(A, lda, M, K, BK, BM, MAP_BF16_SW128, &ma);
     if (rc) return rc;
-    rc = get_map(W, K, N, K, BN, MAP_OPERAND, &mw);
+    rc = get_map(W, K, N, K, BK, BN, MAP_BF16_SW128, &mw);
     if (rc) return rc;
     // The copy engine writes the result when its rows are 16-byte aligned; a residual sum goes through
     // it only in 32-bit (its bfloat16 addition would round the new term before adding).
     const int tma_out = (uintptr_t)out % 16 == 0 && (ldo * (long long)sizeof(TO)) % 16 == 0 &&
                         !(accumulate && sizeof(TO) == 2);
     if (tma_out) {
-        rc = get_map(out, ldo, M, N, 32, sizeof(TO) == 4 ? MAP_OUT_F32 : MAP_OUT_BF16, &mo);
+        rc = get_map(out, ldo, M, N, 32, 32, sizeof(TO) == 4 ? MAP_F32_SW128 : MAP_BF16_SW64, &mo);
         if (rc) return rc;
     } else {
         mo = ma;                                       // not used by the kernel

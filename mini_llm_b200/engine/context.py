@@ -38,16 +38,18 @@ class StepLayout:
     R: int
     max_pages: Tuple[int, ...]
     n_tiles: int = 0
+    n_tiles_wide: int = 0
     offsets: Dict[str, int] = field(default_factory=dict)
     total: int = 0
 
     @classmethod
-    def make(cls, T: int, S: int, R: int, max_pages: Sequence[int], n_tiles: int = 0) -> "StepLayout":
-        lay = cls(T, S, R, tuple(max_pages), n_tiles)
+    def make(cls, T: int, S: int, R: int, max_pages: Sequence[int], n_tiles: int = 0,
+             n_tiles_wide: int = 0) -> "StepLayout":
+        lay = cls(T, S, R, tuple(max_pages), n_tiles, n_tiles_wide)
         off = 0
         for name, n in (("token_ids", T), ("positions", T), ("token_seq", T), ("logit_rows", R),
                         ("state_slots", S), ("cu_q", S + 1), ("q_start", S), ("ctx_len", S),
-                        ("attn_tiles", 3 * n_tiles)):
+                        ("attn_tiles", 3 * n_tiles), ("attn_tiles_wide", 3 * n_tiles_wide)):
             lay.offsets[name] = off
             off += _pad4(n)
         for g, mp in enumerate(max_pages):
@@ -59,7 +61,7 @@ class StepLayout:
         return lay
 
     def key(self):
-        return (self.T, self.S, self.R, self.max_pages, self.n_tiles)
+        return (self.T, self.S, self.R, self.max_pages, self.n_tiles, self.n_tiles_wide)
 
 
 class Workspace:
@@ -133,6 +135,9 @@ class StepContext:
         # query tiles of the tensor-core attention: (request index, first flat token, rows)
         self.attn_tiles = sec("attn_tiles", 3 * layout.n_tiles)
         self.n_tiles = layout.n_tiles
+        # the same tokens cut into tiles of ATTN_TILE_WIDE rows, for the tcgen05 attention
+        self.attn_tiles_wide = sec("attn_tiles_wide", 3 * layout.n_tiles_wide)
+        self.n_tiles_wide = layout.n_tiles_wide
         self.groups: List[GroupView] = []
         for g, mp in enumerate(layout.max_pages):
             bt = dev[o[f"block_table.{g}"]:o[f"block_table.{g}"] + self.S * mp].view(self.S, mp)
@@ -148,11 +153,13 @@ class StepContext:
         self.decode_only = self.max_q_len == 1
 
 
-ATTN_TILE = 64      # query rows per tile of csrc/attention_flash.cu
+ATTN_TILE = 64      # query rows per tile of csrc/attention_flash.cu and attention_tiled.cu
+ATTN_TILE_WIDE = 128     # query rows per tile of csrc/attention_tcgen05.cu
 
 
-def attention_tiles(q_lens: Sequence[int], q_starts: Optional[Sequence[int]] = None) -> List[int]:
-    """Cut every request's new tokens into tiles of at most ATTN_TILE rows: triples of
+def attention_tiles(q_lens: Sequence[int], q_starts: Optional[Sequence[int]] = None,
+                    tile_rows: int = ATTN_TILE) -> List[int]:
+    """Cut every request's new tokens into tiles of at most ``tile_rows`` rows: triples of
     (request index in the batch, flat index of the tile's first token, rows).  With the
     positions at which the portions start, the tiles that see the most keys come first,
     so that the longest walks of the attention kernel start earliest."""
@@ -160,8 +167,8 @@ def attention_tiles(q_lens: Sequence[int], q_starts: Optional[Sequence[int]] = N
     base = 0
     for s, n in enumerate(q_lens):
         start = 0 if q_starts is None else int(q_starts[s])
-        for q0 in range(0, n, ATTN_TILE):
-            rows = min(ATTN_TILE, n - q0)
+        for q0 in range(0, n, tile_rows):
+            rows = min(tile_rows, n - q0)
             tiles.append((start + q0 + rows, s, base + q0, rows))
         base += n
     if q_starts is not None:
@@ -173,7 +180,7 @@ def attention_tiles(q_lens: Sequence[int], q_starts: Optional[Sequence[int]] = N
 
 
 def pack_step(layout: StepLayout, host: np.ndarray, *, token_ids, positions, token_seq, logit_rows, state_slots,
-              cu_q, q_start, ctx_len, slot_mappings, block_tables, attn_tiles=()) -> None:
+              cu_q, q_start, ctx_len, slot_mappings, block_tables, attn_tiles=(), attn_tiles_wide=()) -> None:
     """Write every section into the int32 array ``host`` (length >= layout.total)."""
     o = layout.offsets
 
@@ -191,6 +198,8 @@ def pack_step(layout: StepLayout, host: np.ndarray, *, token_ids, positions, tok
     put("ctx_len", ctx_len)
     if layout.n_tiles:
         put("attn_tiles", attn_tiles)
+    if layout.n_tiles_wide:
+        put("attn_tiles_wide", attn_tiles_wide)
     for g, mp in enumerate(layout.max_pages):
         put(f"slot_mapping.{g}", slot_mappings[g])
         bt = np.zeros((layout.S, mp), dtype=np.int32)

@@ -21,7 +21,7 @@ from ..cache.manager import CacheManager
 from ..config.base import EngineConfig, ModelConfig, get_architecture, load_config
 from ..parts.model import Model
 from ..weights.loader import load_weights
-from .context import StepContext, StepLayout, Workspace, attention_tiles, pack_step
+from .context import ATTN_TILE_WIDE, StepContext, StepLayout, Workspace, attention_tiles, pack_step
 
 
 class StepError(RuntimeError):
@@ -233,12 +233,13 @@ class ModelRunner:
             mp = max(len(t) for t in tables[g])
             max_pages.append(max(16, 1 << (mp - 1).bit_length()))   # powers of two: few distinct shapes for captured graphs
         tiles = [] if T == S else attention_tiles(q_lens, q_start)
-        layout = StepLayout.make(T, S, len(logit_rows), max_pages, len(tiles) // 3)
+        wide = [] if T == S else attention_tiles(q_lens, q_start, ATTN_TILE_WIDE)
+        layout = StepLayout.make(T, S, len(logit_rows), max_pages, len(tiles) // 3, len(wide) // 3)
         i, host = self._staging(layout.total)
         self._last_layout_total = layout.total
         pack_step(layout, host.numpy(), token_ids=token_ids, positions=positions, token_seq=token_seq,
                   logit_rows=logit_rows, state_slots=slots, cu_q=cu_q, q_start=q_start, ctx_len=ctx_len,
-                  slot_mappings=slot_maps, block_tables=tables, attn_tiles=tiles)
+                  slot_mappings=slot_maps, block_tables=tables, attn_tiles=tiles, attn_tiles_wide=wide)
         self._dev[:layout.total].copy_(host[:layout.total], non_blocking=True)
         self._host_events[i].record()
         self._pending_ids = pending

@@ -61,6 +61,9 @@ def _signatures(lib):
                                   c_int, c_int, c_int, c_int, c_void_p],
         "mllm_attention_flash": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                  c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "mllm_attention_tcgen05": [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                                   c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "mllm_attention_tcgen05_error": [c_void_p],
         "mllm_attention_tiled": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                  c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "mllm_argmax": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
@@ -120,6 +123,11 @@ def check_device_errors() -> None:
         who = {1: "the TMA producer (no free stage)", 2: "the MMA issuer (no full stage)",
                3: "the epilogue (accumulator never ready)"}.get(code.value, "?")
         raise KernelError(f"a tcgen05 kernel gave up waiting: code {code.value}, {who}")
+    if lib.mllm_attention_tcgen05_error(ctypes.byref(code)) != 0:
+        raise KernelError(lib.mllm_last_error().decode(errors="replace"))
+    if code.value:
+        raise KernelError(f"the tcgen05 attention kernel gave up waiting: code {code.value} "
+                          "(1 producer, 2-6 MMA issuer, 7-8 softmax warps)")
 
 
 _stream_handle = None     # set by stream_scope(); None: ask torch on every call
@@ -405,6 +413,15 @@ def kv_write(k, v, k_pages, v_pages, slot_mapping) -> None:
           slot_mapping.data_ptr(), T, Hkv, dh, ps, _dt(k), _stream())
 
 
+attention_launches = {}     # attention kernel name -> launches so far (tests check which kernel a step took)
+
+
+def _flash_tc_ok(q, k_pages, out, ctx, head_dim, ps, ldq, ldo) -> bool:
+    return (q.dtype == torch.bfloat16 and head_dim == 64 and 8 <= ps <= 128 and ps & (ps - 1) == 0
+            and getattr(ctx, "n_tiles_wide", 0) > 0 and ldq % 8 == 0 and q.data_ptr() % 16 == 0 and ldo % 8 == 0
+            and out.data_ptr() % 16 == 0 and k_pages.is_contiguous() and k_pages.data_ptr() % 16 == 0)
+
+
 def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, num_kv_heads, head_dim, scale,
                     window=None, impl: Optional[str] = None) -> None:
     """Causal attention of the step's tokens over the cache.
@@ -431,16 +448,28 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
         if getattr(ctx, "decode_only", False) and head_dim in _DECODE_HEAD_DIMS[q.dtype] and ldq % 8 == 0 \
                 and q.data_ptr() % 16 == 0:
             impl = "decode"
+        elif _flash_tc_ok(q, k_pages, out, ctx, head_dim, ps, ldq, ldo) and ctx.T >= 256:
+            impl = "flash_tc"       # long prompt portions: the tensor-memory kernel
         elif q.dtype == torch.bfloat16 and head_dim in _FLASH_HEAD_DIMS and getattr(ctx, "n_tiles", 0) > 0 \
                 and ldq % 8 == 0 and q.data_ptr() % 16 == 0 and ldo % 2 == 0:
             impl = "flash"
         elif getattr(ctx, "n_tiles", 0) > 0:
             impl = "tiled"          # float32, or a head size the tensor-core kernel does not take
+    attention_launches[impl] = attention_launches.get(impl, 0) + 1
     if impl == "tiled":
         _call("mllm_attention_tiled", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(),
               block_table.data_ptr(), bt_stride, ctx.attn_tiles.data_ptr(), int(ctx.n_tiles),
               ctx.positions.data_ptr(), out.data_ptr(), ldo, num_heads, num_kv_heads, head_dim, ps, float(scale),
               int(window or 0), _dt(q), _stream())
+        return
+    if impl == "flash_tc":
+        if not _flash_tc_ok(q, k_pages, out, ctx, head_dim, ps, ldq, ldo):
+            raise KernelError("paged_attention: the tcgen05 kernel takes bfloat16, head size 64, pages of 8..128 "
+                              "tokens (a power of two), 16-byte aligned rows and a list of 128-row tiles")
+        _call("mllm_attention_tcgen05", q.data_ptr(), ldq, T, k_pages.data_ptr(), v_pages.data_ptr(),
+              int(k_pages.shape[0]), block_table.data_ptr(), bt_stride, ctx.attn_tiles_wide.data_ptr(),
+              int(ctx.n_tiles_wide), ctx.positions.data_ptr(), out.data_ptr(), ldo, num_heads, num_kv_heads, head_dim,
+              ps, float(scale), int(window or 0), _stream())
         return
     if impl == "flash":
         if q.dtype != torch.bfloat16 or head_dim not in _FLASH_HEAD_DIMS:

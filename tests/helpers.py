@@ -22,8 +22,13 @@ CONFIG_A = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=2,
 CONFIG_B = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=3, n_embd=96, n_head=3,
                 n_inner=320, vocab_size=1000, n_positions=256, layer_norm_epsilon=1e-6,
                 activation_function="gelu", scale_attn_by_inverse_layer_idx=True, eos_token_id=999)
-PAGE_SIZE = {"A": 16, "B": 8}
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B}
+# A third one with heads of 64 and room for long prompts: the sizes at which the tensor-memory attention
+# kernel (128-query tiles, 128-key blocks) takes over from the others.
+CONFIG_C = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=2, n_embd=128, n_head=2,
+                n_inner=192, vocab_size=300, n_positions=704, layer_norm_epsilon=1e-5,
+                activation_function="gelu_new", scale_attn_by_inverse_layer_idx=True, eos_token_id=299)
+PAGE_SIZE = {"A": 16, "B": 8, "C": 32}
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
 
 
 def make_tensors(cfg: dict, seed: int, sharp: bool = True) -> Dict[str, torch.Tensor]:

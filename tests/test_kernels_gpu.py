@@ -458,6 +458,58 @@ def test_flash_attention_mixed_batch(ops, H, Hkv, dh, page, window):
         assert torch.equal(part, whole[lo:hi]), (lo, hi)
 
 
+@pytest.mark.parametrize("H,Hkv,page,window", [(2, 2, 16, None), (12, 12, 16, None), (6, 2, 8, None), (3, 1, 32, None),
+                                               (2, 2, 128, None), (4, 1, 16, 37), (2, 2, 64, 200)])
+def test_tcgen05_attention_mixed_batch(ops, H, Hkv, page, window):
+    """The tensor-memory attention (128-query tiles, 128-key blocks, head size 64): prompt portions of
+    many lengths (tile edges at 128, page edges, portions that start in the middle of a key block) beside
+    single tokens, against float64 and the plain kernel; the same queries cut differently give the same bits."""
+    from mini_llm_b200.engine.context import ATTN_TILE_WIDE, attention_tiles
+    dtype, dh = torch.bfloat16, 64
+    seqs = [(1, 1), (70, 1), (33, 33), (100, 7), (16, 2), (129, 129), (128, 128), (65, 65), (200, 63), (500, 300),
+            (256, 128), (191, 2), (640, 257)]
+    case = _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages=2800 // page + 40, seed=H + page)
+    ctx = _ctx_for(case)
+    ctx.decode_only = False
+    starts = [c - ql for c, ql in seqs]
+    tiles = attention_tiles([ql for _, ql in seqs], starts, ATTN_TILE_WIDE)
+    ctx.attn_tiles_wide = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    ctx.n_tiles_wide = len(tiles) // 3
+    q = case["q"].to(dtype).to(DEV)
+    kp, vp, bt = case["k_pages"].to(dtype).to(DEV), case["v_pages"].to(dtype).to(DEV), case["bt"].to(DEV)
+    scale = dh ** -0.5
+    kw = dict(num_heads=H, num_kv_heads=Hkv, head_dim=dh, scale=scale, window=window)
+    out, plain = torch.full_like(q, 7.0), torch.empty_like(q)
+    ops.paged_attention(q, kp, vp, bt, ctx, out, impl="flash_tc", **kw)
+    ops.check_device_errors()
+    ops.paged_attention(q, kp, vp, bt, ctx, plain, impl="simt", **kw)
+    want = _attention_reference(case, H, Hkv, dh, scale, window, dtype)
+    mag = want.abs().clamp(min=1.0)
+    err = ((out.double().cpu() - want).abs() / mag).max(dim=1).values
+    assert err.max() < 1e-2, (int(err.argmax()), float(err.max()))
+    assert ((out.double() - plain.double()).abs().cpu() / mag).max() < 2 ** -7 * 1.05
+    # the same queries cut differently give the same bits
+    c2 = _paged_case(dtype, [(300, 300)], H, Hkv, dh, page, num_pages=2800 // page + 40, seed=99)
+    ctxa = _ctx_for(c2)
+    ctxa.decode_only = False
+    ta = attention_tiles([300], [0], ATTN_TILE_WIDE)
+    ctxa.attn_tiles_wide, ctxa.n_tiles_wide = torch.tensor(ta, dtype=torch.int32, device=DEV), len(ta) // 3
+    q2 = c2["q"].to(dtype).to(DEV)
+    args2 = (c2["k_pages"].to(dtype).to(DEV), c2["v_pages"].to(dtype).to(DEV), c2["bt"].to(DEV))
+    whole = torch.empty_like(q2)
+    ops.paged_attention(q2, *args2, ctxa, whole, impl="flash_tc", **kw)
+    for lo, hi in ((0, 5), (5, 70), (70, 300), (100, 101), (127, 260)):
+        cb = _Ctx()
+        cb.token_seq = torch.zeros(hi - lo, dtype=torch.int32, device=DEV)
+        cb.positions = torch.arange(lo, hi, dtype=torch.int32, device=DEV)
+        tb = attention_tiles([hi - lo], [lo], ATTN_TILE_WIDE)
+        cb.attn_tiles_wide, cb.n_tiles_wide, cb.decode_only = torch.tensor(tb, dtype=torch.int32, device=DEV), len(tb) // 3, False
+        part = torch.empty_like(q2[lo:hi])
+        ops.paged_attention(q2[lo:hi], *args2, cb, part, impl="flash_tc", **kw)
+        assert torch.equal(part, whole[lo:hi]), (lo, hi)
+    ops.check_device_errors()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,Hkv,dh,page,window", [(4, 4, 16, 16, None), (3, 3, 32, 8, None), (12, 12, 64, 16, None),
                                                   (5, 1, 48, 4, None), (2, 2, 128, 32, 100), (2, 1, 256, 16, None),

@@ -125,3 +125,66 @@ def test_mixed_with_page_reuse(setup, tmp_path):
     assert rp.close() == 0
     for r in order:
         assert_close(np.concatenate(got[r]), reqs[r][1], setup["dtype"], f"mixed {r}")
+
+
+# ---------------------------------------------------------------------------------- long prompts, heads of 64
+@pytest.fixture(scope="module", params=["float32", "bfloat16"])
+def long_setup(request, tmp_path_factory):
+    dtype = request.param
+    d = str(tmp_path_factory.mktemp(f"model_C_{dtype}"))
+    make_model(d, "C", seed=31, dtype=STORE[dtype])
+    cfg, w = plain_gpt2.read_model(d)
+    reqs = {}
+    for i, n in enumerate([700, 300, 513]):
+        ids = random_ids(n, cfg["vocab_size"], 500 + i)
+        reqs[f"c{i}"] = (ids, plain_gpt2.forward_logits(cfg, w, ids, oracle_store(dtype)).numpy())
+    return dict(dtype=dtype, dir=d, cfg=cfg, reqs=reqs, page=PAGE_SIZE["C"])
+
+
+def test_long_prompts_whole_and_in_long_portions(long_setup, tmp_path):
+    """Prompts of several hundred tokens with heads of 64: whole, then in portions whose edges fall inside
+    query tiles and key blocks (one of them long enough for the tensor-memory attention kernel on the
+    bfloat16 path), then both beside a decoding request."""
+    dtype = long_setup["dtype"]
+    rp = Replay(long_setup["dir"], dtype, str(tmp_path), round64(704) * 3, long_setup["page"])
+    reqs = long_setup["reqs"]
+    for rid, (ids, want) in reqs.items():
+        n = len(ids)
+        places = sorted(set([0, 1, 63, 127, 128, 129, 255, 256, 257, n // 2, n - 2, n - 1]) & set(range(n)))
+        got = rp.step([(rid, ids, places)], end=[rid])
+        assert_close(got, want[places], dtype, f"whole {rid}")
+    # portions: 290 + 300 + the rest, the last logits of every portion and a few inside
+    ids, want = reqs["c0"]
+    cuts = [0, 290, 590, 700]
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        places = [0, (b - a) // 2, b - a - 1]
+        got = rp.step([("p", ids[a:b], places)])
+        assert_close(got, want[[a + p for p in places]], dtype, f"portion {a}:{b}")
+    rp.step([], end=["p"])
+    # two long portions of different requests in one step beside a single decoded token of a third
+    i1, w1 = reqs["c1"]
+    i2, w2 = reqs["c2"]
+    rp.step([("d", ids[:600], [])])
+    got = rp.step([("x", i1[:260], [259]), ("d", [ids[600]], [0]), ("y", i2[:400], [0, 399])])
+    assert_close(got, np.stack([w1[259], want[600], w2[0], w2[399]]), dtype, "mixed long portions")
+    got = rp.step([("x", i1[260:], [39]), ("y", i2[400:], [112]), ("d", ids[601:603], [1])], end=["x", "y", "d"])
+    assert_close(got, np.stack([w1[299], w2[512], want[602]]), dtype, "mixed, second step")
+    assert rp.close() == 0
+
+
+def test_long_portions_take_the_tensor_memory_attention(long_setup):
+    """The step function itself: a 600-token portion on the bfloat16 path goes through the tcgen05 attention."""
+    if long_setup["dtype"] != "bfloat16":
+        pytest.skip("the 32-bit path has its own attention kernels")
+    from mini_llm_b200 import ops
+    from mini_llm_b200.config.base import EngineConfig
+    from mini_llm_b200.engine.runner import ModelRunner, StepEntry
+    runner = ModelRunner(long_setup["dir"], EngineConfig(dtype="bfloat16", page_size=long_setup["page"], max_tokens=1408,
+                                                         max_num_seqs=2, max_num_batched_tokens=1024))
+    ids, want = long_setup["reqs"]["c0"]
+    before = ops.attention_launches.get("flash_tc", 0)
+    runner.add_request("a")
+    got = runner.step([StepEntry("a", ids[:600], [0, 300, 599])]).cpu().numpy()
+    assert ops.attention_launches.get("flash_tc", 0) == before + long_setup["cfg"]["n_layer"]
+    assert_close(got, want[[0, 300, 599]], "bfloat16", "600-token portion")
+    ops.check_device_errors()
