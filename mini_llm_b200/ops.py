@@ -448,8 +448,9 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
         if getattr(ctx, "decode_only", False) and head_dim in _DECODE_HEAD_DIMS[q.dtype] and ldq % 8 == 0 \
                 and q.data_ptr() % 16 == 0:
             impl = "decode"
-        elif _flash_tc_ok(q, k_pages, out, ctx, head_dim, ps, ldq, ldo) and ctx.T >= 256:
-            impl = "flash_tc"       # long prompt portions: the tensor-memory kernel
+        elif _flash_tc_ok(q, k_pages, out, ctx, head_dim, ps, ldq, ldo) and ctx.T >= 256 \
+                and ctx.T >= 80 * ctx.n_tiles_wide:
+            impl = "flash_tc"       # long prompt portions (tiles of 128 rows mostly full): the tensor-memory kernel
         elif q.dtype == torch.bfloat16 and head_dim in _FLASH_HEAD_DIMS and getattr(ctx, "n_tiles", 0) > 0 \
                 and ldq % 8 == 0 and q.data_ptr() % 16 == 0 and ldo % 2 == 0:
             impl = "flash"
