@@ -345,9 +345,14 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--profile-step", choices=["prefill", "decode"],
                     help="run one small eager step for a profiler instead of the benchmark")
+    ap.add_argument("--attention", choices=["auto", "mma_sync"], default="auto",
+                    help="mma_sync: prompt portions stay on the mma.sync attention kernel (to compare or profile it)")
     ap.add_argument("--workload", choices=["medium", "xl"],
                     help="run a continuous-batching workload of GPT-2 medium or XL instead of the benchmark")
     args = ap.parse_args()
+    if args.attention == "mma_sync":
+        from mini_llm_b200 import ops
+        ops.use_tcgen05_attention = False
     if args.profile_step:
         return profile_step(args.profile_step, args.dtype, args.layers, args.batch)
     if args.workload:

@@ -414,6 +414,7 @@ def kv_write(k, v, k_pages, v_pages, slot_mapping) -> None:
 
 
 attention_launches = {}     # attention kernel name -> launches so far (tests check which kernel a step took)
+use_tcgen05_attention = True    # False: prompt portions stay on the mma.sync kernel (for comparisons and profiles)
 
 
 def _flash_tc_ok(q, k_pages, out, ctx, head_dim, ps, ldq, ldo) -> bool:
@@ -448,7 +449,7 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
         if getattr(ctx, "decode_only", False) and head_dim in _DECODE_HEAD_DIMS[q.dtype] and ldq % 8 == 0 \
                 and q.data_ptr() % 16 == 0:
             impl = "decode"
-        elif _flash_tc_ok(q, k_pages, out, ctx, head_dim, ps, ldq, ldo) and ctx.T >= 256 \
+        elif use_tcgen05_attention and _flash_tc_ok(q, k_pages, out, ctx, head_dim, ps, ldq, ldo) and ctx.T >= 256 \
                 and ctx.T >= 80 * ctx.n_tiles_wide:
             impl = "flash_tc"       # long prompt portions (tiles of 128 rows mostly full): the tensor-memory kernel
         elif q.dtype == torch.bfloat16 and head_dim in _FLASH_HEAD_DIMS and getattr(ctx, "n_tiles", 0) > 0 \
