@@ -290,3 +290,186 @@ def test_toy_architecture_with_a_window_and_grouped_heads(tmp_path, dtype):
         runner.finish_request("r")
     runner.cache.check()
     assert all(g.allocator.num_free == 40 for g in runner.cache.groups)
+
+
+# ---------------------------------------------------------------------------------- rotary positions, routed experts
+def _register_rotary_routed():
+    """A position encoding that acts on queries and keys (a rotation by the absolute position) and a
+    feed-forward that routes every token to one of several experts, both defined here."""
+    import mini_llm_b200 as m
+    from mini_llm_b200.config.base import ModelConfig
+    from mini_llm_b200.parts.base import FeedForward, ParamSpec, Positions
+    from mini_llm_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, WeightRef
+
+    class ToyRotary(Positions):
+        acts_on_qk = True
+        graph_safe = False
+
+        def __init__(self, head_dim, base):
+            self.head_dim, self.base = int(head_dim), float(base)
+            self.max_positions = None
+
+        def apply_qk(self, q, k, ctx):
+            dh = self.head_dim
+            pos = ctx.positions.float()
+            inv = self.base ** (-torch.arange(0, dh, 2, device=q.device, dtype=torch.float32) / dh)
+            ang = pos[:, None] * inv[None, :]                       # 32-bit angles
+            cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            for x in (q, k):
+                v = x.view(x.shape[0], -1, dh // 2, 2)
+                a, b = v[..., 0].float().clone(), v[..., 1].float().clone()     # copies: .float() of float32 is a view
+                v[..., 0] = (a * cos - b * sin).to(x.dtype)
+                v[..., 1] = (a * sin + b * cos).to(x.dtype)
+
+    class ToyRouted(FeedForward):
+        """Top-1 routing: y = p_e(h) * down_e . gelu(up_e . h) for the expert e with the largest router logit."""
+        graph_safe = False
+
+        def __init__(self, hidden_size, inner_size, num_experts):
+            self.D, self.I, self.E = int(hidden_size), int(inner_size), int(num_experts)
+
+        def param_specs(self):
+            return {"router": ParamSpec((self.E, self.D), "matrix"), "up": ParamSpec((self.E * self.I, self.D), "matrix"),
+                    "down": ParamSpec((self.E * self.D, self.I), "matrix")}
+
+        def forward(self, h, ctx, out_accum):
+            x = h.float()
+            probs = torch.softmax(x @ self.router.float().t(), -1)      # router logits and softmax in 32-bit
+            top = probs.argmax(-1)
+            for e in range(self.E):
+                rows = (top == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                up = self.up[e * self.I:(e + 1) * self.I].float()
+                down = self.down[e * self.D:(e + 1) * self.D].float()
+                y = torch.nn.functional.gelu(x[rows] @ up.t()) @ down.t()
+                out_accum[rows] += y * probs[rows, e][:, None]
+
+    @dataclass
+    class RRConfig(ModelConfig):
+        hidden: int = 0
+        vocab: int = 0
+        heads: int = 0
+        inner: int = 0
+        experts: int = 0
+        base: float = 10000.0
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(hidden=d["hidden"], vocab=d["vocab"], heads=d["heads"], inner=d["inner"], experts=d["experts"],
+                       base=d["base"])
+
+        def to_dict(self):
+            return dict(architectures=["ToyRotaryRoutedLM"], hidden=self.hidden, vocab=self.vocab, heads=self.heads,
+                        inner=self.inner, experts=self.experts, base=self.base)
+
+    def build(cfg):
+        D, H = cfg.hidden, cfg.heads
+        dh = D // H
+
+        def norm(name):
+            return PartSpec("layernorm", dict(hidden_size=D, eps=1e-5),
+                            {"weight": WeightRef((name + ".g",), init=("ones",)), "bias": WeightRef((name + ".b",), init=("zeros",))})
+
+        def layer(i):
+            att = PartSpec("attention", dict(hidden_size=D, num_heads=H, head_dim=dh, scale=dh ** -0.5, bias=False),
+                           {"qkv_weight": WeightRef((f"l{i}.qkv",), init=("normal", 0.4)),
+                            "out_weight": WeightRef((f"l{i}.o",), init=("normal", 0.3))})
+            ff = PartSpec("toy_routed", dict(hidden_size=D, inner_size=cfg.inner, num_experts=cfg.experts),
+                          {"router": WeightRef((f"l{i}.router",), init=("normal", 1.0)),
+                           "up": WeightRef((f"l{i}.up",), init=("normal", 0.2)),
+                           "down": WeightRef((f"l{i}.down",), init=("normal", 0.2))})
+            return LayerSpec(mixer=att, ff=ff, mixer_norm=norm(f"l{i}.n1"), ff_norm=norm(f"l{i}.n2"))
+
+        return ModelSpec(hidden_size=D, vocab_size=cfg.vocab,
+                         embedding=PartSpec("token", dict(hidden_size=D, vocab_size=cfg.vocab), {"table": WeightRef(("emb",), init=("normal", 1.0))}),
+                         positions=PartSpec("toy_rotary", dict(head_dim=dh, base=cfg.base), {}),
+                         layers=[layer(0), layer(1)], final_norm=norm("nf"),
+                         head=PartSpec("tied", dict(hidden_size=D, vocab_size=cfg.vocab)), max_positions=None)
+
+    m.register_part("positions", "toy_rotary", ToyRotary, replace=True)
+    m.register_part("feed_forward", "toy_routed", ToyRouted, replace=True)
+    m.register_architecture("ToyRotaryRoutedLM", RRConfig, build, replace=True)
+    return dict(architectures=["ToyRotaryRoutedLM"], hidden=64, vocab=150, heads=2, inner=48, experts=3, base=100.0)
+
+
+def _rotary_routed_reference(folder, ids):
+    from safetensors.torch import load_file
+    w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    cfg = json.load(open(os.path.join(folder, "config.json")))
+    D, H, E, I, T = cfg["hidden"], cfg["heads"], cfg["experts"], cfg["inner"], len(ids)
+    dh = D // H
+
+    def ln(x, n):
+        return torch.nn.functional.layer_norm(x, (D,), w[n + ".g"], w[n + ".b"], 1e-5)
+
+    def rotate(x):                                           # [T, heads*dh]
+        pos = torch.arange(T, dtype=torch.float64)
+        inv = cfg["base"] ** (-torch.arange(0, dh, 2, dtype=torch.float64) / dh)
+        ang = pos[:, None] * inv[None, :]
+        v = x.reshape(T, -1, dh // 2, 2)
+        a, b = v[..., 0], v[..., 1]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        return torch.stack([a * c - b * s, a * s + b * c], -1).reshape(T, -1)
+
+    x = w["emb"][torch.tensor(ids)]
+    mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
+    margins = []
+    for i in range(2):
+        qkv = ln(x, f"l{i}.n1") @ w[f"l{i}.qkv"].t()
+        q, k, v = rotate(qkv[:, :D]), rotate(qkv[:, D:2 * D]), qkv[:, 2 * D:]
+        att = torch.zeros(T, D, dtype=torch.float64)
+        for hh in range(H):
+            sl = slice(hh * dh, (hh + 1) * dh)
+            s = (q[:, sl] @ k[:, sl].t()) * dh ** -0.5
+            att[:, sl] = torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ v[:, sl]
+        x = x + att @ w[f"l{i}.o"].t()
+        h = ln(x, f"l{i}.n2")
+        probs = torch.softmax(h @ w[f"l{i}.router"].t(), -1)
+        top2 = torch.topk(probs, 2, -1).values
+        margins.append((top2[:, 0] - top2[:, 1]).min().item())
+        top = probs.argmax(-1)
+        y = torch.zeros_like(x)
+        for e in range(E):
+            rows = (top == e).nonzero().flatten()
+            up, down = w[f"l{i}.up"][e * I:(e + 1) * I], w[f"l{i}.down"][e * D:(e + 1) * D]
+            y[rows] = (torch.nn.functional.gelu(h[rows] @ up.t()) @ down.t()) * probs[rows, e][:, None]
+        x = x + y
+    return ln(x, "nf") @ w["emb"].t(), min(margins)
+
+
+def test_toy_architecture_with_rotary_positions_and_routed_experts(tmp_path):
+    """Another position encoding (it rotates queries and keys before the keys are cached, so decoded tokens
+    must meet keys rotated at their own positions) and a feed-forward with routing, registered from here and
+    run whole, in portions and token by token through the package's step function and attention kernels."""
+    import mini_llm_b200 as m
+    from mini_llm_b200.config.base import EngineConfig
+    from mini_llm_b200.engine.runner import ModelRunner, StepEntry
+
+    cfg = _register_rotary_routed()
+    folder = m.write_random_model(cfg, 9, str(tmp_path / "rr"))
+    runner = ModelRunner(folder, EngineConfig(dtype="float32", page_size=8, num_pages=64, max_num_seqs=2))
+    ids = torch.randint(0, cfg["vocab"], (140,), generator=torch.Generator().manual_seed(4)).tolist()
+    want, margin = _rotary_routed_reference(folder, ids)
+    assert margin > 1e-4                                    # no routing decision of the oracle hangs on rounding
+    for plan in ([140], [60, 1, 1, 1, 33, 44], [2] + [1] * 30 + [108]):
+        runner.add_request("r")
+        got, pos = [], 0
+        for n in plan:
+            got.append(runner.step([StepEntry("r", ids[pos:pos + n], list(range(n)))]).double().cpu())
+            pos += n
+        err = (torch.cat(got) - want).abs().max() / want.abs().max()
+        assert err < 2e-4, (plan[:3], float(err))
+        runner.finish_request("r")
+    # two requests side by side at different positions: every token is rotated by its own position
+    other = ids[50:90]
+    want2, _ = _rotary_routed_reference(folder, other)
+    runner.add_request("a")
+    runner.add_request("b")
+    runner.step([StepEntry("a", ids[:100], [])])
+    out = runner.step([StepEntry("a", ids[100:103], [2]), StepEntry("b", other, [39])]).double().cpu()
+    assert (out[0] - want[102]).abs().max() < 2e-4 * want.abs().max()
+    assert (out[1] - want2[39]).abs().max() < 2e-4 * want2.abs().max()
+    runner.finish_request("a")
+    runner.finish_request("b")
+    runner.cache.check()
