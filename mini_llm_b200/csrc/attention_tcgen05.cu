@@ -228,7 +228,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int d = 0; d < 16; ++d) o[d] = 0.f;
         float m_run = -INFINITY, l_part = 0.f, alpha_prev = 1.f;
         // A warp that gave up on a wait stays in step with the three that share its rows: it skips the work but
-        // still arrives at their barriers, which also carry the verdict, so nobody waits for a warp that left.
+        // still arrives at their barriers, which also carry whether all of them are still running, so nobody waits for a warp that left.
         bool alive = true;
         uint32_t v[32];
         auto row_barrier = [&](bool fine) -> bool {          // barrier of the 4 warps of this quarter; true if all are fine

@@ -50,6 +50,17 @@ template <int BN> struct Cfg {
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + EPI_BYTES + BIAS_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
+// Cache write fused into the epilogue of a Q|K|V projection: output columns [0, q_size) are the
+// queries and go to `out`; the key and the value columns of row m go straight to the page slot
+// slots[m] ([page][kv_head][offset][head_dim], slot = page * page_size + offset).  A block of 32
+// columns lies inside one head (head_dim is a multiple of 32), so a lane stores 64 contiguous bytes.
+struct KvOut {
+    __nv_bfloat16* k_pages;      // null: a plain product
+    __nv_bfloat16* v_pages;
+    const int* slots;
+    int q_size, kv_heads, head_dim, page_size;
+};
+
 // A persistent CTA: tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...; tile -> (m tile, n tile)
 // with n fastest.  Two accumulators in tensor memory let the epilogue of one tile run while
 // the next tile's MMAs are issued.
@@ -58,7 +69,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       const __grid_constant__ CUtensorMap map_o, const float* __restrict__ bias, TO* out, long long ldo,
                       int M, int N, int K, int act, int accumulate, int vec_ok, int tma_out, int tiles_n,
-                      int num_tiles) {
+                      int num_tiles, KvOut kv) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -170,6 +181,10 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 constexpr int ES = (int)sizeof(TO);
                 uint8_t* sblk = reinterpret_cast<uint8_t*>(epi) + (size_t)(warp - 2) * 4096;    // 1024-byte aligned
                 const int row0 = m0 + q * 32;
+                int my_slot = -1;                            // this lane's row: where its keys and values go
+                if constexpr (sizeof(TO) == 2) {
+                    if (kv.k_pages && row0 + lane < M) my_slot = kv.slots[row0 + lane];
+                }
                 if (half < NC) {
                     tmem_ld32_issue(t_addr + (uint32_t)(half * 32), r);
                     tmem_ld_wait();
@@ -197,6 +212,34 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     } else if (act == MLLM_ACT_GELU_ERF) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = gelu_erf_f(v[j]);
+                    }
+                    if constexpr (sizeof(TO) == 2) {
+                        if (kv.k_pages && n0 + c * 32 >= kv.q_size) {
+                            // key or value columns: straight from the registers to the row's page slot
+                            if (my_slot >= 0 && n0 + c * 32 < N) {
+                                const int cc = n0 + c * 32 - kv.q_size, kvs = kv.kv_heads * kv.head_dim;
+                                const int which = cc / kvs, c2 = cc % kvs;
+                                const int head = c2 / kv.head_dim, d0 = c2 % kv.head_dim;
+                                __nv_bfloat16* dst = (which == 0 ? kv.k_pages : kv.v_pages) +
+                                    (((size_t)(my_slot / kv.page_size) * kv.kv_heads + head) * kv.page_size +
+                                     my_slot % kv.page_size) * kv.head_dim + d0;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    uint4 pk;
+                                    __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) hh[i] = __floats2bfloat162_rn(v[8 * j + 2 * i], v[8 * j + 2 * i + 1]);
+                                    *reinterpret_cast<uint4*>(dst + 8 * j) = pk;
+                                }
+                            }
+                            if (c + 2 < NC) tmem_ld_wait();
+                            if (c + 2 < NC && c + 4 >= NC) {
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                            }
+                            continue;
+                        }
                     }
                     if (lane == 0) bulk_wait_read();         // the copy engine has read the last block out of the buffer
                     __syncwarp();
@@ -356,7 +399,7 @@ int sm_count() {
 
 template <int BN, typename TO>
 int launch(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo, int M, int N,
-           int K, int act, int accumulate, cudaStream_t stream) {
+           int K, int act, int accumulate, cudaStream_t stream, const KvOut& kv) {
     using C = Cfg<BN>;
     static_assert(C::STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of swizzled tiles");
     CUtensorMap ma, mw, mo;
@@ -368,8 +411,10 @@ int launch(const void* A, long long lda, const void* W, const float* bias, void*
     // it only in 32-bit (its bfloat16 addition would round the new term before adding).
     const int tma_out = (uintptr_t)out % 16 == 0 && (ldo * (long long)sizeof(TO)) % 16 == 0 &&
                         !(accumulate && sizeof(TO) == 2);
+    if (kv.k_pages && !tma_out) return mllm_fail(1, "linear_tcgen05: the cache-writing epilogue needs 16-byte aligned query rows");
     if (tma_out) {
-        rc = get_map(out, ldo, M, N, 32, 32, sizeof(TO) == 4 ? MAP_F32_SW128 : MAP_BF16_SW64, &mo);
+        // with the cache write fused in, `out` holds the query columns only: the map ends there
+        rc = get_map(out, ldo, M, kv.k_pages ? kv.q_size : N, 32, 32, sizeof(TO) == 4 ? MAP_F32_SW128 : MAP_BF16_SW64, &mo);
         if (rc) return rc;
     } else {
         mo = ma;                                       // not used by the kernel
@@ -386,13 +431,13 @@ int launch(const void* A, long long lda, const void* W, const float* bias, void*
     const int num_tiles = tiles_n * tiles_m;
     const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
     MLLM_CUDA(mllm_launch(kern, dim3(grid), dim3(THREADS), C::SMEM, stream, true, ma, mw, mo, bias, (TO*)out, ldo, M, N,
-                          K, act, accumulate, vec_ok, tma_out, tiles_n, num_tiles));
+                          K, act, accumulate, vec_ok, tma_out, tiles_n, num_tiles, kv));
     return 0;
 }
 
 template <typename TO>
 int pick_bn(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo, int M, int N,
-            int K, int act, int accumulate, cudaStream_t stream) {
+            int K, int act, int accumulate, cudaStream_t stream, const KvOut& kv = KvOut{}) {
     // The tile width that moves the fewest bytes per SM: a CTA runs ceil(tiles / SMs) tiles one after
     // the other and every k-step of a tile brings in (128 + BN) rows of 64 values.
     const int widths[5] = {256, 192, 128, 96, 64};
@@ -407,7 +452,7 @@ int pick_bn(const void* A, long long lda, const void* W, const float* bias, void
         const long long cost = rounds * (BM + bn) + rounds * 24;  // + a fixed part per tile (epilogue tail)
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
     }
-#define GO(B) return launch<B, TO>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream)
+#define GO(B) return launch<B, TO>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream, kv)
     switch (best) {
         case 256: GO(256);
         case 192: GO(192);
@@ -444,4 +489,24 @@ MLLM_EXPORT int mllm_linear_tcgen05(const void* A, long long lda, const void* W,
     if (out_dtype == MLLM_F32)
         return pick_bn<float>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
     return mllm_fail(1, "linear_tcgen05: unknown dtype code %d", out_dtype);
+}
+
+// The Q|K|V projection of many rows with the cache write fused in: out [M, q_size] (row stride ldo)
+// receives the query columns, keys and values go to their page slots (slots[m] = page * page_size +
+// offset, negative: not stored).  bfloat16 throughout; q_size and head_dim multiples of 32.
+MLLM_EXPORT int mllm_linear_tcgen05_qkv(const void* A, long long lda, const void* W, const float* bias, void* out,
+                                        long long ldo, int M, int N, int K, void* k_pages, void* v_pages,
+                                        const int* slots, int q_size, int kv_heads, int head_dim, int page_size,
+                                        cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || lda % 8 != 0)
+        return mllm_fail(1, "linear_tcgen05: K=%d and the row stride %lld must be multiples of 8", K, lda);
+    if ((uintptr_t)A % 16 != 0 || (uintptr_t)W % 16 != 0) return mllm_fail(1, "linear_tcgen05: operands must be 16-byte aligned");
+    if (q_size <= 0 || q_size % 32 || head_dim <= 0 || head_dim % 32 || kv_heads <= 0 || page_size <= 0 ||
+        N != q_size + 2 * kv_heads * head_dim)
+        return mllm_fail(1, "linear_tcgen05: %d output columns do not split into %d query and 2 x %d x %d cache columns "
+                            "in blocks of 32", N, q_size, kv_heads, head_dim);
+    if ((uintptr_t)k_pages % 16 || (uintptr_t)v_pages % 16) return mllm_fail(1, "linear_tcgen05: the pages must be 16-byte aligned");
+    KvOut kv{(__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, slots, q_size, kv_heads, head_dim, page_size};
+    return pick_bn<__nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, MLLM_ACT_NONE, 0, stream, kv);
 }

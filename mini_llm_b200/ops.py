@@ -55,6 +55,8 @@ def _signatures(lib):
                                    c_void_p],
         "mllm_linear_tcgen05": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p],
+        "mllm_linear_tcgen05_qkv": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_void_p,
+                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_tcgen05_error": [c_void_p],
         "mllm_attention_decode": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -302,9 +304,11 @@ def linear_qkv_cache(x, weight, bias, q_out, k_pages, v_pages, slot_mapping, ws)
     """Q|K|V projection whose keys and values go to their page slots; returns the queries.
 
     weight [q_size + 2*kv_heads*head_dim, K]; q_out [M, q_size] is where the queries may be
-    put.  With few rows the cache write rides in the product's epilogue (and a NormedInput's
-    norm in its loads) and q_out is returned; otherwise the product writes a [M, N] buffer,
-    kv_write copies keys and values from it, and the buffer's query columns are returned.
+    put.  The cache write rides in the product's epilogue - the weight-streaming kernel's with few
+    rows (which also takes a NormedInput's norm into its loads), the tensor-memory kernel's with
+    many - and q_out is returned; where neither applies (32-bit, head sizes that are no multiple
+    of 32) the product writes a [M, N] buffer, kv_write copies keys and values from it, and the
+    buffer's query columns are returned.
     """
     M = x.shape[0]
     N, K = weight.shape
@@ -316,6 +320,8 @@ def linear_qkv_cache(x, weight, bias, q_out, k_pages, v_pages, slot_mapping, ws)
     _cuda("k_pages", k_pages, q_out.dtype)
     _cuda("v_pages", v_pages, q_out.dtype)
     _cuda("slot_mapping", slot_mapping, torch.int32)
+    if slot_mapping.numel() != M or q_out.shape[0] != M or v_pages.shape != k_pages.shape:
+        raise KernelError(f"linear_qkv_cache: {M} rows, {slot_mapping.numel()} slots, q_out {tuple(q_out.shape)}")
     norm = x if isinstance(x, NormedInput) else None
     if norm is not None and not _norm_ok(norm):
         x, norm = norm.materialize(), None
@@ -326,6 +332,21 @@ def linear_qkv_cache(x, weight, bias, q_out, k_pages, v_pages, slot_mapping, ws)
             _cuda("bias", bias, torch.float32)
         _linear_fused(None if norm is not None else x, weight, bias, q_out, None, False, norm,
                       (k_pages, v_pages, slot_mapping, q_size))
+        return q_out
+    if norm is not None:
+        x, norm = norm.materialize(), None
+    _cuda("x", x, contiguous=False)
+    if (q_out.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and not _small_m_wins(M, N, K) and q_size % 32 == 0 and dh % 32 == 0 and K % 8 == 0
+            and _rows("x", x) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+            and _rows("q_out", q_out) % 8 == 0 and q_out.data_ptr() % 16 == 0 and k_pages.is_contiguous()
+            and v_pages.is_contiguous()):
+        # many rows: the tensor-memory product, whose epilogue stores keys and values into their pages
+        if bias is not None:
+            _cuda("bias", bias, torch.float32)
+        _call("mllm_linear_tcgen05_qkv", x.data_ptr(), _rows("x", x), weight.data_ptr(),
+              bias.data_ptr() if bias is not None else None, q_out.data_ptr(), _rows("q_out", q_out), M, N, K,
+              k_pages.data_ptr(), v_pages.data_ptr(), slot_mapping.data_ptr(), q_size, Hkv, dh, ps, _stream())
         return q_out
     qkv = ws.buf("qkv", M, N, q_out.dtype)
     linear(x, weight, bias, out=qkv)

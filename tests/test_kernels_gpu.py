@@ -203,7 +203,7 @@ def test_small_m_qkv_product_writes_the_cache(ops, M, H, Hkv, dh, page, K):
     N = q_size + 2 * kv
     x = rnd(M, K, seed=1, dtype=torch.bfloat16)
     w, b = rnd(N, K, seed=2, scale=K ** -0.5, dtype=torch.bfloat16), rnd(N, seed=3)
-    P = 40
+    P = 40 + 300 // page               # room for the 300 rows of the second part
     g = torch.Generator().manual_seed(4)
     slots = torch.randperm(P * page, generator=g)[:M].to(torch.int32).to(DEV)
     qkv = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
@@ -217,19 +217,27 @@ def test_small_m_qkv_product_writes_the_cache(ops, M, H, Hkv, dh, page, K):
     q = ops.linear_qkv_cache(x, w, b, q_buf, gk, gv, slots, ws)
     assert q.data_ptr() == q_buf.data_ptr()
     assert torch.equal(q, qkv[:, :q_size]) and torch.equal(gk, wk) and torch.equal(gv, wv)
-    # many rows: the unfused route gives the same cache
-    M2 = 100
+    # many rows: the tensor-memory product's epilogue (head sizes that are multiples of 32) or the product
+    # followed by the copy kernel give the same cache
+    M2 = 300
     x2 = rnd(M2, K, seed=5, dtype=torch.bfloat16)
     slots2 = torch.randperm(P * page, generator=g)[:M2].to(torch.int32).to(DEV)
+    assert slots2.numel() == M2
+    with pytest.raises(Exception):       # one slot per row, or the call is refused
+        ops.linear_qkv_cache(x2, w, b, torch.empty(M2, q_size, device=DEV, dtype=torch.bfloat16), gk, gv, slots2[:-1], ws)
     gk.fill_(9.0), gv.fill_(9.0)
     q2 = ops.linear_qkv_cache(x2, w, b, torch.empty(M2, q_size, device=DEV, dtype=torch.bfloat16), gk, gv, slots2, ws)
     full = torch.empty(M2, N, device=DEV, dtype=torch.bfloat16)
     ops.linear(x2, w, b, out=full)
     assert torch.equal(q2, full[:, :q_size])
-    for t in (0, 57, 99):
-        s_ = int(slots2[t])
-        assert torch.equal(gk[s_ // page, :, s_ % page].reshape(-1), full[t, q_size:q_size + kv])
-        assert torch.equal(gv[s_ // page, :, s_ % page].reshape(-1), full[t, q_size + kv:])
+    sl = slots2.long()
+    assert torch.equal(gk[sl // page, :, sl % page].reshape(M2, -1), full[:, q_size:q_size + kv])
+    assert torch.equal(gv[sl // page, :, sl % page].reshape(M2, -1), full[:, q_size + kv:])
+    untouched = torch.ones(P * page, dtype=torch.bool, device=DEV)
+    untouched[sl] = False
+    rest = gk.permute(0, 2, 1, 3).reshape(P * page, -1)[untouched]
+    assert torch.all(rest == 9.0)
+    ops.check_device_errors()
 
 
 def test_linear_small_m_rows_do_not_depend_on_the_batch(ops):
