@@ -592,6 +592,48 @@ def test_paged_attention_finds_one_far_key_among_hundreds(ops, dtype):
             assert out.float().mean().item() > 6.5, impl
 
 
+@pytest.mark.parametrize("impl,dtype", [("tiled", torch.float32), ("tiled", torch.bfloat16), ("flash", torch.bfloat16),
+                                        ("flash_tc", torch.bfloat16)])
+def test_prompt_attention_finds_one_far_key_among_hundreds(ops, impl, dtype):
+    """The same for the kernels of prompt portions: the last 150 queries of a 700-token request all lean on one
+    key far back - at a page's first and last slot, in the first key tile, at a tile's edge - which sits in
+    another key tile or block than the queries; a kernel that skipped or misplaced that tile shows at once."""
+    from mini_llm_b200.engine.context import ATTN_TILE_WIDE, attention_tiles
+    H, dh, page, ctx_len, ql = 2, 64, 16, 700, 150
+    for far in (0, 16 * 3 + 15, 127, 128, 383, 549):
+        case = _paged_case(dtype, [(ctx_len, ql)], H, H, dh, page, num_pages=64, seed=far)
+        K, V = case["dense"][0]
+        u = torch.randn(H, dh, generator=torch.Generator().manual_seed(far + 1))
+        case["q"] = (case["q"].view(ql, H, dh) * 0.3 + u * 1.5).reshape(ql, H * dh)   # all queries get a common component ...
+        K[far] = u * 3.0                                        # ... that one key answers: its score is about 36
+        V[far] = 7.0
+        tab = case["bt"][0].tolist()
+        case["k_pages"][tab[far // page], :, far % page] = K[far]
+        case["v_pages"][tab[far // page], :, far % page] = V[far]
+        ctx = _ctx_for(case)
+        ctx.decode_only = False
+        t64 = attention_tiles([ql], [ctx_len - ql])
+        t128 = attention_tiles([ql], [ctx_len - ql], ATTN_TILE_WIDE)
+        ctx.attn_tiles, ctx.n_tiles = torch.tensor(t64, dtype=torch.int32, device=DEV), len(t64) // 3
+        ctx.attn_tiles_wide, ctx.n_tiles_wide = torch.tensor(t128, dtype=torch.int32, device=DEV), len(t128) // 3
+        q = case["q"].to(dtype).to(DEV)
+        want = _attention_reference(case, H, H, dh, dh ** -0.5, None, dtype)
+        out = torch.empty_like(q)
+        ops.paged_attention(q, case["k_pages"].to(dtype).to(DEV), case["v_pages"].to(dtype).to(DEV), case["bt"].to(DEV),
+                            ctx, out, num_heads=H, num_kv_heads=H, head_dim=dh, scale=dh ** -0.5, impl=impl)
+        assert (out.double().cpu() - want).abs().max() < (2e-5 * 8 if dtype == torch.float32 else 3e-2), (impl, far)
+        assert out.float().mean().item() > 6.0, (impl, far)
+    ops.check_device_errors()
+
+
+def test_resolve_tokens(ops):
+    """Ids that stand for "row r of the last sampling launch" (negative) are filled in on the device."""
+    ids = torch.tensor([5, -1, 17, -3, -2, 0, -4], dtype=torch.int32, device=DEV)
+    sampled = torch.tensor([100, 200, 300, 400], dtype=torch.int32, device=DEV)
+    ops.resolve_tokens(ids, sampled)
+    assert ids.tolist() == [5, 100, 17, 300, 200, 0, 400]
+
+
 def test_paged_attention_refuses_sizes_it_cannot_take(ops):
     from mini_llm_b200.ops import KernelError
     ctx = _Ctx()
