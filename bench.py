@@ -8,7 +8,11 @@ n_positions 1024) with seeded random weights in bfloat16, a batch of 8 requests 
 512-token random prompts, page size 16.  It prints ONE JSON line:
 
   value       decoded tokens per second over exactly K steps, timed on the device
-              with CUDA events (forward pass + on-device argmax per step);
+              with CUDA events (forward pass + on-device argmax per step).  The default
+              K = 512 is the benchmark's whole generation: contexts grow from 512 to
+              1,023.  The warm-up is the same generation by other requests (max(W, K)
+              steps), so the timed steps replay captured graphs; a K beyond the 512
+              positions a request has left is cut to 512;
   e2e         the same through the Python entry point (LLM.step): host token ids in,
               sampled ids back on the host every step;
   prefill     2,048 prompt tokens (2 x 1024) in one step: tokens/s, ms, and the share
@@ -127,8 +131,16 @@ def prefill_flops(cfg, lens, rows) -> float:
     return linear + attn
 
 
+def decode_steps(cfg, steps: int) -> int:
+    """A request starts at a PROMPT_LEN-token prompt and may be fed a token at every further position."""
+    return max(1, min(int(steps), int(cfg["n_positions"]) - PROMPT_LEN))
+
+
 def run_decode(model_dir, dtype, batch, steps, warmup, sample_clocks=False):
-    """Device-timed decode: K steps of (forward + argmax) on ``batch`` live requests."""
+    """Device-timed decode: K steps of (forward + argmax) on ``batch`` live requests whose contexts grow from
+    PROMPT_LEN.  The warm-up is a generation of max(W, K) steps by other requests of the same shape (every step
+    shape of the timed run has then been seen and captured); the timed K steps start right after the prompts of
+    the timed requests are in, so that K = 512 covers the contexts 512 .. 1023 of the benchmark."""
     import torch
     import mini_llm_b200 as m
     from mini_llm_b200 import ops
@@ -136,42 +148,52 @@ def run_decode(model_dir, dtype, batch, steps, warmup, sample_clocks=False):
     from mini_llm_b200.engine.runner import ModelRunner, StepEntry
 
     cfg = json.load(open(os.path.join(model_dir, "config.json")))
+    steps = decode_steps(cfg, steps)
+    warm_steps = decode_steps(cfg, max(steps, warmup))
     eng = EngineConfig(dtype=dtype, page_size=PAGE, max_tokens=batch * cfg["n_positions"], max_num_seqs=max(batch, 1),
                        max_num_batched_tokens=max(2048, batch))
     runner = ModelRunner(model_dir, eng)
     g = torch.Generator().manual_seed(1234)
     prompts = torch.randint(0, cfg["vocab_size"], (batch, PROMPT_LEN), generator=g).tolist()
     out = torch.empty(batch, dtype=torch.int32, device=runner.device)
-    for i in range(batch):
-        runner.add_request(i)
-    for lo in range(0, batch, 4):                       # prompts, 2,048 tokens per step
-        runner.step([StepEntry(i, prompts[i], []) for i in range(lo, min(batch, lo + 4))])
     toks = [int(p[-1]) for p in prompts]
 
-    def one():
-        logits = runner.step([StepEntry(i, [toks[i]], [0]) for i in range(batch)])
+    def start(tag):
+        ids = [(tag, i) for i in range(batch)]
+        for r in ids:
+            runner.add_request(r)
+        for lo in range(0, batch, 4):                       # prompts, 2,048 tokens per step
+            runner.step([StepEntry(ids[i], prompts[i], []) for i in range(lo, min(batch, lo + 4))])
+        return ids
+
+    def one(ids):
+        logits = runner.step([StepEntry(ids[i], [toks[i]], [0]) for i in range(batch)])
         ops.argmax(logits, out)
 
-    for _ in range(warmup):
-        one()
+    ids = start("warm")
+    for _ in range(warm_steps):
+        one(ids)
+    for r in ids:
+        runner.finish_request(r)
+    ids = start("timed")
     torch.cuda.synchronize()
     clocks = ClockSampler()
     if sample_clocks:
         clocks.start()
-    ctx0 = runner.computed(0)
+    ctx0 = runner.computed(ids[0])
     n0 = ops.launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
     for _ in range(steps):
-        one()
+        one(ids)
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
     launches = ops.launches - n0
     mean_ctx = ctx0 + (steps + 1) / 2.0
-    res = dict(ms_per_step=ms / steps, tok_s=batch * steps / (ms / 1e3), launches=launches,
-               bytes=decode_bytes(runner, cfg, batch, mean_ctx), mean_ctx=mean_ctx,
+    res = dict(ms_per_step=ms / steps, tok_s=batch * steps / (ms / 1e3), launches=launches, steps=steps,
+               warmup=warm_steps, bytes=decode_bytes(runner, cfg, batch, mean_ctx), mean_ctx=mean_ctx,
                clocks=clocks.stop() if sample_clocks else None)
     del runner
     torch.cuda.empty_cache()
@@ -179,33 +201,43 @@ def run_decode(model_dir, dtype, batch, steps, warmup, sample_clocks=False):
 
 
 def run_e2e(model_dir, dtype, batch, steps, warmup):
-    """The same decode steps through LLM.step(): host token lists in, sampled ids out."""
+    """The same decode steps through LLM.step(): host token lists in, sampled ids out.  One generation by other
+    requests warms up; then the timed requests' prompts go in and the clock runs from their first decode step
+    until the last of their K decoded tokens has been handed back to the host."""
     import torch
     import mini_llm_b200 as m
 
     cfg = json.load(open(os.path.join(model_dir, "config.json")))
+    steps = decode_steps(cfg, steps)
+    # all prompts go in with one step, so that the requests decode side by side from the first timed step to the last
     llm = m.LLM(model_dir, dtype=dtype, page_size=PAGE, max_tokens=batch * cfg["n_positions"], max_num_seqs=batch,
-                max_num_batched_tokens=2048, prefill_chunk=2048)
+                max_num_batched_tokens=batch * PROMPT_LEN, prefill_chunk=PROMPT_LEN)
     g = torch.Generator().manual_seed(1234)
     prompts = torch.randint(0, cfg["vocab_size"], (batch, PROMPT_LEN), generator=g).tolist()
-    sp = m.SamplingParams(max_new_tokens=steps + warmup + 2, ignore_eos=True)
-    for p in prompts:
-        llm.add_request(p, sp)
-    while any(r.state.value in ("waiting_prefill", "prefill_running", "deferred_prefill_kv")
-              for r in list(llm.scheduler.waiting) + llm.scheduler.prefill + list(llm.scheduler.deferred_prefill)):
+    sp = m.SamplingParams(max_new_tokens=steps + 1, ignore_eos=True)     # one token from the prompt's step, K decoded
+
+    def prompts_in():
+        for p in prompts:
+            llm.add_request(p, sp)
+        first = 0
+        while llm.scheduler.waiting or llm.scheduler.prefill or llm.scheduler.deferred_prefill:
+            first += len(llm.step())
+        return first
+
+    prompts_in()
+    while llm.has_unfinished():
         llm.step()
-    for _ in range(warmup):
-        llm.step()
+    first = prompts_in()
     torch.cuda.synchronize()
-    h2d = 0
     t0 = time.perf_counter()
     produced = 0
-    for _ in range(steps):
+    while llm.has_unfinished():
         produced += len(llm.step())
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    produced -= batch - first                  # tokens of the prompts' step that were only handed back inside the clock
     lay = llm.runner._last_layout_total if hasattr(llm.runner, "_last_layout_total") else None
-    res = dict(tok_s=produced / dt, h2d=(lay or 0) * 4, d2h=batch * 4)
+    res = dict(tok_s=produced / dt, h2d=(lay or 0) * 4, d2h=batch * 4, tokens=produced)
     del llm
     torch.cuda.empty_cache()
     return res
@@ -336,7 +368,7 @@ def run_workload(kind: str, dtype: str, layers: int) -> int:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
@@ -366,8 +398,7 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
-    if PROMPT_LEN + args.warmup + args.steps + 1 > SMALL["n_positions"]:
-        args.steps = SMALL["n_positions"] - PROMPT_LEN - args.warmup - 1
+    args.steps = decode_steps(SMALL, args.steps)        # a request has 512 positions left after its prompt
     import torch
     import mini_llm_b200 as m
 
@@ -380,7 +411,7 @@ def main() -> int:
         points, prefill = {}, None
         if not args.no_points:
             for b in (1, 64):
-                points[f"decode_b{b}"] = round(run_decode(d, args.dtype, b, min(args.steps, 128), args.warmup)["tok_s"], 1)
+                points[f"decode_b{b}"] = round(run_decode(d, args.dtype, b, args.steps, args.warmup)["tok_s"], 1)
             pf = run_prefill(d, args.dtype)
             peak_fl = pk["bf16_tflops"] * 1e12 if args.dtype == "bfloat16" else None
             prefill = {"value": round(pf["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(pf["ms"], 3),
@@ -388,8 +419,8 @@ def main() -> int:
     achieved = main_run["bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9
     line = {
         "metric": "decode tok/s at batch 8 (GPT-2 small, 512-token prompts, greedy)",
-        "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True,
+        "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": main_run["steps"],
+        "warmup": main_run["warmup"], "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": round(main_run["tok_s"] / 854.41, 2) if args.batch == 8 else None,
         "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic (seeded random weights and token ids)",
         "config": {"model": "gpt2-small", "n_layer": cfg["n_layer"], "n_layer_full": SMALL["n_layer"],

@@ -31,6 +31,7 @@ class LLM:
         self.sampler = Sampler(self.runner.device, engine.max_num_seqs)
         self._next_id = 0
         self._inflight = None          # (advanced step, sampler ticket, request id -> row) of a step whose tokens are not read yet
+        self._held: List[Response] = []     # responses read while aborting, handed out by the next step()
 
     # ------------------------------------------------------------------ low level
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -44,8 +45,15 @@ class LLM:
         self.scheduler.add(Request(request_id, list(prompt), params or SamplingParams()))
         return request_id
 
+    def abort(self, request_id: Hashable) -> bool:
+        """Stop a request: its pages and slot are free for others from the next step on.  True if
+        the request was still unfinished."""
+        if self._inflight is not None:
+            self._held += self._finalize()        # tokens that were on their way are still handed out by the next step()
+        return self.scheduler.abort(request_id) is not None
+
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished() or self._inflight is not None
+        return self.scheduler.has_unfinished() or self._inflight is not None or bool(self._held)
 
     def step(self) -> List[Response]:
         """Schedule, launch and sample one step; returns the tokens that became known.
@@ -58,7 +66,8 @@ class LLM:
         every other situation (prompts waiting or running, pages short) the tokens are read
         first and a call returns the tokens of its own step, as with
         ``async_scheduling=False``."""
-        out: List[Response] = []
+        out: List[Response] = self._held
+        self._held = []
         ahead = self.engine_config.async_scheduling and self.scheduler.can_run_ahead()
         if self._inflight is not None and not ahead:
             out += self._finalize()

@@ -299,6 +299,31 @@ class Scheduler:
         """advance and resolve in one call, for a caller that has the tokens at hand."""
         return self.resolve(self.advance(step), sampled)
 
+    def abort(self, request_id: Hashable) -> Optional[Request]:
+        """Take a request out wherever it stands: waiting requests just leave their queue, running
+        ones give back their pages and their slot.  Returns the request (state Aborted), or None
+        if no unfinished request has this id.  Tokens of a step that was launched before the
+        abort and is resolved after it are dropped."""
+        for q in (self.waiting, self.deferred_prefill):
+            for req in q:
+                if req.request_id == request_id:
+                    q.remove(req)
+                    req.state = RequestState.Aborted
+                    return req
+        for q in (self.prefill, self.decode, self.deferred_decode):
+            for req in q:
+                if req.request_id == request_id:
+                    q.remove(req)
+                    self.cache.release(req.request_id)
+                    # what an unresolved step computed for it is dropped; unread tokens leave the list
+                    while req.tokens and req.tokens[-1] == PENDING:
+                        req.tokens.pop()
+                    req.ended_at = len(req.tokens) - 1
+                    req.state = RequestState.Aborted
+                    self.admission_paused = False
+                    return req
+        return None
+
     def _finish(self, req: Request) -> None:
         self.cache.release(req.request_id)
         req.state = RequestState.Finished

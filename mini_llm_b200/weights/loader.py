@@ -1,4 +1,4 @@
-"""Loading a model's parameters from model.safetensors by tensor name.
+"""Loading a model's parameters from model.safetensors (or its shards) by tensor name.
 
 Every part declares its parameters (``param_specs``); the model description
 says which checkpoint tensor each one is (``WeightRef``).  All problems are
@@ -20,7 +20,7 @@ from typing import Dict, List
 import torch
 
 from ..parts.spec import ModelSpec
-from .safetensors_io import SafetensorsFile
+from .safetensors_io import Checkpoint
 
 
 class WeightsError(ValueError):
@@ -60,8 +60,8 @@ def target_dtype(role: str, engine_dtype: torch.dtype) -> torch.dtype:
 
 def load_weights(model, spec: ModelSpec, model_dir: str, rt) -> None:
     """Read, check, convert, upload and bind every parameter of ``model``."""
-    path = os.path.join(model_dir, "model.safetensors")
-    sf = SafetensorsFile(path)
+    sf = Checkpoint(model_dir)       # model.safetensors, or the shards named by model.safetensors.index.json
+    path = sf.path
     try:
         names = set(sf.names())
         used = set()

@@ -130,3 +130,73 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]], me
             if t.numel():
                 f.write(t.view(torch.uint8).numpy().tobytes() if t.dim() else t.reshape(1).view(torch.uint8).numpy().tobytes())
     os.replace(tmp, path)
+
+
+class Checkpoint:
+    """The tensors of a model folder: ``model.safetensors``, or the shards that
+    ``model.safetensors.index.json`` names (its ``weight_map``: tensor name -> file).  Same
+    interface as one SafetensorsFile."""
+
+    INDEX = "model.safetensors.index.json"
+
+    def __init__(self, model_dir: str):
+        single = os.path.join(model_dir, "model.safetensors")
+        index = os.path.join(model_dir, self.INDEX)
+        self._files: Dict[str, SafetensorsFile] = {}
+        self._where: Dict[str, SafetensorsFile] = {}
+        if os.path.isfile(single) or not os.path.isfile(index):
+            self.path = single
+            f = SafetensorsFile(single)                  # raises when neither file exists
+            self._files[single] = f
+            self._where = {n: f for n in f.names()}
+            return
+        self.path = index
+        try:
+            with open(index, "r", encoding="utf-8") as fh:
+                weight_map = json.load(fh)["weight_map"]
+            if not isinstance(weight_map, dict):
+                raise TypeError("weight_map is not an object")
+        except (OSError, KeyError, TypeError, json.JSONDecodeError) as e:
+            raise SafetensorsError(f"{index}: not a usable index: {e}") from e
+        try:
+            for name, fname in weight_map.items():
+                fpath = os.path.join(model_dir, str(fname))
+                f = self._files.get(fpath)
+                if f is None:
+                    f = self._files[fpath] = SafetensorsFile(fpath)
+                if name not in f:
+                    raise SafetensorsError(f"{index}: tensor {name!r} is not in {fname!r}")
+                self._where[name] = f
+            # a tensor that a shard holds but the index does not list is reported as unexpected by the loader
+            for f in list(self._files.values()):
+                for n in f.names():
+                    self._where.setdefault(n, f)
+        except Exception:
+            self.close()
+            raise
+
+    def names(self) -> List[str]:
+        return list(self._where)
+
+    def shape(self, name: str) -> Tuple[int, ...]:
+        return self._where[name].shape(name)
+
+    def dtype(self, name: str) -> torch.dtype:
+        return self._where[name].dtype(name)
+
+    def __contains__(self, name: str) -> bool:
+        return name in self._where
+
+    def tensor(self, name: str) -> torch.Tensor:
+        return self._where[name].tensor(name)
+
+    def close(self):
+        for f in self._files.values():
+            f.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+

@@ -175,6 +175,32 @@ def test_running_ahead_gives_the_same_tokens_as_reading_every_step(setup):
             assert o[-1][1] and all(not f for _, f in o[:-1])
 
 
+def test_abort_while_running_ahead(setup):
+    """A request stopped in the middle of decoding: the others' tokens are what they are without the
+    abort, the stopped one hands out no token after the call that stopped it, its pages come back."""
+    import mini_llm_b200 as m
+    cfg, dtype, page = setup["cfg"], setup["dtype"], setup["page"]
+    prompts = [random_ids(n, cfg["vocab_size"], 600 + n) for n in (12, 7, 25)]
+    sp = m.SamplingParams(max_new_tokens=12, ignore_eos=True)
+    base = m.LLM(setup["dir"], dtype=dtype, page_size=page, max_tokens=512, max_num_seqs=4).generate(prompts, sp)
+    llm = m.LLM(setup["dir"], dtype=dtype, page_size=page, max_tokens=512, max_num_seqs=4)
+    ids = [llm.add_request(p, sp) for p in prompts]
+    out = {i: [] for i in ids}
+    stopped_at = None
+    while llm.has_unfinished():
+        for r in llm.step():
+            out[r.request_id].append(r.token)
+        if stopped_at is None and len(out[ids[1]]) >= 4:
+            assert llm.abort(ids[1])
+            assert not llm.abort(ids[1])
+            stopped_at = True
+    n1 = len(out[ids[1]])
+    assert 4 <= n1 <= 6 and out[ids[1]] == base[1][:n1]          # at most the tokens that were already on their way
+    assert out[ids[0]] == base[0] and out[ids[2]] == base[2]
+    llm.runner.cache.check()
+    assert llm.runner.cache.num_live == 0 and llm.runner.cache.num_free_pages() == llm.runner.num_pages
+
+
 def test_command_line(setup, tmp_path):
     cfg, dtype = setup["cfg"], setup["dtype"]
     p1, p2 = random_ids(6, cfg["vocab_size"], 1), random_ids(11, cfg["vocab_size"], 2)

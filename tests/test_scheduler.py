@@ -284,3 +284,37 @@ def test_running_ahead_stops_while_pages_are_short_or_prompts_wait():
     assert len(out[0]) == 11 and len(out[1]) == 12      # request 0 had one token before
     assert cm.num_live == 0
     cm.check()
+
+
+def test_abort_frees_pages_and_drops_what_was_on_its_way():
+    from mini_llm_b200.engine.scheduler import PENDING
+    cm, s = make(num_pages=32, budget=64, chunk=64)
+    for i, n in enumerate((6, 9, 4)):
+        s.add(Request(i, list(range(20, 20 + n)), SamplingParams(max_new_tokens=10, ignore_eos=True)))
+    s.add(Request(7, [1, 2, 3], SamplingParams(max_new_tokens=4)))
+    st = s.schedule()                               # max_num_seqs is 4: all four are admitted
+    s.update(st, [1000, 1001, 1002, 1003])
+    free_before = cm.num_free_pages()
+    # a running request: pages and slot come back at once
+    gone = s.abort(1)
+    assert gone is not None and gone.state == RequestState.Aborted
+    assert cm.num_free_pages() > free_before and not cm.is_live(1)
+    assert s.abort(1) is None                       # only once
+    # a step that was advanced before the abort: its token for the aborted request is dropped
+    st = s.schedule()
+    assert sorted(e.request.request_id for e in st.entries) == [0, 2, 7]
+    adv = s.advance(st)
+    r2 = next(e.request for e in st.entries if e.request.request_id == 2)
+    assert r2.tokens[-1] == PENDING
+    s.abort(2)
+    assert PENDING not in r2.tokens and r2.tokens[-1] == 1002
+    out = s.resolve(adv, [2000, 2002, 2007])
+    assert [(r.request_id, r.token) for r in out] == [(0, 2000), (7, 2007)]
+    # a waiting request leaves its queue; the rest run to their ends
+    s.add(Request(9, [5, 6], SamplingParams(max_new_tokens=3)))
+    s.add(Request(10, [5, 6, 7], SamplingParams(max_new_tokens=3)))
+    assert s.abort(10).state == RequestState.Aborted
+    done, _ = run(s, cm)
+    assert set(done) == {0, 7, 9} and len(done[9]) == 3
+    cm.check()
+    assert cm.num_live == 0 and cm.num_free_pages() == 32

@@ -128,3 +128,36 @@ def test_random_weights_mode_writes_a_loadable_folder(tmp_path):
     d4 = m.write_random_model(CONFIG_A, 1, str(tmp_path / "d"), dtype="bfloat16")
     with SafetensorsFile(os.path.join(d4, "model.safetensors")) as f:
         assert f.dtype("wte.weight") == torch.bfloat16
+
+
+def test_sharded_checkpoint_with_an_index(tmp_path):
+    """model.safetensors.index.json names the shard of every tensor; loading gives the same model, and the
+    single error still lists what is missing, unexpected or misshapen across the shards."""
+    t = make_tensors(CONFIG_A, 5)
+    whole = write_model(str(tmp_path / "whole"), CONFIG_A, t)
+    d = tmp_path / "sharded"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(CONFIG_A))
+    names = sorted(t)
+    shards = {"model-00001-of-00002.safetensors": names[:len(names) // 2], "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+    for fname, ns in shards.items():
+        write_safetensors(str(d / fname), [(n, t[n]) for n in ns])
+    (d / "model.safetensors.index.json").write_text(json.dumps(
+        {"metadata": {}, "weight_map": {n: f for f, ns in shards.items() for n in ns}}))
+    _, _, a = _load(whole)
+    _, _, b = _load(str(d))
+    for la, lb in zip(a.layers, b.layers):
+        assert torch.equal(la.mixer.qkv_weight, lb.mixer.qkv_weight) and torch.equal(la.ff.proj_weight, lb.ff.proj_weight)
+    assert torch.equal(a.embedding.table, b.embedding.table)
+    # a shard that lacks a tensor the index promises
+    write_safetensors(str(d / "model-00002-of-00002.safetensors"), [(n, t[n]) for n in shards["model-00002-of-00002.safetensors"][1:]])
+    with pytest.raises(SafetensorsError, match="is not in"):
+        _load(str(d))
+    # an extra tensor in a shard and a wrong shape elsewhere: one error for both
+    extra = [(n, t[n]) for n in shards["model-00002-of-00002.safetensors"]] + [("stray.weight", torch.zeros(2))]
+    write_safetensors(str(d / "model-00002-of-00002.safetensors"), extra)
+    first = shards["model-00001-of-00002.safetensors"]
+    write_safetensors(str(d / "model-00001-of-00002.safetensors"), [(n, t[n] if n != first[0] else torch.zeros(3, 3)) for n in first])
+    with pytest.raises(WeightsError) as e:
+        _load(str(d))
+    assert "stray.weight" in e.value.unexpected and e.value.wrong_shape and e.value.wrong_shape[0][0] == first[0]
