@@ -81,8 +81,15 @@ template <> struct Exp<__nv_bfloat16> {
     }
 };
 
-template <typename T, int LPK, int MODE, bool ONE>        // ONE: every CTA takes exactly one split
-__global__ void __launch_bounds__(THREADS)
+// Keys and values of a split can be staged in shared memory (cp.async, no registers held while they fly) when a
+// split's rows fit there: bfloat16 with heads up to 64.  That leaves room for six CTAs per SM instead of four,
+// which pays as soon as the grid is larger than four CTAs per SM; smaller grids keep the rows in registers,
+// one hop less on the way.  The arithmetic is the same either way.
+template <typename T, int LPK> struct Staged { static constexpr bool value = sizeof(T) == 2 && LPK * Vec16<T>::N <= 64; };
+
+// ONE: every CTA takes exactly one split.  STG: keys and values go through shared memory.
+template <typename T, int LPK, int MODE, bool ONE, bool STG>
+__global__ void __launch_bounds__(THREADS, STG ? 6 : 0)
 attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
                    const T* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
                    const int* __restrict__ token_seq, const int* __restrict__ positions, T* __restrict__ out,
@@ -99,8 +106,12 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
     // One split per CTA in a cluster: every CTA writes its (o, m, l) straight into the shared memory of the
     // CTA that merges, so the merge reads local memory only and the others may leave after one barrier.
     constexpr bool PUSH = MODE == MODE_CLUSTER && ONE;
+    constexpr bool STAGE = STG;
+    static_assert(!STG || Staged<T, LPK>::value, "a split's rows do not fit the staging area");
     __shared__ float sm_m[NG], sm_l[NG], sm_w[NG];
-    __shared__ float sm_o[NG * DH];
+    __shared__ __align__(16) uint4 s_stage[STAGE ? 2 * SPLIT * LPK : 1];   // a split's keys, then its values: [key][16-byte piece]
+    __shared__ float sm_o_own[STAGE ? 1 : NG * DH];
+    float* sm_o = STAGE ? reinterpret_cast<float*>(s_stage) : sm_o_own;   // staged: the groups' outputs reuse the keys' space
     __shared__ float sm_res[(PUSH ? MAX_CLUSTER : MODE == MODE_SCRATCH || ONE ? 1 : MAX_SPC) * RES];
     __shared__ int s_last;
     const int cx = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
@@ -180,24 +191,42 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
                 ok[u] = kp < k_hi && kp >= first;
                 page[u] = ok[u] ? bt[page_index(kp)] : 0;
             }
-            uint4 kr[UNR], vr[UNR];
+            uint4 kr[STAGE ? 1 : UNR], vr[STAGE ? 1 : UNR];
+            uint4* sk = s_stage;
+            uint4* sv = s_stage + SPLIT * LPK;
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
                 const int kp = kb + u * NG;
-                kr[u] = make_uint4(0, 0, 0, 0);
-                vr[u] = make_uint4(0, 0, 0, 0);
-                if (ok[u]) {
-                    const size_t off = (((size_t)page[u] * Hkv + hk) * page_size + page_offset(kp)) * DH + li * VEC;
-                    kr[u] = *reinterpret_cast<const uint4*>(k_pages + off);
-                    vr[u] = *reinterpret_cast<const uint4*>(v_pages + off);
+                size_t off = 0;
+                if (ok[u]) off = (((size_t)page[u] * Hkv + hk) * page_size + page_offset(kp)) * DH + li * VEC;
+                if constexpr (STAGE) {
+                    // 16 bytes of the key row and of the value row to this lane's own places (zeros where the key is not visible)
+                    const int idx = (kp - k_lo) * LPK + li;
+                    const int nbytes = ok[u] ? 16 : 0;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(sk + idx)),
+                                 "l"(k_pages + off), "r"(nbytes) : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(sv + idx)),
+                                 "l"(v_pages + off), "r"(nbytes) : "memory");
+                } else {
+                    kr[u] = make_uint4(0, 0, 0, 0);
+                    vr[u] = make_uint4(0, 0, 0, 0);
+                    if (ok[u]) {
+                        kr[u] = *reinterpret_cast<const uint4*>(k_pages + off);
+                        vr[u] = *reinterpret_cast<const uint4*>(v_pages + off);
+                    }
                 }
+            }
+            if constexpr (STAGE) {
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                asm volatile("cp.async.wait_group 0;" ::: "memory");      // a lane reads back only what it brought itself
             }
             float s[UNR];
             float mx = m;
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
                 float kv[VEC];
-                Vec16<T>::unpack(kr[u], kv);
+                if constexpr (STAGE) Vec16<T>::unpack(sk[(kb + u * NG - k_lo) * LPK + li], kv);
+                else Vec16<T>::unpack(kr[u], kv);
                 float d = 0.f;
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) d = fmaf(qv[i], kv[i], d);
@@ -215,7 +244,8 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
                 for (int u = 0; u < UNR; ++u) {
                     const float pr = ok[u] ? Exp<T>::of(s[u] - mx) : 0.f;
                     float vv[VEC];
-                    Vec16<T>::unpack(vr[u], vv);
+                    if constexpr (STAGE) Vec16<T>::unpack(sv[(kb + u * NG - k_lo) * LPK + li], vv);
+                    else Vec16<T>::unpack(vr[u], vv);
                     l += pr;
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) o[i] = fmaf(pr, vv[i], o[i]);
@@ -224,6 +254,7 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
             }
         }
         // the groups of the CTA are merged in group order
+        if constexpr (STAGE) __syncthreads();                 // every group has read its keys: their space takes the outputs
         if (li == 0) { sm_m[gi] = m; sm_l[gi] = l; }
 #pragma unroll
         for (int i = 0; i < VEC; ++i) sm_o[gi * DH + li * VEC + i] = o[i];
@@ -374,11 +405,22 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
     dim3 grid(ctas, H, T_tokens);
 #define ARGS (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table, bt_stride, token_seq, positions, \
              (T*)out, out_stride, part_o, part_ml, counters, H, Hkv, page_size, scale, window, max_splits, spc
-    if (!scratch_path && ctas == 1) {
-        MLLM_CUDA(mllm_launch(attn_decode_kernel<T, LPK, MODE_LOCAL, false>, grid, dim3(THREADS), 0, stream, true, ARGS));
-        return 0;
-    }
-    if (!scratch_path && ctas <= MAX_CLUSTER) {
+    using K = void (*)(const T*, long long, const T*, const T*, const int*, int, const int*, const int*, T*, long long,
+                       float*, float*, unsigned int*, int, int, int, float, int, int, int);
+    constexpr bool CAN_STAGE = Staged<T, LPK>::value;
+    const bool stg = CAN_STAGE && pairs * ctas > 2LL * decode_sm_count();     // measured: from about two CTAs per SM on
+    const int mode = scratch_path ? MODE_SCRATCH : ctas == 1 ? MODE_LOCAL : ctas <= MAX_CLUSTER ? MODE_CLUSTER : MODE_SCRATCH;
+    const bool one = spc == 1 && mode != MODE_LOCAL;
+    K kern;
+#define PICK(M, O)                                                                     \
+    kern = stg ? (K)attn_decode_kernel<T, LPK, M, O, CAN_STAGE> : (K)attn_decode_kernel<T, LPK, M, O, false>
+    if (mode == MODE_LOCAL) PICK(MODE_LOCAL, false);
+    else if (mode == MODE_CLUSTER && one) PICK(MODE_CLUSTER, true);
+    else if (mode == MODE_CLUSTER) PICK(MODE_CLUSTER, false);
+    else if (one) PICK(MODE_SCRATCH, true);
+    else PICK(MODE_SCRATCH, false);
+#undef PICK
+    if (mode == MODE_CLUSTER) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(THREADS);
@@ -392,14 +434,10 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = g_mllm_pdl ? 2 : 1;
-        if (spc == 1) MLLM_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel<T, LPK, MODE_CLUSTER, true>, ARGS));
-        else MLLM_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel<T, LPK, MODE_CLUSTER, false>, ARGS));
+        MLLM_CUDA(cudaLaunchKernelEx(&cfg, kern, ARGS));
         return 0;
     }
-    if (spc == 1)
-        MLLM_CUDA(mllm_launch(attn_decode_kernel<T, LPK, MODE_SCRATCH, true>, grid, dim3(THREADS), 0, stream, true, ARGS));
-    else
-        MLLM_CUDA(mllm_launch(attn_decode_kernel<T, LPK, MODE_SCRATCH, false>, grid, dim3(THREADS), 0, stream, true, ARGS));
+    MLLM_CUDA(mllm_launch(kern, grid, dim3(THREADS), 0, stream, true, ARGS));
 #undef ARGS
     return 0;
 }
