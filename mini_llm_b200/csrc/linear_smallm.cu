@@ -103,8 +103,23 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
         }
     };
     load_w(warp, wa, wb);
+    const bool two_rounds = warp + WARPS * U < nchunks;
+    if (two_rounds) load_w(warp + WARPS * U, wa_next, wb_next);     // a second round too: K up to 2 x 32 x WARPS x U needs no load after the wait
+    if constexpr (LN) {
+        // gamma and beta are weights as well: into shared memory now, so that normalising costs no trip to L2 later
+        if (ln_smem) {
+            float* gb = reinterpret_cast<float*>(xs + (size_t)M * xs_stride);
+            for (int k = threadIdx.x * 4; k < K; k += WARPS * 32 * 4) {
+                *reinterpret_cast<float4*>(gb + k) = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
+                *reinterpret_cast<float4*>(gb + K + k) = __ldg(reinterpret_cast<const float4*>(ln.beta + k));
+            }
+        }
+    }
     pdl_wait();                 // everything below reads what earlier kernels of the step wrote
     pdl_launch();
+    if constexpr (LN) {
+        if (ln_smem) __syncthreads();               // gamma and beta are in shared memory for every warp
+    }
 
     // The epilogue's operands of this thread's first output element, fetched early as well.
     const int e_row = threadIdx.x % ROWS, e_col = threadIdx.x / ROWS;
@@ -165,8 +180,9 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
                 for (int i = 0; i < KEEP; ++i) {
                     const int k = lane * 4 + i * 128;
                     if (k < K) {
-                        const float4 ga = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
-                        const float4 be = __ldg(reinterpret_cast<const float4*>(ln.beta + k));
+                        const float* gb = reinterpret_cast<const float*>(xs + (size_t)M * xs_stride);   // staged before the wait (fits: K <= 1024)
+                        const float4 ga = *reinterpret_cast<const float4*>(gb + k);
+                        const float4 be = *reinterpret_cast<const float4*>(gb + K + k);
                         uint2 pk;
                         pk.x = pack2((keep[i].x - mean) * rstd * ga.x + be.x, (keep[i].y - mean) * rstd * ga.y + be.y);
                         pk.y = pack2((keep[i].z - mean) * rstd * ga.z + be.z, (keep[i].w - mean) * rstd * ga.w + be.w);
@@ -188,7 +204,7 @@ linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
 
     for (int c0 = warp; c0 < nchunks; c0 += WARPS * U) {
         const bool more = c0 + WARPS * U < nchunks;
-        if (more) load_w(c0 + WARPS * U, wa_next, wb_next);     // the next round's weights fly while this one is used
+        if (more && c0 != warp) load_w(c0 + WARPS * U, wa_next, wb_next);     // the next round's weights fly while this one is used (the second round went out before the wait)
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int k = (c0 + u * WARPS) * 32 + 8 * t;
@@ -290,7 +306,7 @@ template <int MT, int RT, typename TO, bool LN, bool KVW>
 int launch_k(const Call& c) {
     constexpr int ROWS = RT == 0 ? 8 : 16 * RT;
     size_t smem = (size_t)WARPS * ROWS * 8 * MT * sizeof(float);
-    if (LN && c.K <= 1024) smem += (size_t)c.M * (c.K + 8) * sizeof(__nv_bfloat16);   // the normed rows
+    if (LN && c.K <= 1024) smem += (size_t)c.M * (c.K + 8) * sizeof(__nv_bfloat16) + 2 * (size_t)c.K * sizeof(float);   // the normed rows, gamma and beta
     auto kern = linear_smallm_kernel<MT, RT, TO, LN, KVW>;
     if (smem > 48 * 1024) {
         static size_t set = 0;                     // per instantiation: the largest size asked for so far
