@@ -90,8 +90,9 @@ template <typename T, int LPK> struct Staged { static constexpr bool value = siz
 // ONE: every CTA takes exactly one split.  STG: keys and values go through shared memory.
 template <typename T, int LPK, int MODE, bool ONE, bool STG>
 __global__ void __launch_bounds__(THREADS, STG ? 6 : 0)
-attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
-                   const T* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
+attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // written by kernels of this step: no __restrict__,
+                   const T* v_pages,                                        // the compiler must not read them on the non-coherent path
+                   const int* __restrict__ block_table, int bt_stride,
                    const int* __restrict__ token_seq, const int* __restrict__ positions, T* __restrict__ out,
                    long long out_stride, float* __restrict__ part_o, float* __restrict__ part_ml,
                    unsigned int* __restrict__ counters, int H, int Hkv, int page_size, float scale, int window,
@@ -115,10 +116,15 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
     __shared__ float sm_res[(PUSH ? MAX_CLUSTER : MODE == MODE_SCRATCH || ONE ? 1 : MAX_SPC) * RES];
     __shared__ int s_last;
     const int cx = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
-    pdl_wait();
+    // Positions, the request index and the block table are written by the host before the step, and the rows of
+    // all keys before the token's own position were written by earlier steps: all of that is read before the
+    // wait on the previous kernel, which only brings the queries and the token's own key and value.
+    // Everything read before the wait goes to L2 (ld.global.cg / cp.async.cg): a kernel that starts while its
+    // predecessors still run finds whatever earlier kernels left in this SM's L1, and with rows shorter than a
+    // cache line that can be a line fetched before a neighbouring row was written.
     pdl_launch();
-    const int p = positions[t];
-    const int seq = token_seq[t];
+    const int p = __ldcg(positions + t);
+    const int seq = __ldcg(token_seq + t);
     int first = 0;
     if (window > 0 && p - window + 1 > 0) first = p - window + 1;
     const int s_lo = first / SPLIT, s_hi = p / SPLIT;         // splits that have work, inclusive
@@ -151,11 +157,8 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
     auto page_index = [&](int kp) { return pow2 ? kp >> pshift : kp / page_size; };
     auto page_offset = [&](int kp) { return pow2 ? kp & pmask : kp % page_size; };
 
-    const uint4 qraw = *reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)h * DH + li * VEC);
-    float qv[VEC];
-    Vec16<T>::unpack(qraw, qv);
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) qv[i] *= scale * Exp<T>::QSCALE;
+    float qv[VEC];                                            // loaded after the wait, in the first split's turn
+    bool waited = false;
     const size_t pair = (size_t)t * H + h;
 
     if constexpr (!ONE) {
@@ -166,7 +169,7 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
 #pragma unroll 4
         for (int kp = (my_lo + 1) * SPLIT + (int)threadIdx.x; kp < k_end; kp += THREADS) {
             if (kp < first) continue;
-            const size_t off = (((size_t)bt[page_index(kp)] * Hkv + hk) * page_size + page_offset(kp)) * DH;
+            const size_t off = (((size_t)__ldcg(bt + page_index(kp)) * Hkv + hk) * page_size + page_offset(kp)) * DH;
 #pragma unroll
             for (int b = 0; b < ROW_BYTES; b += 128) {
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(k_pages + off) + b));
@@ -189,14 +192,28 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
             for (int u = 0; u < UNR; ++u) {
                 const int kp = kb + u * NG;
                 ok[u] = kp < k_hi && kp >= first;
-                page[u] = ok[u] ? bt[page_index(kp)] : 0;
+                page[u] = ok[u] ? __ldcg(bt + page_index(kp)) : 0;
             }
             uint4 kr[STAGE ? 1 : UNR], vr[STAGE ? 1 : UNR];
             uint4* sk = s_stage;
             uint4* sv = s_stage + SPLIT * LPK;
 #pragma unroll
+            for (int pass = 0; pass < 2; ++pass) {            // pass 0: the keys of earlier steps; pass 1, after the wait: the token's own
+            if (pass == 1) {
+                if (!waited) {
+                    pdl_wait();
+                    waited = true;
+                    // (what the previous kernel wrote is read past L1 as well)
+                    const uint4 qraw = __ldcg(reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)h * DH + li * VEC));
+                    Vec16<T>::unpack(qraw, qv);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) qv[i] *= scale * Exp<T>::QSCALE;
+                }
+            }
+#pragma unroll
             for (int u = 0; u < UNR; ++u) {
                 const int kp = kb + u * NG;
+                if ((kp == p) != (pass == 1)) continue;
                 size_t off = 0;
                 if (ok[u]) off = (((size_t)page[u] * Hkv + hk) * page_size + page_offset(kp)) * DH + li * VEC;
                 if constexpr (STAGE) {
@@ -211,10 +228,11 @@ attn_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restr
                     kr[u] = make_uint4(0, 0, 0, 0);
                     vr[u] = make_uint4(0, 0, 0, 0);
                     if (ok[u]) {
-                        kr[u] = *reinterpret_cast<const uint4*>(k_pages + off);
-                        vr[u] = *reinterpret_cast<const uint4*>(v_pages + off);
+                        kr[u] = __ldcg(reinterpret_cast<const uint4*>(k_pages + off));
+                        vr[u] = __ldcg(reinterpret_cast<const uint4*>(v_pages + off));
                     }
                 }
+            }
             }
             if constexpr (STAGE) {
                 asm volatile("cp.async.commit_group;" ::: "memory");

@@ -65,8 +65,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 template <int DH>
 __global__ void __launch_bounds__(GROUPS * WARPS * 32, DH <= 64 ? 2 : 1)
-attention_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
-                       const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+attention_flash_kernel(const __nv_bfloat16* q, long long q_stride,          // q and the pages are written by kernels of this step:
+                       const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages,   // no __restrict__, never the non-coherent load path
                        const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tiles,
                        const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, long long out_stride,
                        int H, int Hkv, int page_size, float scale, int window) {

@@ -23,8 +23,8 @@ constexpr int MAX_DH = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
-attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
-                      const T* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
+attention_simt_kernel(const T* q, long long q_stride, const T* k_pages,     // written by kernels of this step: no __restrict__
+                      const T* v_pages, const int* __restrict__ block_table, int bt_stride,
                       const int* __restrict__ token_seq, const int* __restrict__ positions, T* __restrict__ out,
                       long long out_stride, int T_tokens, int H, int Hkv, int dh, int page_size, float scale,
                       int window) {

@@ -19,8 +19,8 @@ constexpr int BQ = 64, BK = 32, THREADS = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
-attention_tiled_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
-                       const T* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
+attention_tiled_kernel(const T* q, long long q_stride, const T* k_pages,    // written by kernels of this step: no __restrict__
+                       const T* v_pages, const int* __restrict__ block_table, int bt_stride,
                        const int* __restrict__ tiles, const int* __restrict__ positions, T* __restrict__ out,
                        long long out_stride, int H, int Hkv, int dh, int page_size, float scale, int window) {
     extern __shared__ float sm[];

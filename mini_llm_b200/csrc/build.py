@@ -23,7 +23,11 @@ from typing import List, Optional
 CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libmini_llm_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
-NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+# -dlcm=cg: plain global loads go to L2, not through L1.  With programmatic dependent launch a kernel is already
+# resident while the kernel before it writes its inputs, and an L1 line left by an earlier kernel on the same SM
+# can then still be read just after the dependency wait returns (seen as a stale query row in decode attention).
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xptxas", "-dlcm=cg", "-Xcompiler", "-fPIC", "-Xcompiler",
+              "-fvisibility=hidden"]
 
 
 class BuildError(RuntimeError):

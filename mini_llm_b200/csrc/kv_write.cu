@@ -7,7 +7,7 @@
 #include "common.cuh"
 
 template <typename T>
-__global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v, long long row_stride,
+__global__ void kv_write_kernel(const T* k, const T* v, long long row_stride,
                                 T* __restrict__ k_pages, T* __restrict__ v_pages,
                                 const int* __restrict__ slots, int Hkv, int dh, int page_size) {
     const int t = blockIdx.x;
@@ -30,7 +30,7 @@ __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v
 // The same copy in 16-byte pieces: a thread moves one piece of a key row and of a value row.
 template <typename T>
 __global__ void __launch_bounds__(256)
-kv_write_vec_kernel(const T* __restrict__ k, const T* __restrict__ v, long long row_stride, T* __restrict__ k_pages,
+kv_write_vec_kernel(const T* k, const T* v, long long row_stride, T* __restrict__ k_pages,
                     T* __restrict__ v_pages, const int* __restrict__ slots, int T_tokens, int Hkv, int dh,
                     int page_size) {
     constexpr int VEC = 16 / sizeof(T);

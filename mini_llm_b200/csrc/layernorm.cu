@@ -6,7 +6,7 @@
 #include "common.cuh"
 
 template <typename TOut>
-__global__ void layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+__global__ void layernorm_kernel(const float* x, const int* __restrict__ rows,
                                  const float* __restrict__ gamma, const float* __restrict__ beta,
                                  TOut* __restrict__ out, int D, float eps) {
     __shared__ float scratch[33];
@@ -34,7 +34,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
 // a row whatever the number of rows.
 template <typename TOut>
 __global__ void __launch_bounds__(256)
-layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ gamma,
+layernorm_warp_kernel(const float* x, const int* __restrict__ rows, const float* __restrict__ gamma,
                       const float* __restrict__ beta, TOut* __restrict__ out, int R, int D, float eps) {
     constexpr int KEEP = 16;
     pdl_wait();

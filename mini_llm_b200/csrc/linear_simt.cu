@@ -22,7 +22,7 @@ constexpr int THREADS = (BM / TM) * (BN / TN);   // 256
 constexpr int PAD = 4;
 
 template <typename T>
-__device__ __forceinline__ void load4(const T* __restrict__ base, long long ld, int row, int nrows, int k, int K,
+__device__ __forceinline__ void load4(const T* base, long long ld, int row, int nrows, int k, int K,
                                       bool vec, float (&v)[4]) {
     v[0] = v[1] = v[2] = v[3] = 0.f;
     if (row >= nrows) return;
@@ -46,7 +46,7 @@ __device__ __forceinline__ void load4(const T* __restrict__ base, long long ld, 
 
 template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(THREADS)
-linear_simt_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, const float* __restrict__ bias,
+linear_simt_kernel(const TA* A, long long lda, const TW* __restrict__ W, const float* __restrict__ bias,
                    TO* out, long long ldo, int M, int N, int K, int act, int accumulate, int vecA, int vecW) {
     __shared__ float As[BK][BM + PAD];
     __shared__ float Ws[BK][BN + PAD];
@@ -109,7 +109,7 @@ constexpr int LBM = 128, LBN = 128, LBK = 16, LTHREADS = 256;
 
 template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(LTHREADS)
-linear_simt_large_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ W,
+linear_simt_large_kernel(const TA* A, long long lda, const TW* __restrict__ W,
                          const float* __restrict__ bias, TO* out, long long ldo, int M, int N, int K, int act,
                          int accumulate, int vecA, int vecW) {
     __shared__ float As[2][LBK][LBM + 4];

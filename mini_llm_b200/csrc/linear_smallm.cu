@@ -28,7 +28,7 @@ __device__ __forceinline__ uint4 ldg16(const void* p) {
     return v;
 }
 __device__ __forceinline__ uint4 ldg16_cached(const void* p) {
-    return __ldg(reinterpret_cast<const uint4*>(p));
+    return __ldcg(reinterpret_cast<const uint4*>(p));     // the previous kernel's output: past L1, never the non-coherent path
 }
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -65,7 +65,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 
 template <int MT, int RT_, typename TO, bool LN, bool KVW>
 __global__ void __launch_bounds__(WARPS * 32)
-linear_smallm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ W,
+linear_smallm_kernel(const __nv_bfloat16* x, long long ldx, const __nv_bfloat16* __restrict__ W,
                      const float* __restrict__ bias, TO* out, long long ldo, int M, int N, int K, int act,
                      int accumulate, NormArgs ln, KvArgs kv) {
     // RT_ == 0 stands for half a row tile: 8 weight rows per CTA (the upper half of the MMA's 16 rows

@@ -17,7 +17,7 @@ constexpr int WARPS = 8;
 
 template <int MT>     // tokens held in registers: 4, 8 or 16
 __global__ void __launch_bounds__(WARPS * 32)
-linear_smallm_f32_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ W,
+linear_smallm_f32_kernel(const float* x, long long ldx, const float* __restrict__ W,
                          const float* __restrict__ bias, float* out, long long ldo, int M, int N, int K, int act,
                          int accumulate) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -51,7 +51,7 @@ linear_smallm_f32_kernel(const float* __restrict__ x, long long ldx, const float
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 if (m < M) {
-                    const float4 xv = __ldg(reinterpret_cast<const float4*>(x + (size_t)m * ldx + k));
+                    const float4 xv = __ldcg(reinterpret_cast<const float4*>(x + (size_t)m * ldx + k));
                     acc[m] = fmaf(cur[u].x, xv.x, acc[m]);
                     acc[m] = fmaf(cur[u].y, xv.y, acc[m]);
                     acc[m] = fmaf(cur[u].z, xv.z, acc[m]);

@@ -14,7 +14,7 @@ namespace {
 constexpr int SAMPLE_THREADS = 1024;
 
 __global__ void __launch_bounds__(256)
-argmax_kernel(const float* __restrict__ logits, long long ld, int V, int* __restrict__ out) {
+argmax_kernel(const float* logits, long long ld, int V, int* __restrict__ out) {
     __shared__ float bv[256];
     __shared__ int bi[256];
     pdl_wait();
@@ -45,7 +45,7 @@ argmax_kernel(const float* __restrict__ logits, long long ld, int V, int* __rest
 // argmax of long rows with few rows in the batch: every row is cut into slices, one CTA
 // each; the CTA that finishes a row last (a counter it resets) reduces the slices' results.
 __global__ void __launch_bounds__(256)
-argmax_sliced_kernel(const float* __restrict__ logits, long long ld, int V, int* __restrict__ out,
+argmax_sliced_kernel(const float* logits, long long ld, int V, int* __restrict__ out,
                      float* __restrict__ part_val, int* __restrict__ part_idx, unsigned int* __restrict__ counters) {
     __shared__ float bv[256];
     __shared__ int bi[256];
@@ -97,7 +97,7 @@ argmax_sliced_kernel(const float* __restrict__ logits, long long ld, int V, int*
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
+sample_kernel(const float* logits, long long ld, int V, const float* __restrict__ temperature,
               const float* __restrict__ uniform, int* __restrict__ out) {
     __shared__ float scratch[33];
     __shared__ float sums[SAMPLE_THREADS];

@@ -255,14 +255,15 @@ def decode_splits(max_ctx_len: int) -> int:
 def _small_m_wins(M: int, N: int, K: int) -> bool:
     """Whether the weight-streaming kernel (mma.sync, K split over warps) beats the tensor-memory
     kernel for M rows.  Measured on GPT-2 small's shapes in a replayed graph: the streaming
-    kernel's time grows with M*N while the other stays near its fixed cost of about 6 us per 768
-    of K; with a long K the streaming kernel keeps winning up to its limit of 64 rows, and a
-    matrix as tall as a vocabulary is streamed faster by the tensor-memory kernel from 9 rows on."""
-    if M > SMALL_M:
+    kernel's time grows with M*N (2.5-5 us up to 32 rows, 8-20 us at 48-64 rows, where it reads
+    its input rows from L2 again and again) while the other stays near its fixed cost of about
+    6 us per 768 of K; a matrix as tall as a vocabulary is streamed faster by the tensor-memory
+    kernel from 9 rows on."""
+    if M > 32:
         return False
     if N >= 16384:
         return M <= 8
-    return K > 2048 or M * N <= 80_000
+    return M * N <= 80_000
 
 
 def _fusable(weight, M, K) -> bool:
