@@ -4,7 +4,7 @@
 //
 // One warp per weight row: a lane reads 16 bytes of the row at k = 4*lane, 4*lane + 128, ...
 // (512 contiguous bytes per warp and step, several steps in flight) and the matching values
-// of every token's row of x (from L1/L2), multiplies with fmaf into one accumulator per
+// of every token's row of x (staged in shared memory once per CTA when they fit), multiplies with fmaf into one accumulator per
 // token, and the warp adds its lanes' sums with shuffles.  The order of the additions
 // depends on K only, so a token's result does not change with the batch.  No tensor core,
 // no reduced-precision mode.  The reference's small-M kernel is a 1x32 SIMT tile
@@ -19,23 +19,33 @@ template <int MT>     // tokens held in registers: 4, 8 or 16
 __global__ void __launch_bounds__(WARPS * 32)
 linear_smallm_f32_kernel(const float* x, long long ldx, const float* __restrict__ W,
                          const float* __restrict__ bias, float* out, long long ldo, int M, int N, int K, int act,
-                         int accumulate) {
+                         int accumulate, int staged) {
+    extern __shared__ __align__(16) float xs[];      // the M rows of x, when they fit (staged != 0)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * WARPS + warp;
-    if (n >= N) return;
-    const float* wr = W + (size_t)n * K;
+    const bool active = n < N;                       // a warp beyond the matrix still helps staging x and meets the barrier
+    const float* wr = W + (size_t)(active ? n : 0) * K;
     constexpr int U = 4;
     float4 w[U];
     auto load_w = [&](int k0) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int k = k0 + u * 128 + lane * 4;
-            w[u] = k < K ? __ldcs(reinterpret_cast<const float4*>(wr + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            w[u] = (k < K && active) ? __ldcs(reinterpret_cast<const float4*>(wr + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     };
     load_w(0);                   // weights do not depend on earlier kernels of the step
     pdl_wait();
     pdl_launch();
+    if (staged) {
+        // every warp of the CTA multiplies with the same rows of x: they come from L2 once, into shared memory
+        for (int i = threadIdx.x * 4; i < M * K; i += WARPS * 32 * 4) {
+            const int m = i / K, k = i % K;
+            *reinterpret_cast<float4*>(xs + i) = __ldcg(reinterpret_cast<const float4*>(x + (size_t)m * ldx + k));
+        }
+        __syncthreads();
+    }
+    if (!active) return;
     float acc[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m] = 0.f;
@@ -51,7 +61,8 @@ linear_smallm_f32_kernel(const float* x, long long ldx, const float* __restrict_
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 if (m < M) {
-                    const float4 xv = __ldcg(reinterpret_cast<const float4*>(x + (size_t)m * ldx + k));
+                    const float4 xv = staged ? *reinterpret_cast<const float4*>(xs + (size_t)m * K + k)
+                                             : __ldcg(reinterpret_cast<const float4*>(x + (size_t)m * ldx + k));
                     acc[m] = fmaf(cur[u].x, xv.x, acc[m]);
                     acc[m] = fmaf(cur[u].y, xv.y, acc[m]);
                     acc[m] = fmaf(cur[u].z, xv.z, acc[m]);
@@ -88,12 +99,23 @@ MLLM_EXPORT int mllm_linear_smallm_f32(const void* x, long long ldx, const void*
     if (K <= 0 || K % 4 != 0 || ldx % 4 != 0 || (uintptr_t)x % 16 != 0 || (uintptr_t)W % 16 != 0)
         return mllm_fail(1, "linear_smallm_f32: K and the row stride must be multiples of 4, operands 16-byte aligned");
     const int grid = (N + WARPS - 1) / WARPS;
+    const size_t want = (size_t)M * K * sizeof(float);
+    const int staged = want <= 96 * 1024;            // else the rows of x are read from L2 as they are needed
+    const size_t smem = staged ? want : 0;
 #define GO(MT)                                                                                                    \
-    MLLM_CUDA(mllm_launch(linear_smallm_f32_kernel<MT>, dim3(grid), dim3(WARPS * 32), 0, stream, true, (const float*)x, \
-                          ldx, (const float*)W, bias, (float*)out, ldo, M, N, K, act, accumulate));               \
-    return 0
-    if (M <= 4) { GO(4); }
-    if (M <= 8) { GO(8); }
-    GO(16);
+    {                                                                                                             \
+        auto kern = linear_smallm_f32_kernel<MT>;                                                                 \
+        static size_t set = 0;                                                                                    \
+        if (smem > 48 * 1024 && smem > set) {                                                                     \
+            MLLM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(96 * 1024))); \
+            set = 96 * 1024;                                                                                      \
+        }                                                                                                         \
+        MLLM_CUDA(mllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, true, (const float*)x, ldx,      \
+                              (const float*)W, bias, (float*)out, ldo, M, N, K, act, accumulate, staged));        \
+        return 0;                                                                                                 \
+    }
+    if (M <= 4) GO(4)
+    if (M <= 8) GO(8)
+    GO(16)
 #undef GO
 }
