@@ -28,6 +28,7 @@
 // results and the order of their merge are the same in every arrangement, so a token's
 // result does not depend on the size of the batch.  Longer contexts use the scratch path.
 #include "common.cuh"
+#include "tcgen05.cuh"
 #include <cooperative_groups.h>
 
 namespace cg = cooperative_groups;
@@ -81,10 +82,13 @@ template <> struct Exp<__nv_bfloat16> {
     }
 };
 
-// Keys and values of a split can be staged in shared memory (cp.async, no registers held while they fly) when a
-// split's rows fit there: bfloat16 with heads up to 64.  That leaves room for six CTAs per SM instead of four,
-// which pays as soon as the grid is larger than four CTAs per SM; smaller grids keep the rows in registers,
-// one hop less on the way.  The arithmetic is the same either way.
+// Keys and values of a split can be staged in shared memory when a split's rows fit there: bfloat16 with heads
+// up to 64.  The rows of one (page, head) are contiguous, so one thread brings each page's visible rows with one
+// bulk copy (cp.async.bulk onto an mbarrier): no thread computes an address per key, no register is held while
+// the rows fly, and six CTAs fit an SM instead of four.  That pays as soon as the grid is larger than about two
+// CTAs per SM; smaller grids keep the rows in registers, one hop less on the way.  The arithmetic is the same
+// either way.
+__device__ int g_decode_error = 0;                   // 1: a staged split never arrived (bounded wait ran out)
 template <typename T, int LPK> struct Staged { static constexpr bool value = sizeof(T) == 2 && LPK * Vec16<T>::N <= 64; };
 
 // ONE: every CTA takes exactly one split.  STG: keys and values go through shared memory.
@@ -115,6 +119,7 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
     float* sm_o = STAGE ? reinterpret_cast<float*>(s_stage) : sm_o_own;   // staged: the groups' outputs reuse the keys' space
     __shared__ float sm_res[(PUSH ? MAX_CLUSTER : MODE == MODE_SCRATCH || ONE ? 1 : MAX_SPC) * RES];
     __shared__ int s_last;
+    __shared__ __align__(8) uint64_t s_bar;                   // STAGE: a split's bulk copies complete here
     const int cx = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
     // Positions, the request index and the block table are written by the host before the step, and the rows of
     // all keys before the token's own position were written by earlier steps: all of that is read before the
@@ -160,6 +165,24 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
     float qv[VEC];                                            // loaded after the wait, in the first split's turn
     bool waited = false;
     const size_t pair = (size_t)t * H + h;
+    uint32_t phase = 0;
+    if constexpr (STAGE) {
+        if (threadIdx.x == 0) {
+            tc::mbar_init(&s_bar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+    }
+    // the wait on the previous kernel, then this thread's part of the query
+    auto wait_and_load_q = [&]() {
+        pdl_wait();
+        waited = true;
+        // (what the previous kernel wrote is read past L1)
+        const uint4 qraw = __ldcg(reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)h * DH + li * VEC));
+        Vec16<T>::unpack(qraw, qv);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) qv[i] *= scale * Exp<T>::QSCALE;
+    };
 
     if constexpr (!ONE) {
         // A CTA that walks several splits asks for the rows of its later splits right away (into L2), one
@@ -184,59 +207,68 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
         float m = -INFINITY, l = 0.f, o[VEC];
 #pragma unroll
         for (int i = 0; i < VEC; ++i) o[i] = 0.f;
+        uint4* sk = s_stage;
+        uint4* sv = s_stage + SPLIT * LPK;
+        if constexpr (STAGE) {
+            // The split's visible rows [v_lo, k_hi), page by page: thread c brings the rows of the c-th page that
+            // the range touches.  Rows of earlier steps go out before the wait on the previous kernel, the
+            // token's own row (position p) after it.  Rows that are not visible are not copied: their places
+            // hold whatever was there, and the arithmetic below skips them.
+            constexpr uint32_t ROW = DH * (uint32_t)sizeof(T);
+            const int v_lo = max(k_lo, first);
+            const int pre_hi = min(k_hi, p);
+            if (threadIdx.x == 0) tc::mbar_expect_tx(&s_bar, (uint32_t)(k_hi - v_lo) * ROW * 2);
+            if (pre_hi > v_lo) {
+                const int pg0 = page_index(v_lo), pg1 = page_index(pre_hi - 1);
+                for (int pg = pg0 + (int)threadIdx.x; pg <= pg1; pg += THREADS) {
+                    const int r0 = max(v_lo, pg * page_size), r1 = min(pre_hi, (pg + 1) * page_size);
+                    const size_t off = (((size_t)__ldcg(bt + pg) * Hkv + hk) * page_size + (r0 - pg * page_size)) * DH;
+                    const uint32_t bytes = (uint32_t)(r1 - r0) * ROW;
+                    tc::bulk_load(sk + (r0 - k_lo) * LPK, k_pages + off, bytes, &s_bar);
+                    tc::bulk_load(sv + (r0 - k_lo) * LPK, v_pages + off, bytes, &s_bar);
+                }
+            }
+            if (!waited) wait_and_load_q();
+            if (threadIdx.x == 0 && p >= v_lo && p < k_hi) {
+                const size_t off = (((size_t)__ldcg(bt + page_index(p)) * Hkv + hk) * page_size + page_offset(p)) * DH;
+                tc::bulk_load(sk + (p - k_lo) * LPK, k_pages + off, ROW, &s_bar);
+                tc::bulk_load(sv + (p - k_lo) * LPK, v_pages + off, ROW, &s_bar);
+            }
+            if (!tc::mbar_wait(&s_bar, phase)) {              // gave up: tell the host, let copies in flight land, go on
+                if (threadIdx.x == 0) atomicCAS(&g_decode_error, 0, 1);
+                for (int i = 0; i < 2000; ++i) __nanosleep(100);
+            }
+            phase ^= 1;
+        }
 #pragma unroll 1
         for (int kb = k_lo + gi; kb < k_lo + SPLIT; kb += NG * UNR) {   // same trip count for every lane
-            int page[UNR];
             bool ok[UNR];
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
                 const int kp = kb + u * NG;
                 ok[u] = kp < k_hi && kp >= first;
-                page[u] = ok[u] ? __ldcg(bt + page_index(kp)) : 0;
             }
             uint4 kr[STAGE ? 1 : UNR], vr[STAGE ? 1 : UNR];
-            uint4* sk = s_stage;
-            uint4* sv = s_stage + SPLIT * LPK;
+            if constexpr (!STAGE) {
+                int page[UNR];
 #pragma unroll
-            for (int pass = 0; pass < 2; ++pass) {            // pass 0: the keys of earlier steps; pass 1, after the wait: the token's own
-            if (pass == 1) {
-                if (!waited) {
-                    pdl_wait();
-                    waited = true;
-                    // (what the previous kernel wrote is read past L1 as well)
-                    const uint4 qraw = __ldcg(reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)h * DH + li * VEC));
-                    Vec16<T>::unpack(qraw, qv);
+                for (int u = 0; u < UNR; ++u) page[u] = ok[u] ? __ldcg(bt + page_index(kb + u * NG)) : 0;
 #pragma unroll
-                    for (int i = 0; i < VEC; ++i) qv[i] *= scale * Exp<T>::QSCALE;
-                }
-            }
+                for (int pass = 0; pass < 2; ++pass) {        // pass 0: the keys of earlier steps; pass 1, after the wait: the token's own
+                    if (pass == 1 && !waited) wait_and_load_q();
 #pragma unroll
-            for (int u = 0; u < UNR; ++u) {
-                const int kp = kb + u * NG;
-                if ((kp == p) != (pass == 1)) continue;
-                size_t off = 0;
-                if (ok[u]) off = (((size_t)page[u] * Hkv + hk) * page_size + page_offset(kp)) * DH + li * VEC;
-                if constexpr (STAGE) {
-                    // 16 bytes of the key row and of the value row to this lane's own places (zeros where the key is not visible)
-                    const int idx = (kp - k_lo) * LPK + li;
-                    const int nbytes = ok[u] ? 16 : 0;
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(sk + idx)),
-                                 "l"(k_pages + off), "r"(nbytes) : "memory");
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(sv + idx)),
-                                 "l"(v_pages + off), "r"(nbytes) : "memory");
-                } else {
-                    kr[u] = make_uint4(0, 0, 0, 0);
-                    vr[u] = make_uint4(0, 0, 0, 0);
-                    if (ok[u]) {
-                        kr[u] = __ldcg(reinterpret_cast<const uint4*>(k_pages + off));
-                        vr[u] = __ldcg(reinterpret_cast<const uint4*>(v_pages + off));
+                    for (int u = 0; u < UNR; ++u) {
+                        const int kp = kb + u * NG;
+                        if ((kp == p) != (pass == 1)) continue;
+                        kr[u] = make_uint4(0, 0, 0, 0);
+                        vr[u] = make_uint4(0, 0, 0, 0);
+                        if (ok[u]) {
+                            const size_t off = (((size_t)page[u] * Hkv + hk) * page_size + page_offset(kp)) * DH + li * VEC;
+                            kr[u] = __ldcg(reinterpret_cast<const uint4*>(k_pages + off));
+                            vr[u] = __ldcg(reinterpret_cast<const uint4*>(v_pages + off));
+                        }
                     }
                 }
-            }
-            }
-            if constexpr (STAGE) {
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                asm volatile("cp.async.wait_group 0;" ::: "memory");      // a lane reads back only what it brought itself
             }
             float s[UNR];
             float mx = m;
@@ -260,6 +292,7 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
                 for (int i = 0; i < VEC; ++i) o[i] *= alpha;
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) {
+                    if (STAGE && !ok[u]) continue;            // nothing was copied to this key's place
                     const float pr = ok[u] ? Exp<T>::of(s[u] - mx) : 0.f;
                     float vv[VEC];
                     if constexpr (STAGE) Vec16<T>::unpack(sv[(kb + u * NG - k_lo) * LPK + li], vv);
@@ -303,7 +336,10 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
             if (MODE == MODE_SCRATCH) { part_ml[slot * 2] = M; part_ml[slot * 2 + 1] = L; }
             else { res[DH] = M; res[DH + 1] = L; }
         }
-        if (split < my_hi) __syncthreads();                   // the group buffers are free for the next split
+        if (split < my_hi) {
+            if constexpr (STAGE) tc::fence_async_smem();      // the next split's copies overwrite what was written here
+            __syncthreads();                                  // the group buffers are free for the next split
+        }
     }
     if (single) return;
 
@@ -426,7 +462,9 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
     using K = void (*)(const T*, long long, const T*, const T*, const int*, int, const int*, const int*, T*, long long,
                        float*, float*, unsigned int*, int, int, int, float, int, int, int);
     constexpr bool CAN_STAGE = Staged<T, LPK>::value;
-    const bool stg = CAN_STAGE && pairs * ctas > 2LL * decode_sm_count();     // measured: from about two CTAs per SM on
+    // measured: from about two CTAs per SM on (bulk copies want 16-byte aligned pools)
+    const bool stg = CAN_STAGE && pairs * ctas > 2LL * decode_sm_count() &&
+                     ((uintptr_t)k_pages | (uintptr_t)v_pages) % 16 == 0;
     const int mode = scratch_path ? MODE_SCRATCH : ctas == 1 ? MODE_LOCAL : ctas <= MAX_CLUSTER ? MODE_CLUSTER : MODE_SCRATCH;
     const bool one = spc == 1 && mode != MODE_LOCAL;
     K kern;
@@ -463,6 +501,14 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
 }  // namespace
 
 MLLM_EXPORT int mllm_attention_decode_split_len() { return SPLIT; }
+
+// The first error recorded by the kernel since the last call (0 = none); resets it.
+MLLM_EXPORT int mllm_attention_decode_error(int* code) {
+    int zero = 0;
+    MLLM_CUDA(cudaMemcpyFromSymbol(code, g_decode_error, sizeof(int)));
+    if (*code) MLLM_CUDA(cudaMemcpyToSymbol(g_decode_error, &zero, sizeof(int)));
+    return 0;
+}
 
 static int attention_decode_impl(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                  const int* block_table, int bt_stride, const int* token_seq, const int* positions,

@@ -66,6 +66,7 @@ def _signatures(lib):
         "mllm_attention_tcgen05": [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
                                    c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mllm_attention_tcgen05_error": [c_void_p],
+        "mllm_attention_decode_error": [c_void_p],
         "mllm_attention_tiled": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                  c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "mllm_argmax": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
@@ -130,6 +131,10 @@ def check_device_errors() -> None:
     if code.value:
         raise KernelError(f"the tcgen05 attention kernel gave up waiting: code {code.value} "
                           "(1 producer, 2-6 MMA issuer, 7-8 softmax warps)")
+    if lib.mllm_attention_decode_error(ctypes.byref(code)) != 0:
+        raise KernelError(lib.mllm_last_error().decode(errors="replace"))
+    if code.value:
+        raise KernelError("the decode attention kernel gave up waiting for a split's keys and values")
 
 
 _stream_handle = None     # set by stream_scope(); None: ask torch on every call
