@@ -59,6 +59,18 @@ template <> struct Vec16<__nv_bfloat16> {
     }
 };
 
+// acc + a.lo * b.lo + a.hi * b.hi for two packed pairs of bfloat16, each step one fused multiply-add whose
+// product is exact and whose sum is rounded once to 32-bit.
+__device__ __forceinline__ float dot2_bf16(uint32_t a, uint32_t b, float acc) {
+    asm("{\n\t.reg .b16 a0, a1, b0, b1;\n\t"
+        "mov.b32 {a0, a1}, %1;\n\t"
+        "mov.b32 {b0, b1}, %2;\n\t"
+        "fma.rn.f32.bf16 %0, a0, b0, %0;\n\t"
+        "fma.rn.f32.bf16 %0, a1, b1, %0;\n\t}"
+        : "+f"(acc) : "r"(a), "r"(b));
+    return acc;
+}
+
 // How the splits of one (token, head) meet.
 enum { MODE_SCRATCH = 0,     // partial results in global scratch; the CTA that arrives last merges them
        MODE_CLUSTER = 1,     // the CTAs of a (token, head) form a cluster and meet in distributed shared memory
@@ -162,6 +174,8 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
     auto page_index = [&](int kp) { return pow2 ? kp >> pshift : kp / page_size; };
     auto page_offset = [&](int kp) { return pow2 ? kp & pmask : kp % page_size; };
 
+    constexpr bool MIXED = STAGE && sizeof(T) == 2;           // scores from the packed query and keys, scaled afterwards
+    uint4 qw = make_uint4(0, 0, 0, 0);
     float qv[VEC];                                            // loaded after the wait, in the first split's turn
     bool waited = false;
     const size_t pair = (size_t)t * H + h;
@@ -179,6 +193,7 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
         waited = true;
         // (what the previous kernel wrote is read past L1)
         const uint4 qraw = __ldcg(reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)h * DH + li * VEC));
+        qw = qraw;
         Vec16<T>::unpack(qraw, qv);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) qv[i] *= scale * Exp<T>::QSCALE;
@@ -274,14 +289,24 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
             float mx = m;
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
-                float kv[VEC];
-                if constexpr (STAGE) Vec16<T>::unpack(sk[(kb + u * NG - k_lo) * LPK + li], kv);
-                else Vec16<T>::unpack(kr[u], kv);
                 float d = 0.f;
+                if constexpr (MIXED) {
+                    // bfloat16 x bfloat16 + 32-bit in one instruction: the products are exact, nothing is unpacked
+                    const uint4 kw = sk[(kb + u * NG - k_lo) * LPK + li];
+                    d = dot2_bf16(qw.x, kw.x, d);
+                    d = dot2_bf16(qw.y, kw.y, d);
+                    d = dot2_bf16(qw.z, kw.z, d);
+                    d = dot2_bf16(qw.w, kw.w, d);
+                } else {
+                    float kv[VEC];
+                    if constexpr (STAGE) Vec16<T>::unpack(sk[(kb + u * NG - k_lo) * LPK + li], kv);
+                    else Vec16<T>::unpack(kr[u], kv);
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) d = fmaf(qv[i], kv[i], d);
+                    for (int i = 0; i < VEC; ++i) d = fmaf(qv[i], kv[i], d);
+                }
 #pragma unroll
                 for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+                if constexpr (MIXED) d *= scale * Exp<T>::QSCALE;
                 s[u] = ok[u] ? d : -INFINITY;
                 mx = fmaxf(mx, s[u]);
             }
@@ -462,9 +487,9 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
     using K = void (*)(const T*, long long, const T*, const T*, const int*, int, const int*, const int*, T*, long long,
                        float*, float*, unsigned int*, int, int, int, float, int, int, int);
     constexpr bool CAN_STAGE = Staged<T, LPK>::value;
-    // measured: from about two CTAs per SM on (bulk copies want 16-byte aligned pools)
-    const bool stg = CAN_STAGE && pairs * ctas > 2LL * decode_sm_count() &&
-                     ((uintptr_t)k_pages | (uintptr_t)v_pages) % 16 == 0;
+    // staged whenever the rows fit (measured: never slower, from two requests on faster); bulk copies want
+    // 16-byte aligned pools
+    const bool stg = CAN_STAGE && ((uintptr_t)k_pages | (uintptr_t)v_pages) % 16 == 0;
     const int mode = scratch_path ? MODE_SCRATCH : ctas == 1 ? MODE_LOCAL : ctas <= MAX_CLUSTER ? MODE_CLUSTER : MODE_SCRATCH;
     const bool one = spc == 1 && mode != MODE_LOCAL;
     K kern;
