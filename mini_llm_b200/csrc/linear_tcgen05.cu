@@ -96,7 +96,23 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();                 // barriers, tensor memory and descriptors are ready; now the operands may be read
+    // The weights are written by no kernel of the step: the W tiles of the first stages are asked for before the
+    // wait on the previous kernel; their A tiles follow after it and complete the same barriers.
+    int pre = 0;                                                 // stages whose W tiles are already on their way
+    if (warp == 0 && lane == 0) {
+        const int my_tiles = (int)blockIdx.x < num_tiles ? (num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+        pre = min(C::STAGES, my_tiles * nk);
+        for (int g = 0; g < pre; ++g) {
+            const int tile = blockIdx.x + (g / nk) * gridDim.x, kt = g % nk;
+            const int n0 = (tile % tiles_n) * BN;
+            uint8_t* a_dst = tiles + (size_t)g * C::STAGE_BYTES;
+            mbar_expect_tx(&full[g], C::STAGE_BYTES);
+#pragma unroll
+            for (int b = 0; b < C::KB; ++b)
+                tma_load_2d(a_dst + b * C::BLOCK_BYTES + C::A_BYTES, &map_w, (kt * C::KB + b) * BK, n0, &full[g]);
+        }
+    }
+    pdl_wait();                 // now what earlier kernels of the step wrote may be read
     pdl_launch();
 
     if (warp == 0) {
@@ -109,11 +125,13 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     if (g >= C::STAGES && !mbar_wait(&empty[s], ((g / C::STAGES) - 1) & 1)) { *failed = 1; break; }
                     if (*failed) break;
                     uint8_t* a_dst = tiles + (size_t)s * C::STAGE_BYTES;
-                    mbar_expect_tx(&full[s], C::STAGE_BYTES);
+                    const bool w_sent = g < pre;
+                    if (!w_sent) mbar_expect_tx(&full[s], C::STAGE_BYTES);
 #pragma unroll
                     for (int b = 0; b < C::KB; ++b) {
                         tma_load_2d(a_dst + b * C::BLOCK_BYTES, &map_a, (kt * C::KB + b) * BK, m0, &full[s]);
-                        tma_load_2d(a_dst + b * C::BLOCK_BYTES + C::A_BYTES, &map_w, (kt * C::KB + b) * BK, n0, &full[s]);
+                        if (!w_sent)
+                            tma_load_2d(a_dst + b * C::BLOCK_BYTES + C::A_BYTES, &map_w, (kt * C::KB + b) * BK, n0, &full[s]);
                     }
                 }
             }

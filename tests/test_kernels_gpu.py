@@ -350,7 +350,8 @@ def _ctx_for(case):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,Hkv,dh,page,window", [(4, 4, 16, 16, None), (3, 3, 32, 8, None), (12, 12, 64, 16, None),
-                                                  (6, 2, 64, 4, None), (2, 2, 128, 32, 300), (4, 1, 64, 16, 37)])
+                                                  (6, 2, 64, 4, None), (2, 2, 128, 32, 300), (4, 1, 64, 16, 37),
+                                                  (2, 1, 64, 24, 70), (2, 2, 32, 1, None)])
 def test_decode_attention_split_keys(ops, dtype, H, Hkv, dh, page, window):
     """Single tokens at contexts around the split (128) and page edges, beside the plain kernel."""
     seqs = [(c, 1) for c in (1, 2, 16, 17, 127, 128, 129, 255, 256, 257, 513, 700, 1024)]
