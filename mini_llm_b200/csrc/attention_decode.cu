@@ -4,11 +4,13 @@
 //
 // Grid (split, head, token).  A split is a fixed range of 128 key positions counted
 // from position 0, so which keys are added together never depends on the batch.
-// Inside a CTA (4 warps) a group of LPK lanes owns one key at a time: each lane loads
+// Inside a CTA (4 warps) a group of LPK lanes owns one key at a time: each lane takes
 // 16 bytes of the key row and of the value row (the cache layout keeps one
-// (page, head, slot) row contiguous).  A group first fetches the page ids of all its
-// keys, then issues all its key and value loads at once (up to 8 keys in flight per
-// group), and only then starts computing: three dependent memory round trips per CTA
+// (page, head, slot) row contiguous).  With a bfloat16 cache and heads up to 64 a
+// split's rows are first brought into shared memory by bulk copies, one per page (see
+// Staged below); otherwise a group fetches the page ids of all its keys, then issues
+// all its key and value loads at once (up to 8 keys in flight per group), and only
+// then starts computing.  Either way it is three dependent memory round trips per CTA
 // instead of two per key.  The group reduces each dot product with shuffles and keeps its
 // own online-softmax state (m, l, o) in 32-bit (src/kernels/prefill/flashattention.cu:
 // 129-168 gives the recurrence); groups are merged in group order through shared memory
