@@ -252,7 +252,7 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
                 tc::bulk_load(sv + (p - k_lo) * LPK, v_pages + off, ROW, &s_bar);
             }
             if (!tc::mbar_wait(&s_bar, phase)) {              // gave up: tell the host, let copies in flight land, go on
-                if (threadIdx.x == 0) atomicCAS(&g_decode_error, 0, 1);
+                if (threadIdx.x == 0) { atomicCAS(&g_decode_error, 0, 1); tc::report_to_host(301); }
                 for (int i = 0; i < 2000; ++i) __nanosleep(100);
             }
             phase ^= 1;
@@ -528,6 +528,9 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
 }  // namespace
 
 MLLM_EXPORT int mllm_attention_decode_split_len() { return SPLIT; }
+
+// The pinned host word that this file's kernels write when they give up on a wait.
+MLLM_EXPORT int mllm_attention_decode_bind_error(int* word) { return tc::bind_host_error(word); }
 
 // The first error recorded by the kernel since the last call (0 = none); resets it.
 MLLM_EXPORT int mllm_attention_decode_error(int* code) {

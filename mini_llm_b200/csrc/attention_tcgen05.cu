@@ -347,7 +347,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     tc_fence_before();
     __syncthreads();
     if (*failed) {
-        if (threadIdx.x == 0) atomicCAS(&g_attn_error, 0, *failed);
+        if (threadIdx.x == 0) { atomicCAS(&g_attn_error, 0, *failed); report_to_host(200 + *failed); }
         for (int i = 0; i < 2000; ++i) __nanosleep(100);          // copies already issued may still be landing
         __syncthreads();
     }
@@ -360,6 +360,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 }  // namespace
 
 MLLM_EXPORT int mllm_attention_tcgen05_tile() { return BQ; }
+
+// The pinned host word that this file's kernels write when they give up on a wait.
+MLLM_EXPORT int mllm_attention_tcgen05_bind_error(int* word) { return bind_host_error(word); }
 
 // The first error recorded by the kernel since the last call (0 = none); resets it.
 MLLM_EXPORT int mllm_attention_tcgen05_error(int* code) {

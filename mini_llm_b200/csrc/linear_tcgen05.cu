@@ -394,7 +394,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     tc_fence_before();
     __syncthreads();
     if (*failed) {
-        if (threadIdx.x == 0) atomicCAS(&g_tc_error, 0, *failed);
+        if (threadIdx.x == 0) { atomicCAS(&g_tc_error, 0, *failed); report_to_host(100 + *failed); }
         // copies already issued may still be writing this CTA's shared memory: let them land
         for (int i = 0; i < 2000; ++i) __nanosleep(100);
         __syncthreads();
@@ -482,6 +482,21 @@ int pick_bn(const void* A, long long lda, const void* W, const float* bias, void
 }
 
 }  // namespace
+
+// The pinned host word that this file's kernels write when they give up on a wait.
+MLLM_EXPORT int mllm_tcgen05_bind_error(int* word) { return bind_host_error(word); }
+
+namespace {
+__global__ void report_error_kernel(int code) { report_to_host(code); }
+}  // namespace
+
+// Writes `code` to the host word from the device, the way a kernel that gave up would: lets a test check
+// that the host notices, without making any wait run out.
+MLLM_EXPORT int mllm_debug_report_error(int code, cudaStream_t stream) {
+    report_error_kernel<<<1, 1, 0, stream>>>(code);
+    MLLM_CHECK_LAUNCH("report_error_kernel");
+    return 0;
+}
 
 // The first error recorded by a tcgen05 kernel since the last call (0 = none); resets it.
 MLLM_EXPORT int mllm_tcgen05_error(int* code) {

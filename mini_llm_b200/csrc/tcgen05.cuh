@@ -10,6 +10,22 @@ namespace tc {
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;     // two seconds, then a wait gives up
 
+// A word in pinned host memory that a kernel writes when it gives up on a bounded wait, so that the host can
+// notice without a copy (it reads the word wherever it has waited for the stream anyway).  Every translation
+// unit has its own pointer to the same word; bind_host_error() sets it.
+static __device__ int* g_host_error = nullptr;
+__device__ __forceinline__ void report_to_host(int code) {
+    int* p = g_host_error;
+    if (p) {
+        *reinterpret_cast<volatile int*>(p) = code;
+        __threadfence_system();
+    }
+}
+inline int bind_host_error(int* word) {
+    cudaError_t e = cudaMemcpyToSymbol(g_host_error, &word, sizeof(word));
+    return e == cudaSuccess ? 0 : mllm_fail(3, "binding the host error word failed: %s", cudaGetErrorString(e));
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

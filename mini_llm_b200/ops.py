@@ -58,6 +58,10 @@ def _signatures(lib):
         "mllm_linear_tcgen05_qkv": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_void_p,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_tcgen05_error": [c_void_p],
+        "mllm_tcgen05_bind_error": [c_void_p],
+        "mllm_attention_tcgen05_bind_error": [c_void_p],
+        "mllm_attention_decode_bind_error": [c_void_p],
+        "mllm_debug_report_error": [c_int, c_void_p],
         "mllm_attention_decode": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                   c_int, c_int, c_int, c_int, c_void_p],
@@ -90,7 +94,39 @@ def library():
             raise KernelError(f"cannot load the kernel library {path}: {e}") from e
         _signatures(lib)
         _lib = lib
+        _bind_error_word(lib)
     return _lib
+
+
+_error_word = None      # one int32 in pinned host memory: kernels that give up on a bounded wait write it
+
+
+def _bind_error_word(lib) -> None:
+    """Give the kernels that have bounded waits the address of a pinned host word (a no-op
+    without a CUDA device: the library can be built and loaded on a machine that has none)."""
+    global _error_word
+    if _error_word is not None or not torch.cuda.is_available():
+        return
+    word = torch.zeros(1, dtype=torch.int32).pin_memory()
+    for name in ("mllm_tcgen05_bind_error", "mllm_attention_tcgen05_bind_error", "mllm_attention_decode_bind_error"):
+        if getattr(lib, name)(word.data_ptr()) != 0:
+            raise KernelError(lib.mllm_last_error().decode(errors="replace"))
+    _error_word = word
+
+
+_WHO = {1: "the tcgen05 product", 2: "the tcgen05 attention", 3: "the decode attention"}
+
+
+def raise_if_kernel_gave_up() -> None:
+    """Costs one read of host memory: call it wherever the host has just waited for the
+    stream (after tokens or logits were fetched).  Raises once per event."""
+    if _error_word is None:
+        return
+    code = int(_error_word[0])
+    if code:
+        _error_word[0] = 0
+        raise KernelError(f"{_WHO.get(code // 100, 'a kernel')} gave up on a bounded wait (code {code % 100}): "
+                          "the results of the step are not valid")
 
 
 def set_pdl(on: bool) -> None:
@@ -116,10 +152,13 @@ def _call(name: str, *args) -> None:
 
 
 def check_device_errors() -> None:
-    """Raise if a tensor-core kernel gave up on a bounded wait since the last check.
-    Reads one device word (a synchronising copy): call it where the host waits anyway."""
+    """Raise if a kernel gave up on a bounded wait since the last check.  Synchronises and reads
+    the kernels' own device words (the thorough check of tests and tools; the engine uses
+    raise_if_kernel_gave_up, which costs nothing)."""
     code = c_int(0)
     lib = library()
+    torch.cuda.synchronize()
+    raise_if_kernel_gave_up()
     if lib.mllm_tcgen05_error(ctypes.byref(code)) != 0:
         raise KernelError(lib.mllm_last_error().decode(errors="replace"))
     if code.value:

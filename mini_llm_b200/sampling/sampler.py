@@ -66,6 +66,7 @@ class Sampler:
     def fetch(self, ticket: Tuple[int, int]) -> List[int]:
         i, R = ticket
         self._events[i].synchronize()
+        ops.raise_if_kernel_gave_up()       # the host has waited for the step: a kernel that gave up has said so by now
         return self.host_out[i][:R].tolist()
 
     def sample(self, logits: torch.Tensor, requests: Sequence) -> List[int]:

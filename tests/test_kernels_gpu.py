@@ -701,3 +701,21 @@ def test_argmax_and_sampling(ops, R, V):
     ops.sample(row, torch.ones(4000, device=DEV), u, o)
     freq = torch.bincount(o.cpu().long(), minlength=5).double() / 4000
     assert (freq - torch.softmax(row[0].double().cpu(), 0)).abs().max() < 0.03
+
+
+def test_a_kernel_that_gives_up_is_noticed_by_the_host(ops):
+    """Kernels with bounded waits write a pinned host word when a wait runs out; the host reads it for free
+    wherever it has waited for the stream.  Here a one-thread kernel writes the word the same way (no wait
+    is made to run out)."""
+    ops.library()
+    torch.cuda.synchronize()
+    ops.raise_if_kernel_gave_up()            # nothing so far
+    ops._call("mllm_debug_report_error", 203, ops._stream())
+    torch.cuda.synchronize()
+    with pytest.raises(ops.KernelError, match="tcgen05 attention.*code 3"):
+        ops.raise_if_kernel_gave_up()
+    ops.raise_if_kernel_gave_up()            # reported once
+    ops._call("mllm_debug_report_error", 301, ops._stream())
+    with pytest.raises(ops.KernelError, match="decode attention"):
+        ops.check_device_errors()            # the thorough check synchronises by itself
+    ops.check_device_errors()
