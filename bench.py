@@ -1,30 +1,47 @@
 """Decode and prefill throughput of the engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--dtype float32|bfloat16]
 
 A "step" is one decode step: every live request gets one more token.  The default
 run is GPT-2 small (n_layer 12, n_embd 768, n_head 12, n_inner 3072, vocab 50257,
-n_positions 1024) with seeded random weights in bfloat16, a batch of 8 requests with
-512-token random prompts, page size 16.  It prints ONE JSON line:
+n_positions 1024) with seeded random weights, a batch of 8 requests with 512-token
+random prompts, page size 16.  The headline numbers are those of the float32 path (true
+32-bit: the reference's only precision, so the two arms compare like with like); the
+bfloat16 path of the same model is measured in the same run and reported under ``points``
+with ``bf16_`` in every key.  ``--dtype bfloat16`` swaps the two.  It prints ONE JSON line:
 
   value       decoded tokens per second over exactly K steps, timed on the device
               with CUDA events (forward pass + on-device argmax per step).  The default
               K = 512 is the benchmark's whole generation: contexts grow from 512 to
-              1,023.  The warm-up is the same generation by other requests (max(W, K)
-              steps), so the timed steps replay captured graphs; a K beyond the 512
-              positions a request has left is cut to 512;
+              1,023.  The warm-up is the same generation by other requests, max(W, K)
+              steps and never fewer than 3 (``warmup`` in the line is that number, which
+              can exceed the W asked for), so the timed steps replay captured graphs; a K
+              beyond the 512 positions a request has left is cut to 512;
   e2e         the same through the Python entry point (LLM.step): host token ids in,
               sampled ids back on the host every step;
-  prefill     2,048 prompt tokens (2 x 1024) in one step: tokens/s, ms, and the share
-              of the bf16 tensor peak its flops reach;
+  prefill     2,048 prompt tokens (2 x 1024) in one step: tokens/s, ms, and the share of
+              the peak for its dtype that its flops reach (bfloat16: the measured cuBLAS
+              rate; float32: the CUDA cores' nominal FFMA rate, SMs x 128 x 2 x clock);
   roofline    bytes the decode step has to read (every weight once + the cache of the
               live requests) / its time, against the HBM copy bandwidth;
-  points      decode tokens/s at batch 1 and 64.
+  points      decode tokens/s at batch 1 and 64 with their share of the HBM rate, the
+              entry point's tokens/s at batch 1, and the other precision's decode at batch
+              1 / 8 / 64, entry-point and prefill figures.
 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from the
 fallback figures 6.65 TB/s and 1.59 PFLOP/s ("peaks": "fallback").
-The reference arm (taejuk/mini-llm itself) is not installable with pip: it is a CMake
-C++/CUDA project without Python packaging, so ``--impl reference`` reports unavailable.
+
+``--impl reference`` runs taejuk/mini-llm itself: its unmodified sources from baseline/_ref,
+compiled with nvcc for sm_100a together with baseline/reference_arm.cu (a main() that calls its
+GPT2Model::prefill / decode only), on the same weights and prompts, and prints the same line
+with "impl": "reference" and "dtype": "fp32".  The reference holds at most 16 requests and
+4096 cache blocks per process, so a batch of 8 can decode 159 steps after 512-token prompts
+(more are cut) and there is no batch-64 point.  Where it cannot be built or run the line is
+{"impl": "reference", "unavailable": "<why>"}.
+
+``--profile-step prefill|decode [--kernel-times]`` runs one small eager step (for a profiler, or to
+print each kernel's share of the step from CUDA events); ``--workload medium|xl`` runs the
+continuous-batching workloads of the larger GPT-2 sizes.
 """
 from __future__ import annotations
 
@@ -153,8 +170,7 @@ def run_decode(model_dir, dtype, batch, steps, warmup, sample_clocks=False):
     eng = EngineConfig(dtype=dtype, page_size=PAGE, max_tokens=batch * cfg["n_positions"], max_num_seqs=max(batch, 1),
                        max_num_batched_tokens=max(2048, batch))
     runner = ModelRunner(model_dir, eng)
-    g = torch.Generator().manual_seed(1234)
-    prompts = torch.randint(0, cfg["vocab_size"], (batch, PROMPT_LEN), generator=g).tolist()
+    prompts = bench_prompts(cfg["vocab_size"], batch)
     out = torch.empty(batch, dtype=torch.int32, device=runner.device)
     toks = [int(p[-1]) for p in prompts]
 
@@ -212,8 +228,7 @@ def run_e2e(model_dir, dtype, batch, steps, warmup):
     # all prompts go in with one step, so that the requests decode side by side from the first timed step to the last
     llm = m.LLM(model_dir, dtype=dtype, page_size=PAGE, max_tokens=batch * cfg["n_positions"], max_num_seqs=batch,
                 max_num_batched_tokens=batch * PROMPT_LEN, prefill_chunk=PROMPT_LEN)
-    g = torch.Generator().manual_seed(1234)
-    prompts = torch.randint(0, cfg["vocab_size"], (batch, PROMPT_LEN), generator=g).tolist()
+    prompts = bench_prompts(cfg["vocab_size"], batch)
     sp = m.SamplingParams(max_new_tokens=steps + 1, ignore_eos=True)     # one token from the prompt's step, K decoded
 
     def prompts_in():
@@ -279,10 +294,13 @@ def run_prefill(model_dir, dtype, iters=5, warmup=3):
     return dict(ms=ms, tok_s=PREFILL_TOKENS / (ms / 1e3), flops=fl)
 
 
-def profile_step(kind: str, dtype: str, layers: int, batch: int) -> int:
+def profile_step(kind: str, dtype: str, layers: int, batch: int, kernel_times: bool = False) -> int:
     """One eager prefill step (2 x 1024 tokens) or a few eager decode steps at GPT-2 small's
     layer sizes with ``layers`` layers: a small, bounded workload to put under ncu, e.g.
-    ncu --set full --clock-control none -k regex:attention_flash -c 1 python bench.py --profile-step prefill --layers 2"""
+    ncu --set full --clock-control none -k regex:attention_flash -c 1 python bench.py --profile-step prefill --layers 2
+    With ``kernel_times`` the last step's launches are timed one by one with CUDA events and the line carries,
+    per entry point of the kernel library, its launches, microseconds and share of the step (eager launches,
+    so the gaps between kernels are larger than in the replayed graphs that generation uses)."""
     import torch
     import mini_llm_b200 as m
     from mini_llm_b200 import ops
@@ -290,6 +308,7 @@ def profile_step(kind: str, dtype: str, layers: int, batch: int) -> int:
     from mini_llm_b200.engine.runner import ModelRunner, StepEntry
 
     cfg = dict(SMALL, n_layer=layers)
+    times = None
     with tempfile.TemporaryDirectory(prefix="mini_llm_prof_") as d:
         m.write_random_model(cfg, 0, d, dtype=dtype)
         n = cfg["n_positions"]
@@ -299,17 +318,40 @@ def profile_step(kind: str, dtype: str, layers: int, batch: int) -> int:
         g = torch.Generator().manual_seed(7)
         plen = n if kind == "prefill" else PROMPT_LEN
         prompts = torch.randint(0, cfg["vocab_size"], (B, plen), generator=g).tolist()
-        for i in range(B):
-            runner.add_request(i)
-        for lo in range(0, B, 2):
-            runner.step([StepEntry(i, prompts[i], [plen - 1]) for i in range(lo, min(B, lo + 2))])
+        out = torch.empty(B, dtype=torch.int32, device=runner.device)
+
+        def prompts_in():
+            for i in range(B):
+                runner.add_request(i)
+            for lo in range(0, B, 2):
+                ops.argmax(runner.step([StepEntry(i, prompts[i], [plen - 1]) for i in range(lo, min(B, lo + 2))]),
+                           out[lo:min(B, lo + 2)])
+
+        def decode_once():
+            ops.argmax(runner.step([StepEntry(i, [11], [0]) for i in range(B)]), out)
+
+        prompts_in()
         if kind == "decode":
-            out = torch.empty(B, dtype=torch.int32, device=runner.device)
             for _ in range(3):
-                ops.argmax(runner.step([StepEntry(i, [11], [0]) for i in range(B)]), out)
+                decode_once()
+        if kernel_times:
+            if kind == "prefill":
+                for i in range(B):
+                    runner.finish_request(i)
+            torch.cuda.synchronize()
+            with ops.time_launches() as tl:
+                prompts_in() if kind == "prefill" else decode_once()
+            rows = tl.rows()
+            total = sum(ms for _, _, ms in rows) or 1.0
+            times = {name.replace("mllm_", ""): {"launches": k, "us": round(ms * 1e3, 1), "share": round(ms / total, 3)}
+                     for name, k, ms in rows}
         torch.cuda.synchronize()
         ops.check_device_errors()
-    print(json.dumps({"profile_step": kind, "layers": layers, "batch": B, "dtype": dtype, "launches": ops.launches}))
+    line = {"profile_step": kind, "layers": layers, "batch": B, "dtype": dtype, "launches": ops.launches}
+    if times is not None:
+        line["kernel_times"] = times
+        line["kernel_us_total"] = round(sum(v["us"] for v in times.values()), 1)
+    print(json.dumps(line))
     return 0
 
 
@@ -365,18 +407,143 @@ def run_workload(kind: str, dtype: str, layers: int) -> int:
     return 0
 
 
+def fp32_peak_flops() -> float:
+    """CUDA-core peak of the float32 path (no tensor-core mode exists for true 32-bit products):
+    SMs x 128 lanes x 2 flops x the highest SM clock; nominal, nothing measures it on this pool."""
+    import torch
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    mhz = 1965.0
+    try:
+        mhz = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("sm_max_mhz") or mhz)
+    except Exception:
+        pass
+    return sms * 128 * 2 * mhz * 1e6
+
+
+def bench_prompts(vocab: int, batch: int, n: int = PROMPT_LEN):
+    """The prompts of the decode benchmark: the same ids for this engine and for the reference arm."""
+    import torch
+    g = torch.Generator().manual_seed(1234)
+    return torch.randint(0, vocab, (batch, n), generator=g).tolist()
+
+
+def base_config(cfg, batch, mean_ctx, pk):
+    return {"model": "gpt2-small", "n_layer": cfg["n_layer"], "n_layer_full": SMALL["n_layer"],
+            "n_embd": cfg["n_embd"], "n_head": cfg["n_head"], "n_inner": cfg["n_inner"],
+            "vocab_size": cfg["vocab_size"], "n_positions": cfg["n_positions"], "global_batch": batch,
+            "prompt_len": PROMPT_LEN, "seq_len": cfg["n_positions"], "page_size": PAGE,
+            "mean_context": mean_ctx, "parallelism": "single GPU",
+            "l2": "inputs exceed L2 (weights + cache > 126 MB)", "peaks": pk["source"],
+            "baseline": "854.41 tok/s, FP32, batch 8, on a TITAN V: other hardware (gpt2_decode_batch_sweep_512.csv:5)"}
+
+
+def run_reference(args) -> int:
+    """The reference arm: taejuk/mini-llm itself, unmodified, built from baseline/_ref and driven through its own
+    GPT2Model::prefill / decode on the same seeded weights and prompts (float32, its only precision).  Its limits
+    (batch <= 16, a pool of 4096 blocks of 16 tokens per layer, include/constants.h:16-26) cap the steps a batch of
+    8 can run after 512-token prompts at 159; more are cut and ``config`` says so."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ra
+
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": str(why).replace("\n", " ")[:400]}))
+        return 0
+
+    if args.gpus != 1:
+        return unavailable("the reference runs on one GPU only")
+    import torch
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device: the reference has no CPU path")
+    if args.layers != SMALL["n_layer"] or args.batch > ra.MAX_BATCH:
+        return unavailable("the reference is compiled for GPT-2 small with 12 layers and at most 16 requests")
+    try:
+        if not ra.have_sources() and os.path.isdir("/root/reference/src"):
+            ra.fetch_sources("/root/reference")
+        exe = ra.build()
+    except ra.ReferenceUnavailable as e:
+        return unavailable(e)
+    import mini_llm_b200 as m
+    pk = peaks()
+    cfg = dict(SMALL)
+    warmup = max(args.warmup, 3)
+    most = ra.most_decode_steps(args.batch, PROMPT_LEN)
+    steps = max(1, min(decode_steps(cfg, args.steps), most))
+    warmup = min(warmup, most)
+    try:
+        with tempfile.TemporaryDirectory(prefix="mini_llm_ref_") as d:
+            m.write_random_model(cfg, 0, os.path.join(d, "model"), dtype="float32")
+            ra.prepare_weights(os.path.join(d, "model"), d)
+            ra.write_prompts(os.path.join(d, "p8.txt"), bench_prompts(cfg["vocab_size"], args.batch))
+            ra.write_prompts(os.path.join(d, "p1.txt"), bench_prompts(cfg["vocab_size"], 1))
+            import torch
+            g = torch.Generator().manual_seed(99)
+            n = cfg["n_positions"]
+            ra.write_prompts(os.path.join(d, "pf.txt"),
+                             [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for _ in range(PREFILL_TOKENS // n)])
+            clocks = ClockSampler()
+            clocks.start()
+            dec = ra.run(exe, d, ["decode", "p8.txt", str(steps), str(warmup)])
+            clk = clocks.stop()
+            b1 = ra.run(exe, d, ["decode", "p1.txt", str(steps), str(warmup)]) if not args.no_points else None
+            pf = ra.run(exe, d, ["prefill", "pf.txt", "5", "3"]) if not args.no_points else None
+    except (ra.ReferenceUnavailable, subprocess.TimeoutExpired, ValueError) as e:
+        return unavailable(e)
+    B = args.batch
+    ms = dec["device_ms_per_step"]
+    mean_ctx = dec["first_context"] + (steps + 1) / 2.0
+    # what the reference's step has to read: its float32 weights once (wte through the transposed copy its head
+    # uses, and the rows of wte/wpe the embedding gathers) and the float32 cache of the live requests
+    D, L, F, V = cfg["n_embd"], cfg["n_layer"], cfg["n_inner"], cfg["vocab_size"]
+    wbytes = 4.0 * (V * D + L * (3 * D * D + D * D + 2 * D * F + 9 * D + F) + 2 * D + 2 * B * D)
+    nbytes = wbytes + B * mean_ctx * L * 2 * D * 4.0
+    achieved = nbytes / (ms / 1e3) / 1e9
+    blocks = sum(-(-(PROMPT_LEN + steps + 1) // ra.KV_BLOCK) for _ in range(B))
+    # host -> device per step (src/model/gpt2_model.cu:474-475, 521-533, 569-588): ids and positions, then per layer
+    # two slot words per request, the flat block table, offsets and lengths; device -> host: the sampled ids (:670-675)
+    h2d = 4 * (2 * B + L * (4 * B + blocks))
+    conf = base_config(cfg, B, round(mean_ctx, 1), pk)
+    line = {
+        "impl": "reference",
+        "note": f"the reference's pool (4096 blocks) and batch limit (16) allow {most} decode steps at batch {B}; no batch 64",
+        "metric": "decode tok/s at batch 8 (GPT-2 small, 512-token prompts, greedy)",
+        "value": round(B * 1e3 / ms, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(B * 1e3 / ms / 854.41, 2) if B == 8 else None,
+        "dtype": "fp32", "data": "synthetic (seeded random weights and token ids)", "config": conf,
+        "e2e": {"value": round(B * 1e3 / dec["wall_ms_per_step"], 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": steps * (L * 7 + 4),
+        "clocks": clk,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+    if pf is not None:
+        fl = prefill_flops(cfg, [cfg["n_positions"]] * (PREFILL_TOKENS // cfg["n_positions"]), PREFILL_TOKENS // cfg["n_positions"])
+        line["prefill"] = {"value": round(PREFILL_TOKENS / (pf["median_ms"] / 1e3), 1), "tokens": PREFILL_TOKENS,
+                           "ms": round(pf["median_ms"], 3),
+                           "frac": round(fl / (pf["median_ms"] / 1e3) / fp32_peak_flops(), 4)}
+    if b1 is not None:
+        line["points"] = {"decode_b1": round(1e3 / b1["device_ms_per_step"], 1), "decode_b64": None,
+                          "e2e_decode_b1": round(1e3 / b1["wall_ms_per_step"], 1)}
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--dtype", default="float32", choices=["bfloat16", "float32"],
+                    help="precision of the headline numbers; the other precision goes into 'points'")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=SMALL["n_layer"], help="fewer layers than GPT-2 small's 12, if needed")
-    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64, prefill and other-precision measurements")
     ap.add_argument("--profile-step", choices=["prefill", "decode"],
                     help="run one small eager step for a profiler instead of the benchmark")
+    ap.add_argument("--kernel-times", action="store_true",
+                    help="with --profile-step: time every launch of one eager step with CUDA events and print the shares")
     ap.add_argument("--attention", choices=["auto", "mma_sync"], default="auto",
                     help="mma_sync: prompt portions stay on the mma.sync attention kernel (to compare or profile it)")
     ap.add_argument("--workload", choices=["medium", "xl"],
@@ -386,14 +553,11 @@ def main() -> int:
         from mini_llm_b200 import ops
         ops.use_tcgen05_attention = False
     if args.profile_step:
-        return profile_step(args.profile_step, args.dtype, args.layers, args.batch)
+        return profile_step(args.profile_step, args.dtype, args.layers, args.batch, args.kernel_times)
     if args.workload:
         return run_workload(args.workload, args.dtype, args.layers if args.layers != SMALL["n_layer"] else 0)
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "taejuk/mini-llm is a CMake C++/CUDA project with no setup.py or pyproject.toml: "
-                          "pip install --no-index of its source tree fails, so it cannot be installed offline"}))
-        return 0
+        return run_reference(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
@@ -404,32 +568,47 @@ def main() -> int:
 
     pk = peaks()
     cfg = dict(SMALL, n_layer=args.layers)
+    other = "bfloat16" if args.dtype == "float32" else "float32"
+    short = {"bfloat16": "bf16", "float32": "fp32"}
+
+    def prefill_entry(d, dtype):
+        pf = run_prefill(d, dtype)
+        peak_fl = pk["bf16_tflops"] * 1e12 if dtype == "bfloat16" else fp32_peak_flops()
+        return {"value": round(pf["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(pf["ms"], 3),
+                "frac": round(pf["flops"] / (pf["ms"] / 1e3) / peak_fl, 4)}
+
+    points, prefill = {}, None
     with tempfile.TemporaryDirectory(prefix="mini_llm_bench_") as d:
         m.write_random_model(cfg, 0, d, dtype=args.dtype)
         main_run = run_decode(d, args.dtype, args.batch, args.steps, args.warmup, sample_clocks=True)
         e2e = run_e2e(d, args.dtype, args.batch, args.steps, args.warmup)
-        points, prefill = {}, None
         if not args.no_points:
             for b in (1, 64):
-                points[f"decode_b{b}"] = round(run_decode(d, args.dtype, b, args.steps, args.warmup)["tok_s"], 1)
-            pf = run_prefill(d, args.dtype)
-            peak_fl = pk["bf16_tflops"] * 1e12 if args.dtype == "bfloat16" else None
-            prefill = {"value": round(pf["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(pf["ms"], 3),
-                       "frac": round(pf["flops"] / (pf["ms"] / 1e3) / peak_fl, 4) if peak_fl else None}
+                r = run_decode(d, args.dtype, b, args.steps, args.warmup)
+                points[f"decode_b{b}"] = round(r["tok_s"], 1)
+                points[f"decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+            points["e2e_decode_b1"] = round(run_e2e(d, args.dtype, 1, args.steps, args.warmup)["tok_s"], 1)
+            prefill = prefill_entry(d, args.dtype)
+    if not args.no_points:
+        # the other precision of the same model: every figure carries its dtype in its name
+        o = short[other]
+        with tempfile.TemporaryDirectory(prefix="mini_llm_bench_") as d:
+            m.write_random_model(cfg, 0, d, dtype=other)
+            for b in (1, args.batch, 64):
+                r = run_decode(d, other, b, args.steps, args.warmup)
+                points[f"{o}_decode_b{b}"] = round(r["tok_s"], 1)
+                points[f"{o}_decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+            points[f"{o}_e2e_decode_b{args.batch}"] = round(run_e2e(d, other, args.batch, args.steps, args.warmup)["tok_s"], 1)
+            pe = prefill_entry(d, other)
+            points[f"{o}_prefill_tok_s"], points[f"{o}_prefill_ms"], points[f"{o}_prefill_frac"] = pe["value"], pe["ms"], pe["frac"]
     achieved = main_run["bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9
     line = {
         "metric": "decode tok/s at batch 8 (GPT-2 small, 512-token prompts, greedy)",
         "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": main_run["steps"],
         "warmup": main_run["warmup"], "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": round(main_run["tok_s"] / 854.41, 2) if args.batch == 8 else None,
-        "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic (seeded random weights and token ids)",
-        "config": {"model": "gpt2-small", "n_layer": cfg["n_layer"], "n_layer_full": SMALL["n_layer"],
-                   "n_embd": cfg["n_embd"], "n_head": cfg["n_head"], "n_inner": cfg["n_inner"],
-                   "vocab_size": cfg["vocab_size"], "n_positions": cfg["n_positions"], "global_batch": args.batch,
-                   "prompt_len": PROMPT_LEN, "seq_len": cfg["n_positions"], "page_size": PAGE,
-                   "mean_context": round(main_run["mean_ctx"], 1), "parallelism": "single GPU",
-                   "l2": "inputs exceed L2 (weights + cache > 126 MB)", "peaks": pk["source"],
-                   "baseline": "854.41 tok/s FP32 on TITAN V (gpt2_decode_batch_sweep_512.csv:5)"},
+        "dtype": short[args.dtype], "data": "synthetic (seeded random weights and token ids)",
+        "config": base_config(cfg, args.batch, round(main_run["mean_ctx"], 1), pk),
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d"],
                 "d2h_bytes_per_step": e2e["d2h"]},
         "gpu_launches": main_run["launches"],

@@ -540,14 +540,43 @@ MLLM_EXPORT int mllm_attention_decode_error(int* code) {
     return 0;
 }
 
+// Everything a raw C caller can get wrong is refused here, on the host, before any launch and before any
+// CUDA call: a bad size would index outside the pools on the device, a misaligned pool would fault in the
+// 16-byte loads.  Returns 0 when the arguments can be launched.
+static int attention_decode_check(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                  const int* block_table, int bt_stride, const int* token_seq, const int* positions,
+                                  const void* out, int T, int H, int Hkv, int dh, int page_size, int window,
+                                  int max_splits, int dtype) {
+    if (T <= 0) return 0;
+    if (!q || !k_pages || !v_pages || !block_table || !token_seq || !positions || !out)
+        return mllm_fail(1, "attention_decode: null pointer among the inputs or the output");
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0)
+        return mllm_fail(1, "attention_decode: %d heads over %d key/value heads", H, Hkv);
+    if (page_size <= 0) return mllm_fail(1, "attention_decode: page size %d", page_size);
+    if (window < 0) return mllm_fail(1, "attention_decode: window %d (0 means all keys)", window);
+    if (bt_stride <= 0) return mllm_fail(1, "attention_decode: block table row stride %d", bt_stride);
+    if (max_splits <= 0 || T > 65535 || H > 65535) return mllm_fail(1, "attention_decode: grid out of range");
+    if (dtype != MLLM_BF16 && dtype != MLLM_F32) return mllm_fail(1, "attention_decode: unknown dtype code %d", dtype);
+    if (dh < 16 || dh > (dtype == MLLM_BF16 ? 256 : 128) || (dh & (dh - 1)))
+        return mllm_fail(1, "attention_decode: head size %d is not one of this kernel's", dh);
+    if (((uintptr_t)k_pages | (uintptr_t)v_pages) % 16)
+        return mllm_fail(1, "attention_decode: the key and value pools must be 16-byte aligned");
+    if (q_stride % (dtype == MLLM_BF16 ? 8 : 4) || (uintptr_t)q % 16)
+        return mllm_fail(1, "attention_decode: queries must be 16-byte aligned");
+    return 0;
+}
+
 static int attention_decode_impl(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                  const int* block_table, int bt_stride, const int* token_seq, const int* positions,
                                  void* out, long long out_stride, float* part_o, float* part_ml,
                                  unsigned int* counters, int T, int H, int Hkv, int dh, int page_size, float scale,
                                  int window, int max_splits, int dtype, bool scratch_path, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (Hkv <= 0 || H % Hkv != 0) return mllm_fail(1, "attention_decode: %d heads over %d key/value heads", H, Hkv);
-    if (max_splits <= 0 || T > 65535 || H > 65535) return mllm_fail(1, "attention_decode: grid out of range");
+    if (int rc = attention_decode_check(q, q_stride, k_pages, v_pages, block_table, bt_stride, token_seq, positions, out,
+                                        T, H, Hkv, dh, page_size, window, max_splits, dtype))
+        return rc;
+    if ((scratch_path || max_splits > 8) && (!part_o || !part_ml || !counters))
+        return mllm_fail(1, "attention_decode: %d splits need the scratch buffers", max_splits);
 #define GO(TT, LPK)                                                                                            \
     return launch<TT, LPK>(q, q_stride, k_pages, v_pages, block_table, bt_stride, token_seq, positions, out,    \
                            out_stride, part_o, part_ml, counters, T, H, Hkv, page_size, scale, window,          \
@@ -579,8 +608,10 @@ static int attention_decode_impl(const void* q, long long q_stride, const void* 
 
 // Scratch (used when max_splits > 8 or scratch_only != 0): part_o [T*H*max_splits*dh] and
 // part_ml [T*H*max_splits*2] floats and counters [T*H] 32-bit words that must be zero before
-// the first call (the kernel leaves them zero), where max_splits >= ceil((largest position
-// + 1) / 128).  With up to 8 splits the splits meet in a thread-block cluster instead and the
+// the first call (the kernel leaves them zero).  The caller guarantees max_splits >=
+// ceil((largest position + 1) / 128): a token whose keys need more splits than that gets no
+// output written (positions live on the device, so the host cannot check this).  Sizes, null
+// pointers and alignments are checked on the host and refused with code 1 before any launch.  With up to 8 splits the splits meet in a thread-block cluster instead and the
 // scratch is not touched.  Fails for head sizes this kernel does not take (the caller then
 // uses the general kernel).
 MLLM_EXPORT int mllm_attention_decode(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
@@ -649,6 +680,9 @@ MLLM_EXPORT int mllm_attention_decode_noalloc(const void* q, long long q_stride,
                          T, H, max_splits, slots, MLLM_NOALLOC_MAX_SLOTS);
     if (dh > MLLM_NOALLOC_MAX_HEAD_DIM)
         return mllm_fail(1, "attention_decode_noalloc: head size %d exceeds %d", dh, MLLM_NOALLOC_MAX_HEAD_DIM);
+    if (int rc = attention_decode_check(q, q_stride, k_pages, v_pages, block_table, bt_stride, token_seq, positions, out,
+                                        T, H, Hkv, dh, page_size, window, max_splits, dtype))
+        return rc;
     unsigned char* base = nullptr;
     const int rc = noalloc_scratch(&base);
     if (rc) return rc;

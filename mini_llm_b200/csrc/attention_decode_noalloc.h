@@ -33,8 +33,12 @@
 //   q [T, H*dh] (row stride q_stride elements), k_pages/v_pages [pages, Hkv, page_size, dh],
 //   block_table [requests, bt_stride] int32, token_seq/positions [T] int32 (the request of
 //   every token and its absolute position), out [T, H*dh] (row stride out_stride),
-//   scale, window (0 = all keys), max_splits >= ceil((largest position + 1) / 128),
-//   dtype 0 = float32, 1 = bfloat16, stream.
+//   scale, window (0 = all keys), max_splits, dtype 0 = float32, 1 = bfloat16, stream.
+// The caller guarantees max_splits >= ceil((largest position + 1) / 128): the positions are
+// on the device, so this cannot be checked here, and a token that needs more splits gets no
+// output written.  Everything the host can check is checked before anything is launched:
+// null pointers, heads, page size > 0, window >= 0, block table stride > 0, and that q (with
+// its row stride) and the two pools are 16-byte aligned.
 // Returns 0, or a non-zero code with the reason in mllm_last_error().
 #pragma once
 #include <cuda_runtime.h>

@@ -142,13 +142,48 @@ def is_loaded() -> bool:
 launches = 0       # kernels launched through this module (bench.py reports the count)
 
 
+_timeline = None    # a list while time_launches() is active: (entry point, start event, end event) per launch
+
+
 def _call(name: str, *args) -> None:
     global launches
     lib = library()
     launches += 1
-    rc = getattr(lib, name)(*args)
+    if _timeline is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = getattr(lib, name)(*args)
+        e1.record()
+        _timeline.append((name, e0, e1))
+    else:
+        rc = getattr(lib, name)(*args)
     if rc != 0:
         raise KernelError(f"{name}: {lib.mllm_last_error().decode(errors='replace')}")
+
+
+class time_launches:
+    """Times every launch made inside the scope with a pair of CUDA events (eager launches only: nothing can be
+    recorded inside a graph capture).  ``rows()`` afterwards gives (entry point, launches, total ms) per entry
+    point in order of first use: the per-kernel share of a step, in the manner of the reference's stage timer
+    (include/profiling/stage_timer.cuh:40-101), without a device synchronisation per stage."""
+
+    def __enter__(self):
+        global _timeline
+        self._old, _timeline = _timeline, []
+        self._mine = _timeline
+        return self
+
+    def __exit__(self, *a):
+        global _timeline
+        _timeline = self._old
+
+    def rows(self):
+        torch.cuda.synchronize()
+        agg = {}
+        for name, e0, e1 in self._mine:
+            n, ms = agg.get(name, (0, 0.0))
+            agg[name] = (n + 1, ms + e0.elapsed_time(e1))
+        return [(k, n, ms) for k, (n, ms) in agg.items()]
 
 
 def check_device_errors() -> None:

@@ -1,6 +1,7 @@
 """bench.py's answers that need no GPU: more than one GPU is refused with one line and exit
-code 2, the reference arm says why it is unavailable, and the helpers that turn a run into
-bytes and flops count what they say."""
+code 2, the reference arm answers with one line of its own where it cannot run, and the helpers
+that turn a run into bytes and flops count what they say.  (That the reference arm runs where it
+can is the GPU box's business: tests/test_reference_anchor_gpu.py builds and runs the reference.)"""
 import json
 import os
 import subprocess
@@ -21,11 +22,27 @@ def test_more_than_one_gpu_is_refused_with_one_line():
     assert len(lines) == 1 and "one GPU" in lines[0]
 
 
-def test_reference_arm_reports_unavailable():
+def test_reference_arm_answers_with_one_line():
+    import torch
+    if torch.cuda.is_available():
+        import pytest
+        pytest.skip("with a GPU the arm runs the reference: covered by the GPU tests")
     p = _run("--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3")
     assert p.returncode == 0
-    line = json.loads(p.stdout.strip().splitlines()[-1])
-    assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
+    lines = [ln for ln in p.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and "no CUDA device" in line["unavailable"]
+
+
+def test_reference_limits_are_the_ones_of_its_constants():
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ra
+    # 4096 blocks / 12 layers / 8 requests = 42 blocks = 672 tokens: 512 prompt + 1 + 159 steps
+    assert ra.most_decode_steps(8, 512) == 159
+    assert ra.most_decode_steps(1, 512) == 1024 - 512 - 1
+    assert ra.most_decode_steps(16, 512) == 0
+    assert ra.blocks_needed([512] * 8, 21) == 8 * 34 * 12
 
 
 def test_decode_steps_leave_room_for_the_prompt():
