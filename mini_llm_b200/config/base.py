@@ -51,6 +51,7 @@ class EngineConfig:
     admission: str = "lazy"            # "lazy" | "reserve"
     memory_fraction: float = 0.5       # of free device memory, when sizes are not given
     use_cuda_graphs: bool = True
+    graph_capture: str = "on_return"   # "on_return": a step shape is captured when it comes back; "at_once": at first sight
     use_pdl: bool = True               # programmatic dependent launch between the kernels of a step
     async_scheduling: bool = True      # while only decodes run, launch a step before the last one's tokens are read
     device: str = "cuda:0"
@@ -70,6 +71,8 @@ class EngineConfig:
             raise ConfigError("max_num_batched_tokens must be positive")
         if self.prefill_chunk <= 0:
             raise ConfigError("prefill_chunk must be positive")
+        if self.graph_capture not in ("on_return", "at_once"):
+            raise ConfigError(f"graph_capture must be 'on_return' or 'at_once', got {self.graph_capture!r}")
         if self.admission not in ("lazy", "reserve"):
             raise ConfigError(f"admission must be 'lazy' or 'reserve', got {self.admission!r}")
 

@@ -18,7 +18,7 @@ import torch
 
 from .. import ops
 from ..cache.manager import CacheManager
-from ..config.base import EngineConfig, ModelConfig, get_architecture, load_config
+from ..config.base import ConfigError, EngineConfig, ModelConfig, get_architecture, load_config
 from ..parts.model import Model
 from ..weights.loader import load_weights
 from .context import ATTN_TILE_WIDE, StepContext, StepLayout, Workspace, attention_tiles, pack_step
@@ -59,18 +59,22 @@ def _element_size(dtype: torch.dtype) -> int:
 class ModelRunner:
     def __init__(self, model_dir: str, engine: Optional[EngineConfig] = None):
         self.engine = engine or EngineConfig()
+        self.config: ModelConfig = load_config(model_dir)
+        arch = get_architecture(self.config.architecture)
+        self.spec = arch.build_spec(self.config)
+        self.model = Model(self.spec)
+        # sizes no kernel takes are refused here, before a device is touched, a weight loaded or a pool allocated
+        problems = list(dict.fromkeys(m.split(": ", 1)[1] for m in self.model.kernel_limits(self.engine.dtype)))
+        if problems:
+            raise ConfigError(f"{model_dir}: this model cannot run on the kernel library: " + "; ".join(problems))
         if not torch.cuda.is_available():
             raise StepError("no CUDA device: this engine has no CPU path")
         self.device = torch.device(self.engine.device)
         torch.cuda.set_device(self.device)
         ops.library()       # build/load now: fail early and loudly
         ops.set_pdl(self.engine.use_pdl)
-        self.config: ModelConfig = load_config(model_dir)
-        arch = get_architecture(self.config.architecture)
-        self.spec = arch.build_spec(self.config)
         self.rt = Runtime(dtype=torch.bfloat16 if self.engine.dtype == "bfloat16" else torch.float32,
                           device=self.device)
-        self.model = Model(self.spec)
         load_weights(self.model, self.spec, model_dir, self.rt)
         self.vocab_size = self.spec.vocab_size
         self.max_positions = self.spec.max_positions
@@ -93,6 +97,10 @@ class ModelRunner:
         # a part that reads device data on the host while it runs sets graph_safe = False
         self._graph_ok = all(getattr(self.model.part(label), "graph_safe", True)
                              for label, _ in self.spec.all_part_specs())
+        self._capture_at_once = self.engine.graph_capture == "at_once"
+        if self._capture_at_once and self.cache.state_layers:
+            raise StepError("graph_capture='at_once' runs a new step shape twice; a mixer with a state of its own "
+                            "would advance it twice")
 
     # ------------------------------------------------------------------ set-up
     def _make_cache(self) -> None:
@@ -304,7 +312,12 @@ class ModelRunner:
         family = key[0][:3] + key[0][4:]
         if seen == 0 and family not in self._graph_families:
             with ops.stream_scope():
-                return self.model.forward(ctx)         # first time: eager, buffers get allocated
+                logits = self.model.forward(ctx)       # first time: eager, buffers get allocated
+            if not self._capture_at_once:
+                return logits
+            # "at_once": the same step again, captured and replayed, so that even a shape that never comes back
+            # is computed by a replayed graph (what the replay tests grade); a step only writes its own tokens'
+            # cache slots and scratch, so running it twice changes nothing
         version = self.ws.version
         torch.cuda.current_stream().synchronize()
         graph = torch.cuda.CUDAGraph()

@@ -19,6 +19,7 @@ F32, BF16 = 0, 1
 SMALL_M = 64                 # rows up to which the weight-streaming product is used
 SMALL_M_F32 = 16             # the same for the float32 weight-streaming product
 DECODE_SPLIT = 128           # keys per split of the decode attention (csrc/attention_decode.cu)
+DECODE_CLUSTER_SPLITS = 8    # splits that can meet in one thread-block cluster (MAX_CLUSTER there)
 _FLASH_HEAD_DIMS = (16, 32, 64, 128)
 _DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16, 32, 64, 128)}
 _ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}
@@ -589,12 +590,18 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
                               f"for {q.dtype}, not {head_dim}")
         # splits cover the longest context of the step, rounded up so that captured graphs keep their grid
         max_splits = decode_splits(ctx.max_ctx_len)
-        part_o = ctx.ws.buf("attn_part_o", T * num_heads * max_splits, head_dim, torch.float32)
-        part_ml = ctx.ws.buf("attn_part_ml", T * num_heads * max_splits, 2, torch.float32)
-        counters = ctx.ws.zeroed("attn_counters", T * num_heads)     # the kernel leaves them zero
+        # Up to DECODE_CLUSTER_SPLITS splits meet in a thread-block cluster and touch no scratch; only beyond that
+        # (contexts over 1,024 tokens) or on request do the partial results go through global memory.  Asking for
+        # the buffers only then keeps a growing context from ever replacing a buffer under the captured graphs.
+        if impl == "decode_scratch" or max_splits > DECODE_CLUSTER_SPLITS:
+            part_o = ctx.ws.buf("attn_part_o", T * num_heads * max_splits, head_dim, torch.float32).data_ptr()
+            part_ml = ctx.ws.buf("attn_part_ml", T * num_heads * max_splits, 2, torch.float32).data_ptr()
+            counters = ctx.ws.zeroed("attn_counters", T * num_heads).data_ptr()     # the kernel leaves them zero
+        else:
+            part_o = part_ml = counters = None
         _call("mllm_attention_decode", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(),
               block_table.data_ptr(), bt_stride, ctx.token_seq.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(),
-              ldo, part_o.data_ptr(), part_ml.data_ptr(), counters.data_ptr(), T, num_heads, num_kv_heads, head_dim, ps, float(scale),
+              ldo, part_o, part_ml, counters, T, num_heads, num_kv_heads, head_dim, ps, float(scale),
               int(window or 0), max_splits, _dt(q), int(impl == "decode_scratch"), _stream())
         return
     if impl != "simt":

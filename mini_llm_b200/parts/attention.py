@@ -50,6 +50,14 @@ class Attention(Mixer):
             p["out_bias"] = ParamSpec((self.hidden_size,), "vector")
         return p
 
+    def kernel_limits(self, dtype: str):
+        # every attention kernel of the library works on head sizes that are multiples of 16 from 16 to 256
+        # (16-byte pieces of a key row per lane; mma tiles of 16): anything else has no kernel
+        if self.head_dim % 16 != 0 or not (16 <= self.head_dim <= 256):
+            return [f"attention: head size {self.head_dim} (hidden size {self.hidden_size} over {self.num_heads} heads) "
+                    f"is not a multiple of 16 between 16 and 256, the sizes the attention kernels take"]
+        return []
+
     def cache_need(self):
         return PagedNeed(kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window)
 

@@ -43,6 +43,12 @@ class Part:
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {}
 
+    def kernel_limits(self, dtype: str):
+        """Sizes of this part that no kernel of the library takes, as a list of sentences (empty: all
+        fine).  Asked once, before any weight is loaded, so that a model that cannot run is refused at
+        construction and not at its first step.  ``dtype``: "bfloat16" or "float32"."""
+        return []
+
     def bind(self, params: Dict[str, Any], rt) -> None:
         """Take the loaded parameters (device tensors) and the runtime."""
         self.rt = rt

@@ -55,6 +55,16 @@ class Model:
             l.mixer.set_positions(self.positions)
         self.rt = None
 
+    def kernel_limits(self, dtype: str) -> List[str]:
+        """What the parts report as sizes no kernel takes, each prefixed with the part's label."""
+        out: List[str] = []
+        for label, _ in self.spec.all_part_specs():
+            part = self.part(label)
+            check = getattr(part, "kernel_limits", None)
+            for msg in (check(dtype) if check is not None else []):
+                out.append(f"{label}: {msg}")
+        return out
+
     # -- parts by the labels ModelSpec.all_part_specs() uses
     def part(self, label: str):
         if label.startswith("layers."):

@@ -92,12 +92,15 @@ class Replay:
     """Drives bin/trace_run as a child process, one step at a time."""
 
     def __init__(self, model_dir: str, dtype: str, out_dir: str, max_tokens: int, page_size: Optional[int] = None,
-                 extra: Sequence[str] = ()):
+                 extra: Sequence[str] = (), graphs: Optional[str] = None):
         self.out_dir = out_dir
+        self.stats_path = os.path.join(out_dir, "stats.json")
         cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
-               "--max-tokens", str(max_tokens)]
+               "--max-tokens", str(max_tokens), "--stats", self.stats_path]
         if page_size is not None:
             cmd += ["--page-size", str(page_size)]
+        if graphs is not None:                      # "on" (the default, as generation runs), "off", "every-step"
+            cmd += ["--cuda-graphs", graphs]
         cmd += list(extra)
         self.p = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
         self.n = 0
@@ -124,6 +127,10 @@ class Replay:
     def close(self) -> int:
         self.p.stdin.close()
         rc = self.p.wait(timeout=120)
+        self.stats = {}
+        if rc == 0 and os.path.isfile(self.stats_path):
+            with open(self.stats_path) as f:
+                self.stats = json.load(f)
         return rc
 
 

@@ -165,6 +165,16 @@ def forward_logits(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int], st
     return lm_head(x, w, cfg, store)
 
 
+def logits_at(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int], rows: Sequence[int], store=_keep) -> torch.Tensor:
+    """Logits at the chosen positions of one whole sequence, [len(rows), vocab]: the blocks run over the
+    whole sequence, the final norm and the head only on the chosen rows, as the reference does it for
+    the last row of a prompt (src/model/gpt2_model.cu:408-428).  For wide vocabularies."""
+    x = embed(ids, w["wte.weight"], w["wpe.weight"])
+    for l in range(int(cfg["n_layer"])):
+        x = block(x, w, l, cfg, store)
+    return lm_head(x[torch.as_tensor(list(rows), dtype=torch.long)], w, cfg, store)
+
+
 def hidden_states(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int]) -> List[torch.Tensor]:
     """The residual stream after the embedding and after every block."""
     x = embed(ids, w["wte.weight"], w["wpe.weight"])

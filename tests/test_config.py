@@ -81,3 +81,24 @@ def test_engine_config_checks():
     for bad in (dict(dtype="fp8"), dict(page_size=0), dict(admission="greedy"), dict(max_num_seqs=0)):
         with pytest.raises(ConfigError):
             EngineConfig(**bad)
+
+
+def test_a_head_size_without_a_kernel_is_refused_at_construction(tmp_path):
+    """n_embd=100 over 5 heads is a valid GPT-2 configuration but gives heads of 20, which no attention kernel
+    takes: the runner refuses it when it is built (before weights, pool or device), naming the limit once."""
+    import json
+    import pytest
+    from mini_llm_b200.config.base import ConfigError, EngineConfig
+    from mini_llm_b200.engine.runner import ModelRunner
+
+    cfg = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=2, n_embd=100, n_head=5, vocab_size=50,
+               n_positions=32)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))          # no weights: it must not get that far
+    with pytest.raises(ConfigError) as e:
+        ModelRunner(str(tmp_path), EngineConfig(dtype="float32"))
+    assert "head size 20" in str(e.value) and str(e.value).count("head size 20") == 1
+    # the parts are asked: heads of 48 (a multiple of 16) pass this check
+    from mini_llm_b200.config.base import config_from_dict, get_architecture
+    from mini_llm_b200.parts.model import Model
+    ok = config_from_dict(dict(cfg, n_embd=96, n_head=2))
+    assert Model(get_architecture(ok.architecture).build_spec(ok)).kernel_limits("bfloat16") == []

@@ -26,37 +26,35 @@ def setup(request, tmp_path_factory):
     return dict(which=which, dtype=dtype, dir=d, cfg=cfg, w=w, page=PAGE_SIZE[which])
 
 
-def plain_generate(cfg, w, prompt, n_new, store, temperature=0.0, seed=0, rid=0):
-    """Greedy or temperature continuation with the margins of every choice."""
+COUNTS = {"float32": [0, 0], "bfloat16": [0, 0]}        # dtype -> [tokens where a near-tie was forgiven, tokens compared]
+
+
+def follow(cfg, w, prompt, got, store, limit, what, dtype, temperature=0.0, seed=0, rid=0):
+    """Every generated token against the plain implementation run on the engine's own prefix: token i must be
+    the plain choice after prompt + got[:i].  A difference is accepted only where the plain choice itself hung on
+    less than ``limit`` (greedy: the gap between the two logits; sampling: the distance of the uniform draw from
+    the edge of the cumulative distribution between the two tokens); such forgiven tokens are counted, and the
+    last test of this file bounds their share.  Following the engine's prefix means that a forgiven near-tie does
+    not leave the rest of the sequence unchecked."""
     from mini_llm_b200.sampling.params import uniform_for
-    ids, out, margins = list(prompt), [], []
-    for i in range(n_new):
-        if len(ids) > cfg["n_positions"]:
-            break
+    ids = list(prompt)
+    for i, tok in enumerate(got):
+        assert len(ids) <= cfg["n_positions"], f"{what}: token {i} lies beyond the last position"
         row = plain_gpt2.forward_logits(cfg, w, ids, store)[-1]
         if temperature == 0:
-            tok = plain_gpt2.greedy_token(row)
-            top2 = torch.topk(row, 2).values
-            margins.append(float(top2[0] - top2[1]))
+            best = plain_gpt2.greedy_token(row)
+            margin = float(row[best] - row[tok])
         else:
             u = uniform_for(seed, rid, i)
-            tok = plain_gpt2.temperature_token(row, temperature, u)
-            p = torch.softmax(row / temperature, 0)
-            c = torch.cumsum(p, 0)
-            margins.append(float(torch.min(torch.abs(c - u))))
-        out.append(tok)
+            best = plain_gpt2.temperature_token(row, temperature, u)
+            c = torch.cumsum(torch.softmax(row.double() / temperature, 0), 0)
+            lo, hi = min(best, tok), max(best, tok)
+            margin = float(torch.min(torch.abs(c[lo:hi] - u))) if lo != hi else 0.0
+        COUNTS[dtype][1] += 1
+        if tok != best:
+            assert margin < limit, f"{what}: token {i} is {tok}, the plain implementation says {best} (margin {margin:.3g})"
+            COUNTS[dtype][0] += 1
         ids.append(tok)
-    return out, margins
-
-
-def check_tokens(got, want, margins, limit, what):
-    """Equal tokens; a difference is only accepted where the oracle's own choice hung on
-    less than ``limit`` (then the rest of the sequence is not comparable)."""
-    for i, (g, w_) in enumerate(zip(got, want)):
-        if g != w_:
-            assert margins[i] < limit, f"{what}: token {i} is {g}, expected {w_} (margin {margins[i]:.3g})"
-            return
-    assert len(got) == len(want), f"{what}: {len(got)} tokens, expected {len(want)}"
 
 
 def test_greedy_generation(setup):
@@ -68,8 +66,8 @@ def test_greedy_generation(setup):
     outs = llm.generate(prompts, m.SamplingParams(max_new_tokens=16, ignore_eos=True))
     limit = 1e-3 if dtype == "float32" else 0.15
     for p, o in zip(prompts, outs):
-        want, margins = plain_generate(cfg, w, p, 16, oracle_store(dtype))
-        check_tokens(o, want, margins, limit, f"greedy prompt of {len(p)}")
+        assert len(o) == 16
+        follow(cfg, w, p, o, oracle_store(dtype), limit, f"greedy prompt of {len(p)}", dtype)
     assert llm.runner.cache.num_live == 0
     llm.runner.cache.check()
 
@@ -88,8 +86,9 @@ def test_temperature_sampling_follows_the_seeded_draws(setup):
             outs[r.request_id].append(r.token)
     limit = 1e-5 if dtype == "float32" else 2e-2
     for p, i in zip(prompts, ids):
-        want, margins = plain_generate(cfg, w, p, 12, oracle_store(dtype), temperature=0.8, seed=1234, rid=i)
-        check_tokens(outs[i], want, margins, limit, f"temperature prompt of {len(p)}")
+        assert len(outs[i]) == 12
+        follow(cfg, w, p, outs[i], oracle_store(dtype), limit, f"temperature prompt of {len(p)}", dtype,
+               temperature=0.8, seed=1234, rid=i)
     # the draw does not depend on the batch: the same request alone gives the same tokens
     llm2 = m.LLM(setup["dir"], dtype=dtype, page_size=setup["page"], max_tokens=512, max_num_seqs=2)
     rid = llm2.add_request(prompts[1], m.SamplingParams(temperature=0.8, seed=1234, max_new_tokens=12, ignore_eos=True),
@@ -110,8 +109,7 @@ def test_long_decoding_to_the_end_of_the_context(setup):
     prompt = random_ids(3, cfg["vocab_size"], 5)
     out = llm.generate([prompt], m.SamplingParams(max_new_tokens=10 * P, ignore_eos=True))[0]
     assert len(out) == P - 3 + 1                      # every position fed once, one token more
-    want, margins = plain_generate(cfg, w, prompt, len(out), oracle_store(dtype))
-    check_tokens(out, want, margins, 1e-3 if dtype == "float32" else 0.15, "long decode")
+    follow(cfg, w, prompt, out, oracle_store(dtype), 1e-3 if dtype == "float32" else 0.15, "long decode", dtype)
 
 
 def test_small_pool_defers_and_preempts_but_tokens_stay_the_same(setup):
@@ -218,3 +216,15 @@ def test_command_line(setup, tmp_path):
     want = llm.generate([p1, p2], m.SamplingParams(max_new_tokens=5, ignore_eos=True))
     got = [[int(t) for t in l[:-len(" [DONE]")].split()] for l in lines]
     assert got == want
+
+
+def test_few_near_ties_had_to_be_forgiven():
+    """The tests above accept a token that differs from the plain choice only where that choice was a near-tie.
+    All generated tokens were compared (each on the engine's own prefix); here the share of forgiven ones is
+    bounded, so that the comparison cannot quietly turn into no comparison: at most one in a hundred in
+    float32, one in ten in bfloat16."""
+    if COUNTS["float32"][1] == 0 and COUNTS["bfloat16"][1] == 0:
+        pytest.skip("the generation tests of this file did not run in this process")
+    for dtype, (forgiven, compared) in COUNTS.items():
+        if compared:
+            assert forgiven <= compared // (100 if dtype == "float32" else 10), f"{dtype}: {forgiven} of {compared} tokens forgiven"

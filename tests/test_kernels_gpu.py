@@ -312,6 +312,23 @@ def _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages, seed, sharp_key=None):
         positions += list(range(ctx - ql, ctx))
     T = len(token_seq)
     q = torch.randn(T, H * dh, generator=g)
+    if sharp_key:
+        # {sequence: [positions]}: every query of that sequence gets a common component that only the keys at
+        # these positions answer (score about 36 at head size 64, against +-3 for the random keys), and each of
+        # those keys has a value row of its own (2, 4, 6 ...), so that the result moves by O(1) when one of them
+        # is dropped, or admitted where a window or the causal mask excludes it
+        for s, where in sharp_key.items():
+            u = torch.randn(Hkv, dh, generator=g)
+            u = u / u.norm(dim=1, keepdim=True) * math.sqrt(dh)          # |u|^2 = dh for every head
+            rows = [t for t, ts in enumerate(token_seq) if ts == s]
+            uq = u.repeat_interleave(H // Hkv, dim=0).reshape(1, H * dh)
+            q[rows] = q[rows] * 0.3 + uq * 1.5
+            K, V = dense[s]
+            for i, p in enumerate(where):
+                K[p] = u * (24.0 / math.sqrt(dh))                        # (q.k)*dh^-0.5 = 1.5 * 24 = 36
+                V[p] = 2.0 * (i + 1)
+                k_pages[tables[s][p // page], :, p % page] = K[p]
+                v_pages[tables[s][p // page], :, p % page] = V[p]
     mp = max(len(t) for t in tables)
     bt = torch.zeros(len(seqs), mp, dtype=torch.int32)
     for s, t in enumerate(tables):
@@ -625,6 +642,53 @@ def test_prompt_attention_finds_one_far_key_among_hundreds(ops, impl, dtype):
                             ctx, out, num_heads=H, num_kv_heads=H, head_dim=dh, scale=dh ** -0.5, impl=impl)
         assert (out.double().cpu() - want).abs().max() < (2e-5 * 8 if dtype == torch.float32 else 3e-2), (impl, far)
         assert out.float().mean().item() > 6.0, (impl, far)
+    ops.check_device_errors()
+
+
+@pytest.mark.parametrize("window", [None, 200])
+@pytest.mark.parametrize("impl,dtype", [("simt", torch.float32), ("decode", torch.float32), ("decode", torch.bfloat16),
+                                        ("tiled", torch.float32), ("tiled", torch.bfloat16), ("flash", torch.bfloat16),
+                                        ("flash_tc", torch.bfloat16)])
+def test_attention_edges_with_sharp_keys(ops, impl, dtype, window):
+    """Keys that carry the weight sit exactly where an off-by-one would drop or admit them: position 0, the
+    first and last key of a page and of a 128-key block, the query's own position, and with a window its first
+    key (p - window + 1, seen) and the key just outside it (p - window, not seen).  Every such key has a value row
+    of its own, so one wrong decision moves the result by O(1), far above any rounding."""
+    from mini_llm_b200.engine.context import ATTN_TILE_WIDE, attention_tiles
+    H, Hkv, dh, page, ctx_len = 4, 2, 64, 16, 700
+    ql = 1 if impl in ("decode", "simt") else 150
+    last = ctx_len - 1
+    for trial in range(3):
+        if window is None:
+            where = [[0, 15, 16, last], [127, 128, last - 1], [383, 384, 640, 0]][trial]
+        else:
+            # for the last query: its window's first key and the one before it; for earlier queries of a portion
+            # the same pair moves with them, so keys all along the edge are placed
+            where = [[last - window + 1, last - window, last], [last - window, 511, 512],
+                     [last - ql + 1 - window + 1, last - ql + 1 - window, 639, 640]][trial]
+            where = [p for p in where if p >= 0]
+        case = _paged_case(dtype, [(40, 1 if ql == 1 else 7), (ctx_len, ql)], H, Hkv, dh, page, num_pages=64,
+                           seed=trial, sharp_key={1: where})
+        ctx = _ctx_for(case)
+        ctx.decode_only = ql == 1
+        qls, starts = [1 if ql == 1 else 7, ql], [40 - (1 if ql == 1 else 7), ctx_len - ql]
+        t64 = attention_tiles(qls, starts)
+        t128 = attention_tiles(qls, starts, ATTN_TILE_WIDE)
+        ctx.attn_tiles, ctx.n_tiles = torch.tensor(t64, dtype=torch.int32, device=DEV), len(t64) // 3
+        ctx.attn_tiles_wide, ctx.n_tiles_wide = torch.tensor(t128, dtype=torch.int32, device=DEV), len(t128) // 3
+        q = case["q"].to(dtype).to(DEV)
+        want = _attention_reference(case, H, Hkv, dh, dh ** -0.5, window, dtype)
+        out = torch.empty_like(q)
+        ops.paged_attention(q, case["k_pages"].to(dtype).to(DEV), case["v_pages"].to(dtype).to(DEV), case["bt"].to(DEV),
+                            ctx, out, num_heads=H, num_kv_heads=Hkv, head_dim=dh, scale=dh ** -0.5, window=window,
+                            impl=impl)
+        err = ((out.double().cpu() - want).abs() / want.abs().clamp(min=1.0)).max()
+        assert err < (2e-4 if dtype == torch.float32 else 1e-2), (impl, window, trial, float(err))
+        # the test has teeth: dropping the first sharp key from the reference moves it by far more than that
+        K, V = case["dense"][1]
+        V[where[0]] += 5.0
+        moved = (_attention_reference(case, H, Hkv, dh, dh ** -0.5, window, dtype) - want).abs().max()
+        assert moved > 0.5 or (window is not None and where[0] == last - window), (trial, float(moved))
     ops.check_device_errors()
 
 

@@ -1,6 +1,12 @@
 """Trace replay against the plain implementation: the same requests whole, with
 the last 32 tokens one by one, in portions of changing size, and mixed with other
-requests in a pool so small that pages are used again; 32-bit and bfloat16."""
+requests in a pool so small that pages are used again; 32-bit and bfloat16.
+
+Every shape runs twice: with launches as generation makes them ("on": a step shape that
+comes back is captured as a CUDA graph and replayed, so the one-by-one steps are replays and
+first sightings run launch by launch) and with every step computed by a replayed graph
+("every-step": captured at first sight), so that the logits of the launch mode that serving
+uses are graded too, with programmatic dependent launch on in both."""
 import os
 
 import numpy as np
@@ -34,18 +40,25 @@ def setup(request, tmp_path_factory):
     return dict(which=which, dtype=dtype, dir=d, cfg=cfg, reqs=reqs, page=PAGE_SIZE[which])
 
 
-def test_whole(setup, tmp_path):
+GRAPHS = pytest.mark.parametrize("graphs", ["on", "every-step"])
+
+
+@GRAPHS
+def test_whole(setup, tmp_path, graphs):
     """Each request alone, whole, all logits wanted."""
-    rp = Replay(setup["dir"], setup["dtype"], str(tmp_path), round64(256), setup["page"])
+    rp = Replay(setup["dir"], setup["dtype"], str(tmp_path), round64(256), setup["page"], graphs=graphs)
     for rid, (ids, want) in setup["reqs"].items():
         got = rp.step([(rid, ids, range(len(ids)))], end=[rid])
         assert_close(got, want, setup["dtype"], f"whole {rid}")
     assert rp.close() == 0
+    if graphs == "every-step":
+        assert rp.stats["graph_replays"] == rp.stats["steps"] > 0
 
 
-def test_last_32_one_by_one(setup, tmp_path):
+@GRAPHS
+def test_last_32_one_by_one(setup, tmp_path, graphs):
     """Most of the request in one step, the last 32 tokens (or all but one) one by one."""
-    rp = Replay(setup["dir"], setup["dtype"], str(tmp_path), round64(256), setup["page"])
+    rp = Replay(setup["dir"], setup["dtype"], str(tmp_path), round64(256), setup["page"], graphs=graphs)
     for rid, (ids, want) in setup["reqs"].items():
         n = len(ids)
         head = max(1, n - 32) if n > 1 else 1
@@ -55,12 +68,15 @@ def test_last_32_one_by_one(setup, tmp_path):
         rp.step([], end=[rid])
         assert_close(np.concatenate(got), want[head - 1:], setup["dtype"], f"decode {rid}")
     assert rp.close() == 0
+    # the single-token steps have the same shape again and again: most of them must have been replayed graphs
+    assert rp.stats["graph_replays"] >= (rp.stats["steps"] if graphs == "every-step" else rp.stats["steps"] // 2)
 
 
-def test_portions_of_changing_size(setup, tmp_path):
+@GRAPHS
+def test_portions_of_changing_size(setup, tmp_path, graphs):
     """Prompts cut into portions of 7, 13, 2, 5, 3, 2, 16, 1 ... tokens."""
     sizes = [7, 13, 2, 5, 3, 2, 16, 1, 9, 2, 31]
-    rp = Replay(setup["dir"], setup["dtype"], str(tmp_path), round64(256), setup["page"])
+    rp = Replay(setup["dir"], setup["dtype"], str(tmp_path), round64(256), setup["page"], graphs=graphs)
     for rid, (ids, want) in setup["reqs"].items():
         pos, k, got = 0, 0, []
         while pos < len(ids):
@@ -73,9 +89,13 @@ def test_portions_of_changing_size(setup, tmp_path):
     assert rp.close() == 0
 
 
-def test_mixed_with_page_reuse(setup, tmp_path):
+@GRAPHS
+@pytest.mark.parametrize("pool_of", [4, 2])
+def test_mixed_with_page_reuse(setup, tmp_path, graphs, pool_of):
     """Up to four live requests, portions of some beside decoded tokens of others; the
-    pool only holds what is live, so pages of finished requests are used again."""
+    pool only holds what is live, so pages of finished requests are used again.  ``pool_of``:
+    the pool holds the 4 or the 2 largest requests; with 2 even the configuration with only four
+    requests has to hand pages on from a finished request to a new one."""
     reqs = setup["reqs"]
     order = list(reqs)
     # a fixed plan: request -> list of portion sizes (prefill portions, then single tokens)
@@ -93,9 +113,10 @@ def test_mixed_with_page_reuse(setup, tmp_path):
             k += 1
         plans[rid] = cuts + [1] * tail
     live, waiting, pos, got = [], list(order), {r: 0 for r in order}, {r: [] for r in order}
-    # pool: the four largest requests at once
-    need = sum(sorted((round64(len(reqs[r][0])) for r in order), reverse=True)[:4])
-    rp = Replay(setup["dir"], setup["dtype"], str(tmp_path), need, setup["page"])
+    # pool: the largest requests at once
+    need = sum(sorted((round64(len(reqs[r][0])) for r in order), reverse=True)[:pool_of])
+    assert need < sum(round64(len(reqs[r][0])) for r in order), "the pool must be smaller than all requests together"
+    rp = Replay(setup["dir"], setup["dtype"], str(tmp_path), need, setup["page"], graphs=graphs)
     step_no = 0
     held = {}
     while waiting or live:
@@ -188,3 +209,99 @@ def test_long_portions_take_the_tensor_memory_attention(long_setup):
     assert ops.attention_launches.get("flash_tc", 0) == before + long_setup["cfg"]["n_layer"]
     assert_close(got, want[[0, 300, 599]], "bfloat16", "600-token portion")
     ops.check_device_errors()
+
+
+# ---------------------------------------------------------------------------------- the benchmark's widths
+# Two layers at the widths, head counts, vocabulary and positions of GPT-2 small, medium and XL: N = 4800 for
+# XL's Q|K|V product, 25 heads, a 50,257-column head whose rows are not 16-byte aligned.
+REAL = {"small": (768, 12), "medium": (1024, 16), "xl": (1600, 25)}
+
+
+def real_config(D, H, n_layer=2):
+    return dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=n_layer, n_embd=D, n_head=H, n_inner=4 * D,
+                vocab_size=50257, n_positions=1024, layer_norm_epsilon=1e-5, activation_function="gelu_new",
+                eos_token_id=50256)
+
+
+@pytest.fixture(scope="module", params=[(s, d) for s in REAL for d in ("float32", "bfloat16")], ids=lambda p: f"{p[0]}-{p[1]}")
+def real_setup(request, tmp_path_factory):
+    from helpers import make_tensors, write_model
+    size, dtype = request.param
+    cfg = real_config(*REAL[size])
+    d = str(tmp_path_factory.mktemp(f"model_{size}_{dtype}"))
+    write_model(d, cfg, make_tensors(cfg, seed=21, sharp=True), STORE[dtype])
+    cfg, w = plain_gpt2.read_model(d)
+    return dict(size=size, dtype=dtype, dir=d, cfg=cfg, w=w)
+
+
+def test_real_widths_whole_in_portions_and_one_by_one(real_setup, tmp_path):
+    """A 300-token prompt whole, the same as 128 + 172 tokens, then 8 tokens one by one, at a dozen places."""
+    dtype, cfg, w = real_setup["dtype"], real_setup["cfg"], real_setup["w"]
+    ids = random_ids(308, cfg["vocab_size"], 77)
+    places = [0, 1, 15, 16, 127, 128, 129, 255, 256, 299]
+    rows = places + list(range(300, 308))
+    want = plain_gpt2.logits_at(cfg, w, ids, rows, oracle_store(dtype)).numpy()
+    rp = Replay(real_setup["dir"], dtype, str(tmp_path), round64(308) * 2, 16)
+    got = rp.step([("w", ids[:300], places)], end=["w"])
+    assert_close(got, want[:len(places)], dtype, "whole")
+    first = [p for p in places if p < 128]
+    got = [rp.step([("p", ids[:128], first)]), rp.step([("p", ids[128:300], [p - 128 for p in places if p >= 128])])]
+    assert_close(np.concatenate(got), want[:len(places)], dtype, "128 + 172")
+    got = [rp.step([("p", [ids[i]], [0])]) for i in range(300, 308)]
+    assert_close(np.concatenate(got), want[len(places):], dtype, "one by one")
+    assert rp.close() == 0
+    assert rp.stats["graph_replays"] >= 6           # the single-token steps come back with the same shape
+
+
+MANY = {
+    # contexts from 1 to the last position, page and split edges among them; mostly short, so that the
+    # plain implementation stays affordable
+    "B": [1, 2, 3, 7, 8, 9, 15, 16, 17, 31, 32, 33, 63, 64, 65, 127, 128, 129, 130, 200, 255, 256] + list(range(20, 146, 3)),
+    "small": [1023, 1024, 641, 513, 512, 257, 129, 128, 127, 65, 64, 17, 16, 1, 2] + list(range(5, 103, 2)),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["B", "small"])
+def test_a_decode_step_of_40_and_of_64_requests(which, dtype, tmp_path):
+    """One decode step with 40 and with 64 live requests, logits of every request against the plain
+    implementation: the routes that only large batches take (on the bfloat16 path the tensor-memory product with
+    a norm kernel of its own and the cache write in its epilogue; decode attention with one CTA per request and
+    head), which the batch-64 point of the benchmark runs."""
+    from helpers import make_tensors, write_model
+    from mini_llm_b200 import ops
+    from mini_llm_b200.config.base import EngineConfig
+    from mini_llm_b200.engine.runner import ModelRunner, StepEntry
+
+    cfg = CONFIGS["B"] if which == "B" else real_config(*REAL["small"])
+    page = PAGE_SIZE["B"] if which == "B" else 16
+    d = write_model(str(tmp_path / "m"), cfg, make_tensors(cfg, seed=5, sharp=True), STORE[dtype])
+    cfg, w = plain_gpt2.read_model(d)
+    lengths = MANY[which]
+    assert len(lengths) == 64 and max(lengths) == cfg["n_positions"]
+    seqs = [random_ids(n, cfg["vocab_size"], 900 + i) for i, n in enumerate(lengths)]
+    want = np.concatenate([plain_gpt2.logits_at(cfg, w, ids, [len(ids) - 1], oracle_store(dtype)).numpy() for ids in seqs])
+    pool = sum(-(-n // page) * page for n in lengths)
+    runner = ModelRunner(d, EngineConfig(dtype=dtype, page_size=page, max_tokens=pool, max_num_seqs=64,
+                                         max_num_batched_tokens=2048))
+    for count in (40, 64):
+        rids = [(count, i) for i in range(count)]
+        for r in rids:
+            runner.add_request(r)
+        batch, used = [], 0
+        for r, ids in zip(rids, seqs):                      # the prompts (all but the last token), 2,048 tokens a step
+            if len(ids) == 1:
+                continue
+            if used + len(ids) - 1 > 2048:
+                runner.step(batch)
+                batch, used = [], 0
+            batch.append(StepEntry(r, ids[:-1], []))
+            used += len(ids) - 1
+        if batch:
+            runner.step(batch)
+        got = runner.step([StepEntry(r, [ids[-1]], [0]) for r, ids in zip(rids, seqs)]).cpu().numpy()
+        ops.check_device_errors()
+        assert_close(got, want[:count], dtype, f"decode step of {count}")
+        for r in rids:
+            runner.finish_request(r)
+        runner.cache.check()
