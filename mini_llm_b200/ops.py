@@ -17,7 +17,8 @@ from .csrc import build as _build
 
 F32, BF16 = 0, 1
 SMALL_M = 64                 # rows up to which the weight-streaming product is used
-SMALL_M_F32 = 16             # the same for the float32 weight-streaming product
+SMALL_M_F32 = 64             # the same for the float32 weight-streaming product (csrc/linear_stream_f32.cu)
+NORM_FUSE_M_F32 = 16         # rows up to which that product takes the norm into its loads (rows up to 2048 wide)
 DECODE_SPLIT = 128           # keys per split of the decode attention (csrc/attention_decode.cu)
 DECODE_CLUSTER_SPLITS = 8    # splits that can meet in one thread-block cluster (MAX_CLUSTER there)
 _FLASH_HEAD_DIMS = (16, 32, 64, 128)
@@ -54,6 +55,11 @@ def _signatures(lib):
                                      c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mllm_linear_smallm_f32": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
                                    c_void_p],
+        "mllm_linear_stream_f32": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
+                                   c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                   c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_linear_stream_f32_bind_error": [c_void_p],
+        "mllm_linear_stream_f32_error": [c_void_p],
         "mllm_linear_tcgen05": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p],
         "mllm_linear_tcgen05_qkv": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_void_p,
@@ -109,13 +115,15 @@ def _bind_error_word(lib) -> None:
     if _error_word is not None or not torch.cuda.is_available():
         return
     word = torch.zeros(1, dtype=torch.int32).pin_memory()
-    for name in ("mllm_tcgen05_bind_error", "mllm_attention_tcgen05_bind_error", "mllm_attention_decode_bind_error"):
+    for name in ("mllm_tcgen05_bind_error", "mllm_attention_tcgen05_bind_error", "mllm_attention_decode_bind_error",
+                 "mllm_linear_stream_f32_bind_error"):
         if getattr(lib, name)(word.data_ptr()) != 0:
             raise KernelError(lib.mllm_last_error().decode(errors="replace"))
     _error_word = word
 
 
-_WHO = {1: "the tcgen05 product", 2: "the tcgen05 attention", 3: "the decode attention"}
+_WHO = {1: "the tcgen05 product", 2: "the tcgen05 attention", 3: "the decode attention",
+        4: "the float32 weight-streaming product"}
 
 
 def raise_if_kernel_gave_up() -> None:
@@ -210,6 +218,10 @@ def check_device_errors() -> None:
         raise KernelError(lib.mllm_last_error().decode(errors="replace"))
     if code.value:
         raise KernelError("the decode attention kernel gave up waiting for a split's keys and values")
+    if lib.mllm_linear_stream_f32_error(ctypes.byref(code)) != 0:
+        raise KernelError(lib.mllm_last_error().decode(errors="replace"))
+    if code.value:
+        raise KernelError("the float32 weight-streaming product gave up waiting for its weights")
 
 
 _stream_handle = None     # set by stream_scope(); None: ask torch on every call
@@ -381,6 +393,39 @@ def _linear_fused(x, weight, bias, out, act, accumulate, norm: Optional[NormedIn
           out.data_ptr(), ldo, M, N, K, _ACT[act], int(accumulate), _dt(out), *nargs, *kargs, _stream())
 
 
+def _stream_f32_ok(weight, M, K) -> bool:
+    return weight.dtype == torch.float32 and M <= SMALL_M_F32 and K % 4 == 0 and weight.data_ptr() % 16 == 0
+
+
+def _norm_ok_f32(n: NormedInput) -> bool:
+    x = n.x
+    return (n.shape[0] <= NORM_FUSE_M_F32 and n.shape[1] <= 2048 and x.dtype == torch.float32 and x.stride(1) == 1
+            and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0 and n.gamma.data_ptr() % 16 == 0
+            and n.beta.data_ptr() % 16 == 0)
+
+
+def _linear_stream_f32(x, weight, bias, out, act, accumulate, norm: Optional[NormedInput], kv) -> None:
+    """The float32 weight-streaming product, with the norm fused on its input and/or the cache write on its output."""
+    M = norm.shape[0] if norm is not None else x.shape[0]
+    N, K = weight.shape
+    ldo = _rows("out", out)
+    if norm is not None:
+        xp, ldx = None, norm.x.stride(0)
+        nargs = (norm.x.data_ptr(), norm.rows.data_ptr() if norm.rows is not None else None,
+                 norm.gamma.data_ptr(), norm.beta.data_ptr(), float(norm.eps))
+    else:
+        xp, ldx = x.data_ptr(), _rows("x", x)
+        nargs = (None, None, None, None, 0.0)
+    if kv is not None:
+        k_pages, v_pages, slots, q_size = kv
+        _, Hkv, ps, dh = k_pages.shape
+        kargs = (k_pages.data_ptr(), v_pages.data_ptr(), slots.data_ptr(), int(q_size), Hkv, dh, ps)
+    else:
+        kargs = (None, None, None, 0, 0, 0, 0)
+    _call("mllm_linear_stream_f32", xp, ldx, weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+          out.data_ptr(), ldo, M, N, K, _ACT[act], int(accumulate), *nargs, *kargs, _stream())
+
+
 def linear_qkv_cache(x, weight, bias, q_out, k_pages, v_pages, slot_mapping, ws):
     """Q|K|V projection whose keys and values go to their page slots; returns the queries.
 
@@ -404,6 +449,17 @@ def linear_qkv_cache(x, weight, bias, q_out, k_pages, v_pages, slot_mapping, ws)
     if slot_mapping.numel() != M or q_out.shape[0] != M or v_pages.shape != k_pages.shape:
         raise KernelError(f"linear_qkv_cache: {M} rows, {slot_mapping.numel()} slots, q_out {tuple(q_out.shape)}")
     norm = x if isinstance(x, NormedInput) else None
+    if q_out.dtype == torch.float32 and _stream_f32_ok(weight, M, K) and q_out.stride(1) == 1 \
+            and k_pages.is_contiguous() and v_pages.is_contiguous():
+        # float32, few rows: the weight-streaming product writes keys and values from its epilogue
+        if norm is not None and not _norm_ok_f32(norm):
+            x, norm = norm.materialize(), None
+        if norm is not None or (x.is_cuda and x.dtype == torch.float32 and _rows("x", x) % 4 == 0 and x.data_ptr() % 16 == 0):
+            if bias is not None:
+                _cuda("bias", bias, torch.float32)
+            _linear_stream_f32(None if norm is not None else x, weight, bias, q_out, None, False, norm,
+                               (k_pages, v_pages, slot_mapping, q_size))
+            return q_out
     if norm is not None and not _norm_ok(norm):
         x, norm = norm.materialize(), None
     if q_out.dtype == torch.bfloat16 and _fusable(weight, M, K) and _small_m_wins(M, N, K) and (
@@ -453,6 +509,16 @@ def linear(x, weight, bias, out, act: Optional[str] = None, accumulate: bool = F
                 raise KernelError(f"linear: unknown activation {act!r}")
             _linear_fused(None, weight, bias, out, act, accumulate, x, None)
             return out
+        if impl in (None, "stream_f32") and _stream_f32_ok(weight, x.shape[0], weight.shape[1]) and _norm_ok_f32(x) \
+                and out.dtype == torch.float32 and x.shape[1] == weight.shape[1] \
+                and tuple(out.shape) == (x.shape[0], weight.shape[0]):
+            _cuda("out", out, contiguous=False)
+            if bias is not None:
+                _cuda("bias", bias, torch.float32)
+            if act not in _ACT:
+                raise KernelError(f"linear: unknown activation {act!r}")
+            _linear_stream_f32(None, weight, bias, out, act, accumulate, x, None)
+            return out
         x = x.materialize()
     _cuda("x", x, contiguous=False)
     _cuda("weight", weight, x.dtype)
@@ -478,7 +544,10 @@ def linear(x, weight, bias, out, act: Optional[str] = None, accumulate: bool = F
             impl = "smallm" if _small_m_wins(M, N, K) else "tcgen05"
         elif x.dtype == torch.float32 and out.dtype == torch.float32 and M <= SMALL_M_F32 and K % 4 == 0 \
                 and lda % 4 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
-            impl = "smallm_f32"
+            impl = "stream_f32"
+    if impl == "stream_f32":
+        _linear_stream_f32(x, weight, bias, out, act, accumulate, None, None)
+        return out
     if impl == "smallm_f32":
         _call("mllm_linear_smallm_f32", x.data_ptr(), lda, weight.data_ptr(),
               bias.data_ptr() if bias is not None else None, out.data_ptr(), ldo, M, N, K, _ACT[act],

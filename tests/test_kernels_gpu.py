@@ -251,26 +251,115 @@ def test_linear_small_m_rows_do_not_depend_on_the_batch(ops):
         assert torch.equal(part, full[lo:hi])
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 768, 768), (8, 2304, 768), (3, 50, 40), (16, 1003, 96), (5, 320, 3072), (13, 50257, 64)])
-def test_linear_small_m_float32(ops, M, N, K):
-    """The 32-bit weight-streaming product beside the plain kernel and float64."""
+@pytest.mark.parametrize("M,N,K", [(1, 768, 768), (8, 2304, 768), (3, 50, 40), (16, 1003, 96), (5, 320, 3072), (13, 50257, 64),
+                                   (17, 768, 3072), (40, 4800, 1600), (64, 768, 768), (64, 100, 6400), (33, 2304, 768),
+                                   (9, 7, 12), (2, 1600, 6400)])
+def test_linear_stream_float32(ops, M, N, K):
+    """The 32-bit weight-streaming product (weights by bulk copy into shared memory, warps own tokens, K slices
+    of narrow matrices shared by a cluster) beside float64, at 1 to 64 rows."""
     x, w, b = rnd(M, K, seed=1), rnd(N, K, seed=2, scale=K ** -0.5), rnd(N, seed=3)
     ref = x.double() @ w.double().t() + b.double()
     for act in (None, "gelu_tanh", "gelu_erf"):
         out = torch.full((M, N), 7.0, device=DEV)
-        ops.linear(x, w, b, out=out, act=act, impl="smallm_f32")
+        ops.linear(x, w, b, out=out, act=act, impl="stream_f32")
         want = ref if act is None else torch.nn.functional.gelu(ref, approximate="tanh" if act == "gelu_tanh" else "none")
         assert (out.double() - want).abs().max() < 2e-5 * max(1.0, want.abs().max().item())
     acc = rnd(M, N, seed=4)
     acc0 = acc.clone()
     wide = rnd(M, K + 8, seed=5)
-    ops.linear(wide[:, 4:4 + K], w, None, out=acc, accumulate=True, impl="smallm_f32")
+    ops.linear(wide[:, 4:4 + K], w, None, out=acc, accumulate=True, impl="stream_f32")
     assert (acc.double() - (acc0.double() + wide[:, 4:4 + K].double() @ w.double().t())).abs().max() < 1e-4
+    # a row does not depend on the batch: alone, in a pair, and in the whole batch it has the same bits
     full = torch.empty(M, N, device=DEV)
-    ops.linear(x, w, None, out=full, impl="smallm_f32")
-    one = torch.empty(1, N, device=DEV)
-    ops.linear(x[M - 1:M], w, None, out=one, impl="smallm_f32")
-    assert torch.equal(one, full[M - 1:M])                     # a row does not depend on the batch
+    ops.linear(x, w, None, out=full, impl="stream_f32")
+    for lo, hi in ((M - 1, M), (0, 1), (max(0, M - 9), M), (0, min(M, 17))):
+        part = torch.empty(hi - lo, N, device=DEV)
+        ops.linear(x[lo:hi], w, None, out=part, impl="stream_f32")
+        assert torch.equal(part, full[lo:hi]), (lo, hi)
+    if M <= 64:                                   # and it is what the dispatcher picks for float32 rows up to 64
+        auto = torch.empty(M, N, device=DEV)
+        n0 = ops.launches
+        ops.linear(x, w, None, out=auto)
+        assert torch.equal(auto, full) and ops.launches == n0 + 1
+    ops.check_device_errors()
+
+
+@pytest.mark.parametrize("M,N,K,eps", [(1, 768, 768, 1e-5), (8, 2304, 768, 1e-5), (5, 1000, 96, 1e-6), (16, 320, 1600, 1e-5),
+                                       (13, 50257, 64, 1e-3), (9, 200, 1024, 1e-5), (16, 4800, 2048, 1e-5)])
+def test_stream_float32_product_with_the_norm_fused_in(ops, M, N, K, eps):
+    """LayerNorm fused into the float32 weight-streaming product (the owning warp keeps the row in registers),
+    also with gathered rows, against float64 and against the two separate kernels; one launch."""
+    from mini_llm_b200.engine.context import Workspace
+    ws = Workspace(torch.device(DEV), 64)
+    x = rnd(M + 3, K, seed=1, scale=2.0) + 0.5
+    gamma, beta = rnd(K, seed=2) + 1.0, rnd(K, seed=3)
+    w, b = rnd(N, K, seed=4, scale=K ** -0.5), rnd(N, seed=5)
+    for rows in (None, torch.tensor([(3 * i + 1) % (M + 3) for i in range(M)], dtype=torch.int32, device=DEV)):
+        xin = x[:M] if rows is None else x
+        src = xin.double() if rows is None else xin.double()[rows.long()]
+        ref = torch.nn.functional.layer_norm(src, (K,), gamma.double(), beta.double(), eps) @ w.double().t() + b.double()
+        for act in (None, "gelu_tanh"):
+            want = ref if act is None else torch.nn.functional.gelu(ref, approximate="tanh")
+            got = torch.full((M, N), 3.0, device=DEV)
+            n0 = ops.launches
+            ops.linear(ops.NormedInput(xin, gamma, beta, eps, rows, ws, torch.float32), w, b, out=got, act=act)
+            assert ops.launches == n0 + 1
+            assert (got.double() - want).abs().max() < 2e-5 * max(1.0, want.abs().max().item())
+        normed = torch.empty(M, K, device=DEV)
+        ops.layernorm(xin, gamma, beta, eps, normed, rows=rows)
+        two = torch.empty(M, N, device=DEV)
+        ops.linear(normed, w, b, out=two, impl="stream_f32")
+        got = torch.empty(M, N, device=DEV)
+        ops.linear(ops.NormedInput(xin, gamma, beta, eps, rows, ws, torch.float32), w, b, out=got)
+        assert (got.double() - two.double()).abs().max() < 2e-5 * max(1.0, ref.abs().max().item())
+    # more than 16 rows or rows wider than 2048: the norm runs as a kernel of its own, the result is the same
+    M2 = 20
+    x2 = rnd(M2, K, seed=7)
+    got = torch.empty(M2, N, device=DEV)
+    ops.linear(ops.NormedInput(x2, gamma, beta, eps, None, ws, torch.float32), w, b, out=got)
+    ref = torch.nn.functional.layer_norm(x2.double(), (K,), gamma.double(), beta.double(), eps) @ w.double().t() + b.double()
+    assert (got.double() - ref).abs().max() < 2e-5 * max(1.0, ref.abs().max().item())
+    ops.check_device_errors()
+
+
+@pytest.mark.parametrize("M,H,Hkv,dh,page,K", [(1, 12, 12, 64, 16, 768), (8, 4, 4, 16, 16, 64), (13, 3, 3, 32, 8, 96),
+                                               (64, 6, 2, 64, 4, 128), (40, 25, 25, 64, 16, 1600)])
+def test_stream_float32_qkv_product_writes_the_cache(ops, M, H, Hkv, dh, page, K):
+    """The float32 Q|K|V projection whose epilogue puts keys and values into their page slots (with and without
+    the fused norm), against the product followed by the copy kernel."""
+    from mini_llm_b200.engine.context import Workspace
+    ws = Workspace(torch.device(DEV), 64)
+    q_size, kv = H * dh, Hkv * dh
+    N = q_size + 2 * kv
+    x = rnd(M, K, seed=1)
+    w, b = rnd(N, K, seed=2, scale=K ** -0.5), rnd(N, seed=3)
+    gamma, beta = rnd(K, seed=6) + 1.0, rnd(K, seed=7)
+    P = 40
+    g = torch.Generator().manual_seed(4)
+    slots = torch.randperm(P * page, generator=g)[:M].to(torch.int32).to(DEV)
+    for normed in (False, True):
+        if normed:
+            xin = torch.empty(M, K, device=DEV)
+            ops.layernorm(x, gamma, beta, 1e-5, xin)
+            arg = ops.NormedInput(x, gamma, beta, 1e-5, None, ws, torch.float32)
+        else:
+            xin = arg = x
+        qkv = torch.empty(M, N, device=DEV)
+        ops.linear(xin, w, b, out=qkv, impl="stream_f32")
+        wk = torch.full((P, Hkv, page, dh), 9.0, device=DEV)
+        wv = wk.clone()
+        ops.kv_write(qkv[:, q_size:q_size + kv], qkv[:, q_size + kv:], wk, wv, slots)
+        gk = torch.full((P, Hkv, page, dh), 9.0, device=DEV)
+        gv = gk.clone()
+        q_buf = torch.empty(M, q_size, device=DEV)
+        n0 = ops.launches
+        q = ops.linear_qkv_cache(arg, w, b, q_buf, gk, gv, slots, ws)
+        assert ops.launches == n0 + (1 if (not normed or M <= 16) else 2)      # one launch; the norm apart beyond 16 rows
+        assert q.data_ptr() == q_buf.data_ptr()
+        tol = 0.0 if not normed or M > 16 else 2e-5 * max(1.0, qkv.abs().max().item())
+        assert (q - qkv[:, :q_size]).abs().max() <= tol
+        assert (gk - wk).abs().max() <= tol and (gv - wv).abs().max() <= tol
+    ops.check_device_errors()
 
 
 def test_linear_rows_do_not_depend_on_the_batch(ops):

