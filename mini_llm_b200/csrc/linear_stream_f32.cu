@@ -3,22 +3,27 @@
 // the time goes into streaming the 32-bit weights from HBM once and into the dependent round trips
 // between the kernels of a step.
 //
-// A CTA of 8 warps owns 8 weight rows (and, when the matrix has too few rows to fill the GPU, a slice of
-// K: the CTAs of a thread-block cluster share a tile's K and meet in distributed shared memory).  Thread 0
-// brings the CTA's weights into shared memory with bulk copies (cp.async.bulk onto an mbarrier, one copy
-// per row) BEFORE the kernel waits for its predecessor: weights depend on no kernel of the step, so they
-// stream from HBM while the previous kernel still runs, and no register is held for them.  After the wait
-// every warp takes whole tokens (warp w the tokens w, w+8, ...; up to 8 per warp), its lanes split K in
-// float4 steps of 128, x comes straight from L2 and the weights from shared memory, conflict-free.
-// A token's sum runs over k in an order that depends on K and on the K slices only (lane partial sums
-// in k order, a butterfly over the lanes, slices in rank order): never on M, so a token's result does
-// not change with the batch.
+// A CTA of 8 warps owns tiles of 8 weight rows (and, when the matrix has too few rows to fill the GPU, a
+// slice of K: the CTAs of a thread-block cluster share a tile's K and meet in distributed shared memory).
+// Thread 0 brings the CTA's weights into shared memory with bulk copies (cp.async.bulk onto an mbarrier, one
+// copy per row) BEFORE the kernel waits for its predecessor: weights depend on no kernel of the step, so
+// they stream from HBM while the previous kernel still runs, and no register is held for them.
+//
+// Up to 16 rows of x (`few`): the threads split K.  Thread t takes the float4 positions t, t + 256, ... of
+// the slice for all 8 weight rows and 8 tokens at a time, so every weight leaves shared memory once and
+// every value of x leaves L2 once per CTA; the 64 sums of a thread meet first inside the warp (a butterfly
+// that halves the values a lane holds at every step: 62 shuffles), then across the warps in shared memory
+// in warp order, then across the slices in rank order.  17 to 64 rows (`many`): every warp takes whole
+// tokens (warp w the tokens w, w + 8, ...), its lanes split K, and the weights are read from shared memory
+// once per warp, which 8 tokens per warp amortise.
+// A token's sum runs over k in an order that depends on K and on the slices only, never on M, so a
+// token's result does not change with the batch (`few` and `many` differ in rounding, as two kernels do).
 //
 // Fused on the input (up to 16 rows, no K slices): LayerNorm of the 32-bit residual rows, optionally
-// gathered by `rows`; the warp that owns a token holds its row in registers, computes mean and variance
-// in two passes as the separate norm kernel does, and multiplies the normalised values.  Fused on the
-// output: bias, activation, the residual sum, and for a Q|K|V projection the write of the key and value
-// columns to their page slots.
+// gathered by `rows`; a warp per token computes mean and variance in two passes from registers, as the
+// separate norm kernel does, and the values are normalised as they are loaded.  Fused on the output:
+// bias, activation, the residual sum, and for a Q|K|V projection the write of the key and value columns
+// to their page slots.
 //
 // The reference's small-M kernel is a 1x32 SIMT tile chosen for M < 4 and the four GPT-2-small shapes
 // (src/kernels/decode_gemm.cu:42-134, 171-210); its norm, cache write and products are separate
@@ -274,6 +279,249 @@ linear_stream_f32_kernel(const float* x, long long ldx, const float* __restrict_
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Up to 16 rows: threads split K.
+
+constexpr int FEW_M = 16;
+constexpr int MAX_TILES = 4;            // tiles of R rows that one CTA may own
+
+// One output of the epilogue: bias, activation, then either a cache slot or the (residual) output.
+template <bool KVW>
+__device__ __forceinline__ void finish_one(float v, int m, int n, float bias, float* out, long long ldo, int act,
+                                           int accumulate, float old, int slot, const KvArgs& kv) {
+    float val = apply_act(v + bias, act);
+    if (KVW && n >= kv.q_size) {
+        const int kvw = kv.kv_heads * kv.head_dim;
+        const int c = n - kv.q_size;
+        float* pages = c < kvw ? kv.k_pages : kv.v_pages;
+        const int cc = c < kvw ? c : c - kvw;
+        const int head = cc / kv.head_dim, d = cc % kv.head_dim;
+        const int page = slot / kv.page_size, off = slot % kv.page_size;
+        pages[(((size_t)page * kv.kv_heads + head) * kv.page_size + off) * kv.head_dim + d] = val;
+    } else {
+        if (accumulate) val += old;
+        out[(size_t)m * ldo + n] = val;
+    }
+}
+
+template <bool LN, bool KVW>
+__global__ void __launch_bounds__(WARPS * 32, 2)
+linear_stream_f32_few_kernel(const float* x, long long ldx, const float* __restrict__ W, const float* __restrict__ bias,
+                             float* out, long long ldo, int M, int N, int K, int Ks, int S, int TILES, int act,
+                             int accumulate, LnArgs ln, KvArgs kv) {
+    extern __shared__ __align__(16) float smem[];
+    __shared__ __align__(8) uint64_t s_bar;
+    __shared__ float s_mean[FEW_M], s_rstd[FEW_M];
+    float* ws = smem;                                       // [TILES * R][Ks] this CTA's weights
+    float* red = ws + (size_t)TILES * R * Ks;               // [2][WARPS][64] the warps' sums, two buffers in turn
+    float* part = red + 2 * WARPS * 64;                     // S > 1, rank 0: [S][2 groups][64] the slices' sums
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
+    const int rank = S > 1 ? (int)cg::this_cluster().block_rank() : 0;
+    const int n0 = (blockIdx.x / S) * TILES * R;
+    const int rows_cta = max(0, min(TILES * R, N - n0));
+    const int k_lo = rank * Ks, k_hi = min(K, k_lo + Ks);
+    const int kn = max(0, k_hi - k_lo);                      // a multiple of 4, as K and Ks are
+    const int npos = (kn / 4 + WARPS * 32 - 1) / (WARPS * 32);
+    const int groups = (M + 7) / 8;
+
+    if (t == 0) {
+        tc::mbar_init(&s_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        tc::mbar_expect_tx(&s_bar, (uint32_t)(rows_cta * kn) * 4u);
+        if (kn > 0)
+            for (int r = 0; r < rows_cta; ++r)
+                tc::bulk_load(ws + (size_t)r * Ks, W + (size_t)(n0 + r) * K + k_lo, (uint32_t)kn * 4u, &s_bar);
+    }
+    if (S > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // "I run": completes once all do
+
+    // Who finishes which output.  A pass over (token group g, tile tl) ends with 64 sums, token g * 8 + i / 8 and row
+    // i % 8 of the tile.  The passes are numbered c = g * MAX_TILES + tl; the 64 threads with t / 64 == c % 4 finish
+    // pass c, so a thread finishes at most two passes (c and c + 4) and keeps their bias, old value and cache slot
+    // in registers, fetched long before they are needed.
+    const int e_i = t & 63, e_m = e_i >> 3, e_r = e_i & 7, e_c = t >> 6;
+    const int e_tl = e_c & (MAX_TILES - 1);                 // the same tile in both passes (c and c + 4 differ in g)
+    const int e_n = n0 + e_tl * R + e_r;
+    const bool e_col = e_tl < TILES && e_n < N && rank == 0;
+    // gamma and beta at this thread's first position and the bias of its output column are weights too: before the wait
+    float4 gam = make_float4(1.f, 1.f, 1.f, 1.f), bet = make_float4(0.f, 0.f, 0.f, 0.f);
+    if constexpr (LN) {
+        if (4 * t < kn) {
+            gam = __ldg(reinterpret_cast<const float4*>(ln.gamma + 4 * t));
+            bet = __ldg(reinterpret_cast<const float4*>(ln.beta + 4 * t));
+        }
+    }
+    const float e_bias = (e_col && bias) ? __ldg(bias + e_n) : 0.f;
+    pdl_wait();                 // everything below reads what earlier kernels of the step wrote
+    pdl_launch();
+
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* xbase = LN ? ln.x : x;
+    auto row_of = [&](int m) -> const float* {
+        return xbase + (size_t)((LN && ln.rows) ? __ldcg(ln.rows + m) : m) * ldx;
+    };
+    // every load of this thread that depends on the step goes out now, before anything waits for any of them
+    float4 xv[8];
+    auto load_x = [&](int g, int p) {
+        const int k = 4 * (t + p * WARPS * 32);
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+            const int mm = g * 8 + m;
+            xv[m] = (mm < M && k < kn) ? __ldcg(reinterpret_cast<const float4*>(row_of(mm) + k_lo + k)) : zero4;
+        }
+    };
+    load_x(0, 0);
+    float e_old[2] = {0.f, 0.f};
+    int e_slot[2] = {0, 0};
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const int mm = g * 8 + e_m;
+        if (e_col && mm < M) {
+            if (KVW && e_n >= kv.q_size) e_slot[g] = __ldcg(kv.slots + mm);
+            else if (accumulate) e_old[g] = __ldcg(out + (size_t)mm * ldo + e_n);
+        }
+    }
+
+    if constexpr (LN) {
+        // a warp per token: the row's first 1024 values in registers, what lies beyond (rows up to 2048 wide) is read a
+        // second time for the variance; mean and variance in two passes, as the separate norm kernel computes them.
+        // (Sums over the whole block of the values that the threads hold anyway were tried: two block-wide meetings
+        // cost more than reading the rows a second time from L2.)
+        for (int m = warp; m < M; m += WARPS) {
+            const float* row = row_of(m);
+            float4 rv[8];
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int k = c * 128 + lane * 4;
+                rv[c] = k < K ? __ldcg(reinterpret_cast<const float4*>(row + k)) : zero4;
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) sum += (rv[c].x + rv[c].y) + (rv[c].z + rv[c].w);
+            for (int k = 1024 + lane * 4; k < K; k += 128) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(row + k));
+                sum += (v.x + v.y) + (v.z + v.w);
+            }
+            const float mean = warp_sum(sum) / (float)K;
+            float var = 0.f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                if (c * 128 + lane * 4 < K) {
+                    const float a = rv[c].x - mean, b = rv[c].y - mean, cc = rv[c].z - mean, d = rv[c].w - mean;
+                    var += (a * a + b * b) + (cc * cc + d * d);
+                }
+            }
+            for (int k = 1024 + lane * 4; k < K; k += 128) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(row + k));
+                const float a = v.x - mean, b = v.y - mean, cc = v.z - mean, d = v.w - mean;
+                var += (a * a + b * b) + (cc * cc + d * d);
+            }
+            var = warp_sum(var) / (float)K;
+            if (lane == 0) {
+                s_mean[m] = mean;
+                s_rstd[m] = rsqrtf(var + ln.eps);
+            }
+        }
+    }
+    __syncthreads();            // the barrier is initialised, the statistics are in place
+
+    // the loaded values of x, normalised in place
+    auto norm_x = [&](int g, int p) {
+        if constexpr (LN) {
+            const int k = 4 * (t + p * WARPS * 32);
+            if (k >= kn) return;
+            float4 gg = gam, bb = bet;
+            if (p > 0) {
+                gg = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
+                bb = __ldg(reinterpret_cast<const float4*>(ln.beta + k));
+            }
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+                const int mm = min(g * 8 + m, FEW_M - 1);
+                const float mean = s_mean[mm], rstd = s_rstd[mm];
+                xv[m].x = (xv[m].x - mean) * rstd * gg.x + bb.x;
+                xv[m].y = (xv[m].y - mean) * rstd * gg.y + bb.y;
+                xv[m].z = (xv[m].z - mean) * rstd * gg.z + bb.z;
+                xv[m].w = (xv[m].w - mean) * rstd * gg.w + bb.w;
+            }
+        }
+    };
+    norm_x(0, 0);
+    const bool arrived = tc::mbar_wait(&s_bar, 0);
+    if (!arrived && t == 0) {             // gave up: tell the host; the results of the step are not used
+        atomicCAS(&g_stream_error, 0, 1);
+        tc::report_to_host(401);
+    }
+    cg::cluster_group cluster = cg::this_cluster();
+    if (S > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // rank 0 runs: its memory may be written
+    int buf = 0;
+    for (int g = 0; g < groups; ++g) {
+        for (int tl = 0; tl < TILES; ++tl) {
+            float acc[64];                                   // [token][row]
+#pragma unroll
+            for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+            const int rows_tile = min(R, rows_cta - tl * R);
+            for (int p = 0; p < npos; ++p) {
+                if (!(g == 0 && tl == 0 && p == 0) && (npos > 1 || tl == 0)) {
+                    load_x(g, p);
+                    norm_x(g, p);
+                }
+                const int k = 4 * (t + p * WARPS * 32);
+                if (k < kn && arrived) {
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const float4 w = r < rows_tile ? *reinterpret_cast<const float4*>(ws + (size_t)(tl * R + r) * Ks + k) : zero4;
+#pragma unroll
+                        for (int m = 0; m < 8; ++m) acc[m * 8 + r] = dot4(w, xv[m], acc[m * 8 + r]);
+                    }
+                }
+            }
+            // inside the warp: at every step a lane hands half of its values to the lane `off` away and adds what
+            // it gets to the half it keeps; afterwards lane l holds the warp's sums of the values 2l and 2l + 1
+#pragma unroll
+            for (int half = 32, off = 16; half >= 2; half >>= 1, off >>= 1) {
+                const bool upper = (lane & off) != 0;
+#pragma unroll
+                for (int i = 0; i < half; ++i) {
+                    const float send = upper ? acc[i] : acc[i + half];
+                    const float keep = upper ? acc[i + half] : acc[i];
+                    acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            }
+            float* rb = red + (size_t)buf * WARPS * 64;
+            *reinterpret_cast<float2*>(rb + warp * 64 + 2 * lane) = make_float2(acc[0], acc[1]);
+            __syncthreads();
+            const int c = g * MAX_TILES + tl;
+            if (e_c == (c & 3)) {                                             // the 64 threads that finish this pass
+                float v = rb[e_i];
+#pragma unroll
+                for (int w = 1; w < WARPS; ++w) v += rb[w * 64 + e_i];         // warp order
+                const int mm = g * 8 + e_m;
+                if (S > 1) {
+                    cluster.map_shared_rank(part, 0)[((size_t)rank * 2 + g) * 64 + e_i] = v;
+                } else if (e_col && mm < M) {
+                    finish_one<KVW>(v, mm, e_n, e_bias, out, ldo, act, accumulate, g ? e_old[1] : e_old[0],
+                                    g ? e_slot[1] : e_slot[0], kv);
+                }
+            }
+            buf ^= 1;
+        }
+    }
+    if (S > 1) {
+        cluster.sync();                                                        // every slice's sums are in place
+        if (rank != 0) return;
+        for (int g = 0; g < groups; ++g) {
+            if (e_c == (g * MAX_TILES & 3)) {                                  // one tile per CTA when K is sliced
+                float v = part[(size_t)g * 64 + e_i];
+                for (int q = 1; q < S; ++q) v += part[((size_t)q * 2 + g) * 64 + e_i];   // rank order
+                const int mm = g * 8 + e_m;
+                if (e_col && mm < M)
+                    finish_one<KVW>(v, mm, e_n, e_bias, out, ldo, act, accumulate, g ? e_old[1] : e_old[0],
+                                    g ? e_slot[1] : e_slot[0], kv);
+            }
+        }
+    }
+}
+
 int sm_count() {
     static int n = 0;
     if (!n) {
@@ -288,11 +536,11 @@ int sm_count() {
 }  // namespace
 
 // K slices that the CTAs of a cluster share, chosen from the matrix alone (never from M): a matrix with few
-// rows gets slices until its CTAs fill the GPU twice, as long as a slice keeps at least 256 of K.
+// rows gets slices while its CTAs still fit the GPU in one wave of two per SM and a slice keeps at least 256 of K.
 MLLM_EXPORT int mllm_linear_stream_f32_slices(int N, int K) {
     int S = 1;
     const int tiles = (N + R - 1) / R;
-    while (S < MAX_SLICES && tiles * S < 2 * sm_count() && K / (2 * S) >= 256) S *= 2;
+    while (S < MAX_SLICES && tiles * S * 2 <= 2 * sm_count() && K / (2 * S) >= 256) S *= 2;
     return S;
 }
 
@@ -326,29 +574,71 @@ MLLM_EXPORT int mllm_linear_stream_f32(const void* x, long long ldx, const void*
     if (kvw && (!v_pages || !slots || kv_heads <= 0 || head_dim <= 0 || page_size <= 0 ||
                 N != q_size + 2 * kv_heads * head_dim || accumulate))
         return mllm_fail(1, "linear_stream_f32: cache write arguments do not fit N=%d", N);
-    int S = norm ? 1 : mllm_linear_stream_f32_slices(N, K);
+    LnArgs ln = {(const float*)ln_x, ln_rows, ln_gamma, ln_beta, ln_eps};
+    KvArgs kv = {(float*)k_pages, (float*)v_pages, slots, q_size, kv_heads, head_dim, page_size};
+    const int tiles = (N + R - 1) / R;
+    if (M <= FEW_M) {
+        // threads split K; CTAs own several tiles of narrow K so that the grid is one wave of two CTAs per SM
+        int S = norm ? 1 : mllm_linear_stream_f32_slices(N, K);
+        int Ks = ((K + S - 1) / S + 3) / 4 * 4;
+        while (!norm && S < MAX_SLICES && (size_t)R * Ks * 4 > 96 * 1024) {       // rows too long for shared memory
+            S *= 2;
+            Ks = ((K + S - 1) / S + 3) / 4 * 4;
+        }
+        int T = 1;
+        if (S == 1)      // measured: two CTAs per SM in one wave beat one CTA per SM with twice the tiles
+            while (T < MAX_TILES && (tiles + T - 1) / T > 2 * sm_count() && (size_t)(T + 1) * R * Ks * 4 <= 96 * 1024) ++T;
+        const size_t smem = ((size_t)T * R * Ks + 2 * WARPS * 64 + (S > 1 ? S * 128 : 0)) * 4;
+        if (smem > 200 * 1024) return mllm_fail(1, "linear_stream_f32: K=%d is too long for shared memory", K);
+        using Few = void (*)(const float*, long long, const float*, const float*, float*, long long, int, int, int, int,
+                             int, int, int, int, LnArgs, KvArgs);
+        Few kern = norm ? (kvw ? (Few)linear_stream_f32_few_kernel<true, true> : (Few)linear_stream_f32_few_kernel<true, false>)
+                        : (kvw ? (Few)linear_stream_f32_few_kernel<false, true> : (Few)linear_stream_f32_few_kernel<false, false>);
+        if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((tiles + T - 1) / T * S);
+        cfg.blockDim = dim3(WARPS * 32);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        int na = 0;
+        if (S > 1) {
+            attr[na].id = cudaLaunchAttributeClusterDimension;
+            attr[na].val.clusterDim.x = S;
+            attr[na].val.clusterDim.y = 1;
+            attr[na].val.clusterDim.z = 1;
+            ++na;
+        }
+        if (g_mllm_pdl) {
+            attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[na].val.programmaticStreamSerializationAllowed = 1;
+            ++na;
+        }
+        cfg.attrs = attr;
+        cfg.numAttrs = na;
+        MLLM_CUDA(cudaLaunchKernelEx(&cfg, kern, (const float*)x, ldx, (const float*)W, bias, (float*)out, ldo, M, N, K, Ks,
+                                     S, T, act, accumulate, ln, kv));
+        return 0;
+    }
+    int S = mllm_linear_stream_f32_slices(N, K);
     int Ks = ((K + S - 1) / S + 3) / 4 * 4;
-    size_t smem = (size_t)R * Ks * 4 + (norm ? (size_t)2 * K * 4 : (S > 1 ? (size_t)S * MAX_M * R * 4 : 0));
-    while (smem > 200 * 1024 && S < MAX_SLICES && !norm) {          // rows too long for shared memory: more slices
+    size_t smem = (size_t)R * Ks * 4 + (S > 1 ? (size_t)S * MAX_M * R * 4 : 0);
+    while (smem > 200 * 1024 && S < MAX_SLICES) {          // rows too long for shared memory: more slices
         S *= 2;
         Ks = ((K + S - 1) / S + 3) / 4 * 4;
         smem = (size_t)R * Ks * 4 + (size_t)S * MAX_M * R * 4;
     }
     if (smem > 200 * 1024) return mllm_fail(1, "linear_stream_f32: K=%d is too long for shared memory", K);
-    const int tiles = (N + R - 1) / R;
-    LnArgs ln = {(const float*)ln_x, ln_rows, ln_gamma, ln_beta, ln_eps};
-    KvArgs kv = {(float*)k_pages, (float*)v_pages, slots, q_size, kv_heads, head_dim, page_size};
-    const int tpw = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
-    const int kc = !norm ? 0 : K <= 1024 ? 8 : 16;
+    const int tpw = M <= 32 ? 4 : 8;
     using Kern = void (*)(const float*, long long, const float*, const float*, float*, long long, int, int, int, int,
                           int, int, int, LnArgs, KvArgs);
     Kern kern = nullptr;
 #define PICK(T, C)                                                                              \
-    if (tpw == T && kc == C)                                                                    \
+    if (tpw == T)                                                                               \
         kern = kvw ? (Kern)linear_stream_f32_kernel<T, C, true> : (Kern)linear_stream_f32_kernel<T, C, false>;
-    PICK(1, 0) PICK(2, 0) PICK(4, 0) PICK(8, 0) PICK(1, 8) PICK(2, 8) PICK(1, 16) PICK(2, 16)
+    PICK(4, 0) PICK(8, 0)
 #undef PICK
-    if (!kern) return mllm_fail(1, "linear_stream_f32: no kernel for M=%d with%s norm", M, norm ? "" : "out");
+    if (!kern) return mllm_fail(1, "linear_stream_f32: no kernel for M=%d", M);
     if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * S);
