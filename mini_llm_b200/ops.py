@@ -53,8 +53,6 @@ def _signatures(lib):
         "mllm_linear_smallm_fused": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int,
                                      c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-        "mllm_linear_smallm_f32": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
-                                   c_void_p],
         "mllm_linear_stream_f32": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
                                    c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
                                    c_int, c_int, c_int, c_int, c_void_p],
@@ -547,11 +545,6 @@ def linear(x, weight, bias, out, act: Optional[str] = None, accumulate: bool = F
             impl = "stream_f32"
     if impl == "stream_f32":
         _linear_stream_f32(x, weight, bias, out, act, accumulate, None, None)
-        return out
-    if impl == "smallm_f32":
-        _call("mllm_linear_smallm_f32", x.data_ptr(), lda, weight.data_ptr(),
-              bias.data_ptr() if bias is not None else None, out.data_ptr(), ldo, M, N, K, _ACT[act],
-              int(accumulate), _stream())
         return out
     if impl in ("smallm", "tcgen05"):
         _call("mllm_linear_" + impl, x.data_ptr(), lda, weight.data_ptr(),
