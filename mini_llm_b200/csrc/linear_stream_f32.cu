@@ -38,7 +38,7 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int R = 8;                    // weight rows per CTA
 constexpr int MAX_M = 64;
-constexpr int MAX_SLICES = 4;
+constexpr int MAX_SLICES = 4;             // K slices of the kernel for up to 16 rows
 
 __device__ int g_stream_error = 0;      // 1: the weights of a CTA never arrived (bounded wait ran out)
 
@@ -61,222 +61,6 @@ __device__ __forceinline__ float dot4(const float4& w, const float4& x, float ac
     acc = fmaf(w.y, x.y, acc);
     acc = fmaf(w.z, x.z, acc);
     return fmaf(w.w, x.w, acc);
-}
-
-// TPW: tokens per warp.  KC: with LN, float4 steps of a row that a lane keeps (rows up to KC*128 wide); 0 = no norm.
-template <int TPW, int KC, bool KVW>
-__global__ void __launch_bounds__(WARPS * 32)
-linear_stream_f32_kernel(const float* x, long long ldx, const float* __restrict__ W, const float* __restrict__ bias,
-                         float* out, long long ldo, int M, int N, int K, int Ks, int S, int act, int accumulate,
-                         LnArgs ln, KvArgs kv) {
-    constexpr bool LN = KC > 0;
-    extern __shared__ __align__(16) float smem[];
-    __shared__ __align__(8) uint64_t s_bar;
-    float* ws = smem;                                   // [R][Ks] this CTA's weights
-    float* part = smem + (size_t)R * Ks;                // S > 1, rank 0: [S][MAX_M][R] partial sums; LN: gamma | beta
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int rank = S > 1 ? (int)cg::this_cluster().block_rank() : 0;
-    const int n0 = (blockIdx.x / S) * R;
-    const int rows = min(R, N - n0);
-    const int k_lo = rank * Ks, k_hi = min(K, k_lo + Ks);
-    const int kn = max(0, k_hi - k_lo);                  // a multiple of 4, as K and Ks are
-
-    if (threadIdx.x == 0) {
-        tc::mbar_init(&s_bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        tc::mbar_expect_tx(&s_bar, (uint32_t)(rows * kn) * 4u);
-        if (kn > 0)
-            for (int r = 0; r < rows; ++r)
-                tc::bulk_load(ws + (size_t)r * Ks, W + (size_t)(n0 + r) * K + k_lo, (uint32_t)kn * 4u, &s_bar);
-    }
-    if (S > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // "I run": completes once all do
-    if constexpr (LN) {
-        // gamma and beta are weights as well: into shared memory before the wait
-        for (int k = threadIdx.x * 4; k < K; k += WARPS * 32 * 4) {
-            *reinterpret_cast<float4*>(part + k) = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
-            *reinterpret_cast<float4*>(part + K + k) = __ldg(reinterpret_cast<const float4*>(ln.beta + k));
-        }
-    }
-    pdl_wait();                 // everything below reads what earlier kernels of the step wrote
-    pdl_launch();
-    __syncthreads();            // the barrier is initialised, gamma and beta are in place
-
-    // the residual values that this lane's outputs are added to, fetched early: lane r finishes row n0 + r
-    const int e_n = n0 + lane;
-    const bool e_ok = lane < rows && rank == 0;
-    float e_old[TPW];
-    int e_slot[TPW];
-#pragma unroll
-    for (int j = 0; j < TPW; ++j) {
-        const int m = warp + j * WARPS;
-        e_old[j] = 0.f;
-        e_slot[j] = 0;
-        if (e_ok && m < M) {
-            if (KVW && e_n >= kv.q_size) e_slot[j] = __ldcg(kv.slots + m);
-            else if (accumulate) e_old[j] = __ldcg(out + (size_t)m * ldo + e_n);
-        }
-    }
-
-    float acc[R][TPW];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int j = 0; j < TPW; ++j) acc[r][j] = 0.f;
-    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    bool arrived = true;
-
-    if constexpr (LN) {
-        // the rows of this warp's tokens, whole, in registers; mean and variance in two passes
-        float4 xr[TPW][KC];
-#pragma unroll
-        for (int j = 0; j < TPW; ++j) {
-            const int m = warp + j * WARPS;
-            const float* row = ln.x + (size_t)((m < M && ln.rows) ? __ldcg(ln.rows + m) : (m < M ? m : 0)) * ldx;
-#pragma unroll
-            for (int c = 0; c < KC; ++c) {
-                const int k = c * 128 + lane * 4;
-                xr[j][c] = (m < M && k < K) ? __ldcg(reinterpret_cast<const float4*>(row + k)) : zero4;
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < TPW; ++j) {
-            float s = 0.f;
-#pragma unroll
-            for (int c = 0; c < KC; ++c) s += (xr[j][c].x + xr[j][c].y) + (xr[j][c].z + xr[j][c].w);
-            const float mean = warp_sum(s) / (float)K;
-            float v = 0.f;
-#pragma unroll
-            for (int c = 0; c < KC; ++c) {
-                if (c * 128 + lane * 4 < K) {
-                    const float a = xr[j][c].x - mean, b = xr[j][c].y - mean, cc = xr[j][c].z - mean, d = xr[j][c].w - mean;
-                    v += (a * a + b * b) + (cc * cc + d * d);
-                }
-            }
-            const float rstd = rsqrtf(warp_sum(v) / (float)K + ln.eps);
-#pragma unroll
-            for (int c = 0; c < KC; ++c) {
-                const int k = c * 128 + lane * 4;
-                if (k < K) {
-                    const float4 g = *reinterpret_cast<const float4*>(part + k);
-                    const float4 b = *reinterpret_cast<const float4*>(part + K + k);
-                    xr[j][c].x = (xr[j][c].x - mean) * rstd * g.x + b.x;
-                    xr[j][c].y = (xr[j][c].y - mean) * rstd * g.y + b.y;
-                    xr[j][c].z = (xr[j][c].z - mean) * rstd * g.z + b.z;
-                    xr[j][c].w = (xr[j][c].w - mean) * rstd * g.w + b.w;
-                }
-            }
-        }
-        arrived = tc::mbar_wait(&s_bar, 0);
-        if (arrived) {
-#pragma unroll
-            for (int c = 0; c < KC; ++c) {
-                const int k = c * 128 + lane * 4;
-                if (k < kn) {
-#pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        const float4 w = r < rows ? *reinterpret_cast<const float4*>(ws + (size_t)r * Ks + k) : zero4;
-#pragma unroll
-                        for (int j = 0; j < TPW; ++j) acc[r][j] = dot4(w, xr[j][c], acc[r][j]);
-                    }
-                }
-            }
-        }
-    } else {
-        // x in steps of 128 floats per warp, the next step's values on their way while this one is multiplied
-        const int nsteps = (kn + 127) / 128;
-        float4 xc[TPW], xn[TPW];
-        auto load_x = [&](int c, float4 (&dst)[TPW]) {
-            const int k = c * 128 + lane * 4;
-#pragma unroll
-            for (int j = 0; j < TPW; ++j) {
-                const int m = warp + j * WARPS;
-                dst[j] = (m < M && k < kn) ? __ldcg(reinterpret_cast<const float4*>(x + (size_t)m * ldx + k_lo + k)) : zero4;
-            }
-        };
-        if (nsteps > 0) load_x(0, xc);
-        arrived = tc::mbar_wait(&s_bar, 0);
-        if (arrived) {
-            for (int c = 0; c < nsteps; ++c) {
-                if (c + 1 < nsteps) load_x(c + 1, xn);
-                const int k = c * 128 + lane * 4;
-                if (k < kn) {
-#pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        const float4 w = r < rows ? *reinterpret_cast<const float4*>(ws + (size_t)r * Ks + k) : zero4;
-#pragma unroll
-                        for (int j = 0; j < TPW; ++j) acc[r][j] = dot4(w, xc[j], acc[r][j]);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < TPW; ++j) xc[j] = xn[j];
-            }
-        }
-    }
-    if (!arrived && lane == 0) {          // gave up: tell the host; the sums stay zero, the step's results are not used
-        atomicCAS(&g_stream_error, 0, 1);
-        tc::report_to_host(401);
-    }
-
-    // lanes' partial sums meet; afterwards lane r holds row r's sum of every token of the warp
-    float v[TPW];
-#pragma unroll
-    for (int j = 0; j < TPW; ++j) v[j] = 0.f;
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int j = 0; j < TPW; ++j) {
-            const float s = warp_sum(acc[r][j]);
-            if (lane == r) v[j] = s;
-        }
-
-    if (S > 1) {
-        // every rank leaves its partial sums in rank 0's shared memory; rank 0 adds them in rank order
-        cg::cluster_group cluster = cg::this_cluster();
-        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");       // rank 0 runs: its memory may be written
-        float* dst = cluster.map_shared_rank(part, 0) + (size_t)rank * MAX_M * R;
-        if (lane < R) {
-#pragma unroll
-            for (int j = 0; j < TPW; ++j) {
-                const int m = warp + j * WARPS;
-                if (m < M) dst[m * R + lane] = v[j];
-            }
-        }
-        cluster.sync();                                                            // all partial sums are in place
-        if (rank != 0) return;
-        if (lane < R) {
-#pragma unroll
-            for (int j = 0; j < TPW; ++j) {
-                const int m = warp + j * WARPS;
-                if (m < M) {
-                    float s = part[m * R + lane];
-                    for (int q = 1; q < S; ++q) s += part[(size_t)q * MAX_M * R + m * R + lane];
-                    v[j] = s;
-                }
-            }
-        }
-    }
-
-    if (e_ok) {
-        const float b = bias ? __ldg(bias + e_n) : 0.f;
-#pragma unroll
-        for (int j = 0; j < TPW; ++j) {
-            const int m = warp + j * WARPS;
-            if (m >= M) continue;
-            float val = apply_act(v[j] + b, act);
-            if (KVW && e_n >= kv.q_size) {
-                const int kvw = kv.kv_heads * kv.head_dim;
-                const int c = e_n - kv.q_size;
-                float* pages = c < kvw ? kv.k_pages : kv.v_pages;
-                const int cc = c < kvw ? c : c - kvw;
-                const int head = cc / kv.head_dim, d = cc % kv.head_dim;
-                const int page = e_slot[j] / kv.page_size, off = e_slot[j] % kv.page_size;
-                pages[(((size_t)page * kv.kv_heads + head) * kv.page_size + off) * kv.head_dim + d] = val;
-            } else {
-                if (accumulate) val += e_old[j];
-                out[(size_t)m * ldo + e_n] = val;
-            }
-        }
-    }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -522,6 +306,147 @@ linear_stream_f32_few_kernel(const float* x, long long ldx, const float* __restr
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// 17 to 64 rows: a CTA owns all tokens and a tile of RT = 4 * RJ weight rows (16, 24 or 32) over a slice of K; its
+// 8 warps split the slice in chunks of 8 floats (warp w the chunks w, w + 8, ...), and inside a warp the lanes form
+// 8 token groups x 4 row groups: lane (tg, rg) multiplies the tokens tg, tg + 8, ... with the rows rg, rg + 4, ...
+// (8 x RJ sums per lane).  Per step of 4 floats of K a lane loads MI float4 of x straight from L2 (an address is
+// shared by the 4 lanes of a token group: one request) and RJ float4 of the weights from shared memory (an address
+// is shared by the 8 lanes of a row group: a broadcast), for 4 * MI * RJ fused multiply-adds.  The warps' tiles meet
+// in shared memory in warp order, the slices' tiles in rank 0's shared memory in rank order.
+constexpr int MANY_WS_PAD = 4;          // floats between weight rows in shared memory: row groups fall on different banks
+constexpr int MANY_RED_PAD = 4;         // the same between token rows of the warps' partial tiles
+
+template <int MI, int RJ, bool KVW>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+linear_stream_f32_many_kernel(const float* x, long long ldx, const float* __restrict__ W, const float* __restrict__ bias,
+                              float* out, long long ldo, int M, int N, int K, int Ks, int S, int act, int accumulate,
+                              KvArgs kv) {
+    constexpr int RT = 4 * RJ, MT = 8 * MI;
+    extern __shared__ __align__(16) float smem[];
+    __shared__ __align__(8) uint64_t s_bar;
+    const int wstride = Ks + MANY_WS_PAD, rstride = RT + MANY_RED_PAD;
+    float* ws = smem;                                       // [RT][Ks + pad] this CTA's weights
+    float* red = ws + (size_t)RT * wstride;                 // [WARPS][MT][RT + pad] the warps' partial tiles
+    float* part = red + (size_t)WARPS * MT * rstride;       // S > 1, rank 0: [S - 1][MT * RT] the other slices' tiles
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
+    const int tg = lane >> 2, rg = lane & 3;
+    const int rank = S > 1 ? (int)cg::this_cluster().block_rank() : 0;
+    const int n0 = (blockIdx.x / S) * RT;
+    const int rows = max(0, min(RT, N - n0));
+    const int k_lo = rank * Ks, k_hi = min(K, k_lo + Ks);
+    const int kn = max(0, k_hi - k_lo);                      // a multiple of 4, as K and Ks are
+
+    if (t == 0) {
+        tc::mbar_init(&s_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        tc::mbar_expect_tx(&s_bar, (uint32_t)(rows * kn) * 4u);
+        if (kn > 0)
+            for (int r = 0; r < rows; ++r)
+                tc::bulk_load(ws + (size_t)r * wstride, W + (size_t)(n0 + r) * K + k_lo, (uint32_t)kn * 4u, &s_bar);
+    }
+    if (S > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // "I run": completes once all do
+    pdl_wait();                 // everything below reads what earlier kernels of the step wrote
+    pdl_launch();
+    __syncthreads();            // the barrier is initialised
+
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int nchunks = (kn + 7) / 8;
+    float acc[MI][RJ];
+#pragma unroll
+    for (int i = 0; i < MI; ++i)
+#pragma unroll
+        for (int j = 0; j < RJ; ++j) acc[i][j] = 0.f;
+    // this lane's rows of x (tokens tg, tg + 8, ...), as offsets from the slice's start; a token beyond M reads token 0
+    // and is never written
+    const float* xs = x + k_lo;
+    long long xoff[MI];
+#pragma unroll
+    for (int i = 0; i < MI; ++i) xoff[i] = (tg + 8 * i < M ? (long long)(tg + 8 * i) : 0LL) * ldx;
+    float4 xa[MI][2], xb[MI][2];
+    auto load_x = [&](int c, float4 (&dst)[MI][2]) {
+        const bool h1 = c * 8 + 4 < kn;                   // the last chunk of a slice may hold 4 floats only
+#pragma unroll
+        for (int i = 0; i < MI; ++i) {
+            const float* row = xs + xoff[i] + c * 8;
+            dst[i][0] = __ldcg(reinterpret_cast<const float4*>(row));
+            dst[i][1] = h1 ? __ldcg(reinterpret_cast<const float4*>(row + 4)) : zero4;
+        }
+    };
+    auto multiply = [&](int c, const float4 (&xv)[MI][2]) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int k = c * 8 + 4 * h;
+            if (k < kn) {
+#pragma unroll
+                for (int j = 0; j < RJ; ++j) {
+                    const int r = rg + 4 * j;
+                    const float4 w = r < rows ? *reinterpret_cast<const float4*>(ws + (size_t)r * wstride + k) : zero4;
+#pragma unroll
+                    for (int i = 0; i < MI; ++i) acc[i][j] = dot4(w, xv[i][h], acc[i][j]);
+                }
+            }
+        }
+    };
+    if (warp < nchunks) load_x(warp, xa);
+    const bool arrived = tc::mbar_wait(&s_bar, 0);
+    if (!arrived && t == 0) {             // gave up: tell the host; the results of the step are not used
+        atomicCAS(&g_stream_error, 0, 1);
+        tc::report_to_host(402);
+    }
+    if (arrived) {
+        // two chunks per round, the two register sets in turn: the next chunk's values are on their way while one is multiplied
+        for (int c = warp; c < nchunks; c += 2 * WARPS) {
+            if (c + WARPS < nchunks) load_x(c + WARPS, xb);
+            multiply(c, xa);
+            if (c + WARPS < nchunks) {
+                if (c + 2 * WARPS < nchunks) load_x(c + 2 * WARPS, xa);
+                multiply(c + WARPS, xb);
+            }
+        }
+    }
+    // the warps' partial tiles meet in shared memory
+#pragma unroll
+    for (int i = 0; i < MI; ++i)
+#pragma unroll
+        for (int j = 0; j < RJ; ++j) red[((size_t)warp * MT + tg + 8 * i) * rstride + rg + 4 * j] = acc[i][j];
+    __syncthreads();
+    cg::cluster_group cluster = cg::this_cluster();
+    if (S > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // rank 0 runs: its memory may be written
+    constexpr int PER = (MT * RT + WARPS * 32 - 1) / (WARPS * 32);        // outputs per thread
+    float v[PER];
+#pragma unroll
+    for (int q = 0; q < PER; ++q) {
+        const int o = t + q * WARPS * 32;
+        v[q] = 0.f;
+        if (o < MT * RT) {
+            const int m = o / RT, r = o % RT;
+            float sum = red[(size_t)m * rstride + r];
+#pragma unroll
+            for (int w = 1; w < WARPS; ++w) sum += red[((size_t)w * MT + m) * rstride + r];     // warp order
+            v[q] = sum;
+            if (rank > 0) cluster.map_shared_rank(part, 0)[(size_t)(rank - 1) * MT * RT + o] = sum;
+        }
+    }
+    if (S > 1) {
+        cluster.sync();                                                        // every slice's tile is in place
+        if (rank != 0) return;
+    }
+#pragma unroll
+    for (int q = 0; q < PER; ++q) {
+        const int o = t + q * WARPS * 32;
+        const int m = o / RT, n = n0 + o % RT;
+        if (o < MT * RT && m < M && n < N) {
+            float sum = v[q];
+            for (int p = 1; p < S; ++p) sum += part[(size_t)(p - 1) * MT * RT + o];               // rank order
+            const bool to_cache = KVW && n >= kv.q_size;
+            const float old = (accumulate && !to_cache) ? __ldcg(out + (size_t)m * ldo + n) : 0.f;
+            const int slot = to_cache ? __ldcg(kv.slots + m) : 0;
+            finish_one<KVW>(sum, m, n, bias ? __ldg(bias + n) : 0.f, out, ldo, act, accumulate, old, slot, kv);
+        }
+    }
+}
+
 int sm_count() {
     static int n = 0;
     if (!n) {
@@ -542,6 +467,27 @@ MLLM_EXPORT int mllm_linear_stream_f32_slices(int N, int K) {
     const int tiles = (N + R - 1) / R;
     while (S < MAX_SLICES && tiles * S * 2 <= 2 * sm_count() && K / (2 * S) >= 256) S *= 2;
     return S;
+}
+
+// Tile height (16, 24 or 32 weight rows) and K slices (1, 2, 4 or 8 CTAs of a cluster) of the kernel for 17 to 64 rows,
+// from the matrix alone (never from M): the pair with the least estimated time, waves of CTAs (one CTA per SM) times a
+// CTA's work, its tile's RT x Ks products plus a fixed cost of meeting, reducing and finishing worth about 32 x 256 of
+// them; among equals the taller tile (it reads x less often), then fewer slices.  A slice keeps at least 192 of K.
+MLLM_EXPORT int mllm_linear_stream_f32_many_shape(int N, int K, int* rt, int* slices) {
+    const int sms = sm_count();
+    int best_rt = 32, best_s = 1;
+    long long best = -1;
+    for (int RT = 32; RT >= 16; RT -= 8)
+        for (int S = 1; S <= 8; S *= 2) {
+            if (S > 1 && K / S < 192) break;
+            const long long ctas = (long long)((N + RT - 1) / RT) * S;
+            const long long waves = (ctas + sms - 1) / sms;
+            const long long cost = waves * ((long long)RT * ((K + S - 1) / S) + 8192);
+            if (best < 0 || cost < best) best = cost, best_rt = RT, best_s = S;
+        }
+    *rt = best_rt;
+    *slices = best_s;
+    return 0;
 }
 
 MLLM_EXPORT int mllm_linear_stream_f32_bind_error(int* word) { return tc::bind_host_error(word); }
@@ -620,28 +566,26 @@ MLLM_EXPORT int mllm_linear_stream_f32(const void* x, long long ldx, const void*
                                      S, T, act, accumulate, ln, kv));
         return 0;
     }
-    int S = mllm_linear_stream_f32_slices(N, K);
-    int Ks = ((K + S - 1) / S + 3) / 4 * 4;
-    size_t smem = (size_t)R * Ks * 4 + (S > 1 ? (size_t)S * MAX_M * R * 4 : 0);
-    while (smem > 200 * 1024 && S < MAX_SLICES) {          // rows too long for shared memory: more slices
-        S *= 2;
-        Ks = ((K + S - 1) / S + 3) / 4 * 4;
-        smem = (size_t)R * Ks * 4 + (size_t)S * MAX_M * R * 4;
-    }
-    if (smem > 200 * 1024) return mllm_fail(1, "linear_stream_f32: K=%d is too long for shared memory", K);
-    const int tpw = M <= 32 ? 4 : 8;
-    using Kern = void (*)(const float*, long long, const float*, const float*, float*, long long, int, int, int, int,
-                          int, int, int, LnArgs, KvArgs);
-    Kern kern = nullptr;
-#define PICK(T, C)                                                                              \
-    if (tpw == T)                                                                               \
-        kern = kvw ? (Kern)linear_stream_f32_kernel<T, C, true> : (Kern)linear_stream_f32_kernel<T, C, false>;
-    PICK(4, 0) PICK(8, 0)
+    // 17 to 64 rows: tile height and K slices from (N, K) alone, so that the CTAs fill the SMs once as fully as possible
+    int RT = 32, S = 1;
+    mllm_linear_stream_f32_many_shape(N, K, &RT, &S);
+    const int Ks = ((K + S - 1) / S + 3) / 4 * 4;
+    const int MT = M <= 32 ? 32 : 64;
+    const size_t smem = ((size_t)RT * (Ks + MANY_WS_PAD) + (size_t)WARPS * MT * (RT + MANY_RED_PAD) +
+                         (S > 1 ? (size_t)(S - 1) * MT * RT : 0)) * 4;
+    if (smem > 220 * 1024) return mllm_fail(1, "linear_stream_f32: K=%d is too long for shared memory", K);
+    using Many = void (*)(const float*, long long, const float*, const float*, float*, long long, int, int, int, int, int,
+                          int, int, KvArgs);
+    Many kern = nullptr;
+#define PICK(I, J)                                                                                                   \
+    if (MT == 8 * I && RT == 4 * J)                                                                                  \
+        kern = kvw ? (Many)linear_stream_f32_many_kernel<I, J, true> : (Many)linear_stream_f32_many_kernel<I, J, false>;
+    PICK(4, 4) PICK(4, 6) PICK(4, 8) PICK(8, 4) PICK(8, 6) PICK(8, 8)
 #undef PICK
-    if (!kern) return mllm_fail(1, "linear_stream_f32: no kernel for M=%d", M);
+    if (!kern) return mllm_fail(1, "linear_stream_f32: no kernel for M=%d, %d rows per tile", M, RT);
     if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles * S);
+    cfg.gridDim = dim3((N + RT - 1) / RT * S);
     cfg.blockDim = dim3(WARPS * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -662,6 +606,6 @@ MLLM_EXPORT int mllm_linear_stream_f32(const void* x, long long ldx, const void*
     cfg.attrs = attr;
     cfg.numAttrs = na;
     MLLM_CUDA(cudaLaunchKernelEx(&cfg, kern, (const float*)x, ldx, (const float*)W, bias, (float*)out, ldo, M, N, K, Ks, S,
-                                 act, accumulate, ln, kv));
+                                 act, accumulate, kv));
     return 0;
 }

@@ -342,18 +342,35 @@ def decode_splits(max_ctx_len: int) -> int:
     return max(1, -(-int(max_ctx_len) // DECODE_SPLIT))
 
 
+_sm_count = None
+
+
+def sm_count() -> int:
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count \
+            if torch.cuda.is_available() else 148
+    return _sm_count
+
+
 def _small_m_wins(M: int, N: int, K: int) -> bool:
-    """Whether the weight-streaming kernel (mma.sync, K split over warps) beats the tensor-memory
-    kernel for M rows.  Measured on GPT-2 small's shapes in a replayed graph: the streaming
-    kernel's time grows with M*N (2.5-5 us up to 32 rows, 8-20 us at 48-64 rows, where it reads
-    its input rows from L2 again and again) while the other stays near its fixed cost of about
-    6 us per 768 of K; a matrix as tall as a vocabulary is streamed faster by the tensor-memory
-    kernel from 9 rows on."""
-    if M > 32:
-        return False
+    """Whether the weight-streaming kernel (mma.sync, 16 weight rows per CTA, K split over its warps) beats the
+    tensor-memory kernel for M rows of bfloat16.  Measured in replayed graphs at the shapes of GPT-2 small, medium
+    and XL (N = D, 3D, 4D and K = D, 4D for D = 768, 1024, 1600, and the 50,257-row head): up to 16 rows the
+    streaming kernel needs one pass of its token tiles and wins everywhere (2.3-12 us against 6-27 us), except
+    that a matrix as tall as a vocabulary is streamed faster by the tensor-memory kernel from 9 rows on; from 17
+    to 32 rows it makes two passes and still wins while its N/16 CTAs fit the SMs in one wave (N <= 2368 on 148
+    SMs: 4.4 against 5.7 us at N = 2304, 8.1 against 5.8 us at N = 3072); beyond 32 rows it loses everywhere (it
+    reads its input rows from L2 again and again while the other stays near its fixed cost)."""
+    if M <= 8:
+        return True
     if N >= 16384:
-        return M <= 8
-    return M * N <= 80_000
+        return False
+    if M <= 16:
+        return True
+    if M <= 32:
+        return -(-N // 16) <= sm_count()
+    return False
 
 
 def _fusable(weight, M, K) -> bool:
