@@ -96,18 +96,22 @@ template <> struct Exp<__nv_bfloat16> {
     }
 };
 
-// Keys and values of a split can be staged in shared memory when a split's rows fit there: bfloat16 with heads
-// up to 64.  The rows of one (page, head) are contiguous, so one thread brings each page's visible rows with one
+// Keys and values of a split can be staged in shared memory when a split's rows fit there: heads up to 64
+// (32 KB per CTA with a bfloat16 cache, 64 KB with a 32-bit one; dynamic shared memory).  The rows of one (page, head) are contiguous, so one thread brings each page's visible rows with one
 // bulk copy (cp.async.bulk onto an mbarrier): no thread computes an address per key, no register is held while
 // the rows fly, and six CTAs fit an SM instead of four.  That pays as soon as the grid is larger than about two
 // CTAs per SM; smaller grids keep the rows in registers, one hop less on the way.  The arithmetic is the same
 // either way.
 __device__ int g_decode_error = 0;                   // 1: a staged split never arrived (bounded wait ran out)
-template <typename T, int LPK> struct Staged { static constexpr bool value = sizeof(T) == 2 && LPK * Vec16<T>::N <= 64; };
+template <typename T, int LPK> struct Staged {
+    static constexpr bool value = LPK * Vec16<T>::N <= 64;                              // heads up to 64, either dtype
+    static constexpr int BYTES = 2 * SPLIT * LPK * 16;                                  // a split's keys and values
+    static constexpr int CTAS = BYTES <= 32 * 1024 ? 6 : 3;                             // resident CTAs per SM to aim for
+};
 
 // ONE: every CTA takes exactly one split.  STG: keys and values go through shared memory.
 template <typename T, int LPK, int MODE, bool ONE, bool STG>
-__global__ void __launch_bounds__(THREADS, STG ? 6 : 0)
+__global__ void __launch_bounds__(THREADS, STG ? Staged<T, LPK>::CTAS : 0)
 attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // written by kernels of this step: no __restrict__,
                    const T* v_pages,                                        // the compiler must not read them on the non-coherent path
                    const int* __restrict__ block_table, int bt_stride,
@@ -128,7 +132,7 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
     constexpr bool STAGE = STG;
     static_assert(!STG || Staged<T, LPK>::value, "a split's rows do not fit the staging area");
     __shared__ float sm_m[NG], sm_l[NG], sm_w[NG];
-    __shared__ __align__(16) uint4 s_stage[STAGE ? 2 * SPLIT * LPK : 1];   // a split's keys, then its values: [key][16-byte piece]
+    extern __shared__ __align__(16) uint4 s_stage[];          // STAGE: a split's keys, then its values: [key][16-byte piece]
     __shared__ float sm_o_own[STAGE ? 1 : NG * DH];
     float* sm_o = STAGE ? reinterpret_cast<float*>(s_stage) : sm_o_own;   // staged: the groups' outputs reuse the keys' space
     __shared__ float sm_res[(PUSH ? MAX_CLUSTER : MODE == MODE_SCRATCH || ONE ? 1 : MAX_SPC) * RES];
@@ -503,10 +507,13 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
     else if (one) PICK(MODE_SCRATCH, true);
     else PICK(MODE_SCRATCH, false);
 #undef PICK
+    const size_t smem = stg ? (size_t)Staged<T, LPK>::BYTES : 0;
+    if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (mode == MODE_CLUSTER) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -520,7 +527,7 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
         MLLM_CUDA(cudaLaunchKernelEx(&cfg, kern, ARGS));
         return 0;
     }
-    MLLM_CUDA(mllm_launch(kern, grid, dim3(THREADS), 0, stream, true, ARGS));
+    MLLM_CUDA(mllm_launch(kern, grid, dim3(THREADS), smem, stream, true, ARGS));
 #undef ARGS
     return 0;
 }
