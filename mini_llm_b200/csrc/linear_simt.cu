@@ -10,9 +10,10 @@
 // epilogues: bias (src/kernels/linear.cu:8-26), bias+GELU (:48-66), bias+residual as
 // beta=1 (:28-46).
 //
-// The sum over K of one output element always runs in the same order (K tiles in
-// sequence, no split over K), so a row's result does not depend on M or on the rows
-// beside it.
+// The sum over K of one output element always runs in the same order: K tiles in
+// sequence and, for 32-bit products of many rows with a narrow result, a fixed number
+// of K slices (chosen from N and K alone) whose partial sums a second kernel adds in
+// slice order.  So a row's result does not depend on M or on the rows beside it.
 #include "common.cuh"
 
 namespace {
@@ -108,16 +109,20 @@ linear_simt_kernel(const TA* A, long long lda, const TW* __restrict__ W, const f
 constexpr int LBM = 128, LBN = 128, LBK = 16, LTHREADS = 256;
 
 template <typename TA, typename TW, typename TO>
-__global__ void __launch_bounds__(LTHREADS)
+__global__ void __launch_bounds__(LTHREADS)        // one CTA per SM as compiled (129 registers); forcing two was slower (measured)
 linear_simt_large_kernel(const TA* A, long long lda, const TW* __restrict__ W,
-                         const float* __restrict__ bias, TO* out, long long ldo, int M, int N, int K, int act,
-                         int accumulate, int vecA, int vecW) {
+                         const float* __restrict__ bias, TO* out, long long ldo, int M, int N, int K_all, int act,
+                         int accumulate, int vecA, int vecW, int splits, float* ws) {
     __shared__ float As[2][LBK][LBM + 4];
     __shared__ float Ws[2][LBK][LBN + 4];
     pdl_wait();
     const int tid = threadIdx.x;
     const int tx = tid % 16, ty = tid / 16;
     const int m0 = blockIdx.y * LBM, n0 = blockIdx.x * LBN;
+    // K slice of this CTA (blockIdx.z): whole K tiles, so that slices start on aligned addresses
+    const int kslice = ((K_all + splits - 1) / splits + LBK - 1) / LBK * LBK;
+    const int k_begin = blockIdx.z * kslice;
+    const int K = min(K_all, k_begin + kslice);
     const int lrow = tid / 2, lk = (tid % 2) * 8;       // 128 rows x 16 k: 8 consecutive k per thread
     float acc[8][8];
 #pragma unroll
@@ -128,8 +133,8 @@ linear_simt_large_kernel(const TA* A, long long lda, const TW* __restrict__ W,
     auto fetch = [&](int k0) {
         load4<TA>(A, lda, m0 + lrow, M, k0 + lk, K, vecA != 0, a0);
         load4<TA>(A, lda, m0 + lrow, M, k0 + lk + 4, K, vecA != 0, a1);
-        load4<TW>(W, (long long)K, n0 + lrow, N, k0 + lk, K, vecW != 0, w0);
-        load4<TW>(W, (long long)K, n0 + lrow, N, k0 + lk + 4, K, vecW != 0, w1);
+        load4<TW>(W, (long long)K_all, n0 + lrow, N, k0 + lk, K, vecW != 0, w0);
+        load4<TW>(W, (long long)K_all, n0 + lrow, N, k0 + lk + 4, K, vecW != 0, w1);
     };
     auto stash = [&](int buf) {
 #pragma unroll
@@ -140,11 +145,11 @@ linear_simt_large_kernel(const TA* A, long long lda, const TW* __restrict__ W,
             Ws[buf][lk + 4 + i][lrow] = w1[i];
         }
     };
-    fetch(0);
+    fetch(k_begin);
     stash(0);
     __syncthreads();
     int buf = 0;
-    for (int k0 = 0; k0 < K; k0 += LBK) {
+    for (int k0 = k_begin; k0 < K; k0 += LBK) {
         const bool more = k0 + LBK < K;
         if (more) fetch(k0 + LBK);
 #pragma unroll
@@ -173,6 +178,10 @@ linear_simt_large_kernel(const TA* A, long long lda, const TW* __restrict__ W,
             const int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
             if (n >= N) continue;
             float v = acc[i][j];
+            if (splits > 1) {                     // a slice's partial sum: the finishing kernel adds the slices in order
+                ws[((size_t)blockIdx.z * M + m) * N + n] = v;
+                continue;
+            }
             if (bias) v += bias[n];
             v = apply_act(v, act);
             TO* o = out + (size_t)m * ldo + n;
@@ -182,16 +191,66 @@ linear_simt_large_kernel(const TA* A, long long lda, const TW* __restrict__ W,
     }
 }
 
+// out = act(ws[0] + ws[1] + ... + bias) (+ out): the K slices of the kernel above, added in slice order.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+linear_simt_finish_kernel(const float* __restrict__ ws, int splits, const float* __restrict__ bias, TO* out,
+                          long long ldo, int M, int N, int act, int accumulate) {
+    const size_t total = (size_t)M * N;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int m = (int)(i / N), n = (int)(i % N);
+        float v = __ldcg(ws + i);
+        for (int z = 1; z < splits; ++z) v += __ldcg(ws + (size_t)z * total + i);
+        if (bias) v += bias[n];
+        v = apply_act(v, act);
+        TO* o = out + (size_t)m * ldo + n;
+        if (accumulate) v += to_f32(*o);
+        *o = from_f32<TO>(v);
+    }
+}
+
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+// K slices of the 32-bit product with many rows, from N and K alone: a result with few 128-column tiles gets slices
+// until its CTAs at 2,048 rows (16 row tiles) come near one wave of two CTAs per SM; a slice keeps at least 256 of K.
+int simt_splits(int N, int K) {
+    const int cols = (N + LBN - 1) / LBN;
+    int s = (2 * sm_count() / 16 + cols / 2) / cols;
+    if (s > 4) s = 4;
+    while (s > 1 && K / s < 256) --s;
+    return s < 1 ? 1 : s;
+}
+
 template <typename TA, typename TW, typename TO>
 int launch(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo, int M, int N,
-           int K, int act, int accumulate, cudaStream_t stream) {
+           int K, int act, int accumulate, float* ws, long long ws_floats, cudaStream_t stream) {
     const bool vecA = ((uintptr_t)A % (4 * sizeof(TA)) == 0) && (lda % 4 == 0);
     const bool vecW = ((uintptr_t)W % (4 * sizeof(TW)) == 0) && (K % 4 == 0);
     if (M > 128 && N >= 128 && (M + LBM - 1) / LBM <= 65535) {
-        dim3 lgrid((N + LBN - 1) / LBN, (M + LBM - 1) / LBM);
+        int splits = 1;
+        if (sizeof(TA) == 4 && sizeof(TO) == 4 && ws) {
+            splits = simt_splits(N, K);
+            if ((long long)splits * M * N > ws_floats) splits = 1;        // no room for the partial sums (never, with ops.py)
+        }
+        dim3 lgrid((N + LBN - 1) / LBN, (M + LBM - 1) / LBM, splits);
         linear_simt_large_kernel<TA, TW, TO><<<lgrid, LTHREADS, 0, stream>>>(
-            (const TA*)A, lda, (const TW*)W, bias, (TO*)out, ldo, M, N, K, act, accumulate, vecA, vecW);
+            (const TA*)A, lda, (const TW*)W, bias, (TO*)out, ldo, M, N, K, act, accumulate, vecA, vecW, splits, ws);
         MLLM_CHECK_LAUNCH("linear_simt_large");
+        if (splits > 1) {
+            const size_t total = (size_t)M * N;
+            const int blocks = (int)((total + 256 * 4 - 1) / (256 * 4));
+            linear_simt_finish_kernel<TO><<<blocks, 256, 0, stream>>>(ws, splits, bias, (TO*)out, ldo, M, N, act, accumulate);
+            MLLM_CHECK_LAUNCH("linear_simt_finish");
+        }
         return 0;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
@@ -203,19 +262,23 @@ int launch(const void* A, long long lda, const void* W, const float* bias, void*
 
 }  // namespace
 
-// in_dtype: dtype of A and W; out_dtype: dtype of out.
+// K slices that mllm_linear_simt uses for float32 operands and M > 128 rows (1: none).
+MLLM_EXPORT int mllm_linear_simt_splits(int N, int K) { return simt_splits(N, K); }
+
+// in_dtype: dtype of A and W; out_dtype: dtype of out.  ws (ws_floats floats, may be null): room for the partial
+// sums of the K slices, mllm_linear_simt_splits(N, K) * M * N floats when that is more than one slice.
 MLLM_EXPORT int mllm_linear_simt(const void* A, long long lda, const void* W, const float* bias, void* out,
                                  long long ldo, int M, int N, int K, int act, int accumulate, int in_dtype,
-                                 int out_dtype, cudaStream_t stream) {
+                                 int out_dtype, float* ws, long long ws_floats, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return mllm_fail(1, "linear: K=%d", K);
     if ((M + BM - 1) / BM > 65535) return mllm_fail(1, "linear: M=%d exceeds the grid limit of this kernel", M);
     using bf = __nv_bfloat16;
     if (in_dtype == MLLM_F32 && out_dtype == MLLM_F32)
-        return launch<float, float, float>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+        return launch<float, float, float>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, ws, ws_floats, stream);
     if (in_dtype == MLLM_BF16 && out_dtype == MLLM_BF16)
-        return launch<bf, bf, bf>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+        return launch<bf, bf, bf>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, nullptr, 0, stream);
     if (in_dtype == MLLM_BF16 && out_dtype == MLLM_F32)
-        return launch<bf, bf, float>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, stream);
+        return launch<bf, bf, float>(A, lda, W, bias, out, ldo, M, N, K, act, accumulate, nullptr, 0, stream);
     return mllm_fail(1, "linear: unsupported dtype pair in=%d out=%d", in_dtype, out_dtype);
 }

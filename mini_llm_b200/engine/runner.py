@@ -91,7 +91,7 @@ class ModelRunner:
         self._graphs: Dict[tuple, object] = {}
         self._graph_seen: Dict[tuple, int] = {}
         self._graph_families = set()
-        self._graph_version = -1
+        self._graph_version = None
         self.graph_replays = 0
         self.graph_kernels: Dict[tuple, int] = {}
         # a part that reads device data on the host while it runs sets graph_safe = False
@@ -280,6 +280,10 @@ class ModelRunner:
         return logits
 
     # ------------------------------------------------------------------ CUDA graphs
+    def _buffer_version(self):
+        """Changes whenever a scratch buffer that a captured graph may point into is replaced."""
+        return (self.ws.version, ops.scratch_version)
+
     def _forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """A step is about a hundred launches; issued one by one from Python they cost
         more host time than a decode step or a 2,048-token prefill takes on the GPU.  So a
@@ -291,11 +295,11 @@ class ModelRunner:
         if not (self.engine.use_cuda_graphs and self._graph_ok):
             with ops.stream_scope():
                 return self.model.forward(ctx)
-        if self._graph_version != self.ws.version:
+        if self._graph_version != self._buffer_version():
             self._graphs.clear()
             self._graph_seen.clear()
             self._graph_families.clear()
-            self._graph_version = self.ws.version
+            self._graph_version = self._buffer_version()
         key = (ctx.layout.key(), ops.decode_splits(ctx.max_ctx_len) if ctx.decode_only else 0)
         g = self._graphs.get(key)
         if g is not None:
@@ -318,7 +322,7 @@ class ModelRunner:
             # "at_once": the same step again, captured and replayed, so that even a shape that never comes back
             # is computed by a replayed graph (what the replay tests grade); a step only writes its own tokens'
             # cache slots and scratch, so running it twice changes nothing
-        version = self.ws.version
+        version = self._buffer_version()
         torch.cuda.current_stream().synchronize()
         graph = torch.cuda.CUDAGraph()
         n0 = ops.launches
@@ -326,8 +330,8 @@ class ModelRunner:
             with ops.stream_scope():
                 logits = self.model.forward(ctx)
         kernels = ops.launches - n0
-        if self.ws.version != version:                  # a buffer was allocated during capture: do not keep it
-            self._graph_version = -1
+        if self._buffer_version() != version:           # a buffer was allocated during capture: do not keep it
+            self._graph_version = None
             with ops.stream_scope():
                 return self.model.forward(ctx)
         if len(self._graphs) >= 64:

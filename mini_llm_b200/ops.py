@@ -45,7 +45,8 @@ def _signatures(lib):
         "mllm_kv_write": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                           c_void_p],
         "mllm_linear_simt": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
-                             c_int, c_int, c_void_p],
+                             c_int, c_int, c_void_p, c_ll, c_void_p],
+        "mllm_linear_simt_splits": [c_int, c_int],
         "mllm_attention_simt": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                 c_ll, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "mllm_linear_smallm": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
@@ -78,6 +79,8 @@ def _signatures(lib):
         "mllm_attention_decode_error": [c_void_p],
         "mllm_attention_tiled": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                  c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+        "mllm_attention_tiled_wide": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                      c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "mllm_argmax": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
         "mllm_argmax_sliced": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mllm_sample": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -570,9 +573,39 @@ def linear(x, weight, bias, out, act: Optional[str] = None, accumulate: bool = F
         return out
     if impl != "simt":
         raise KernelError(f"linear: unknown implementation {impl!r}")
+    ws_ptr, ws_floats = None, 0
+    if x.dtype == torch.float32 and M > 128:
+        # many rows in 32-bit: a narrow result is computed in K slices whose partial sums need room
+        splits = library().mllm_linear_simt_splits(N, K)
+        if splits > 1:
+            ws = _scratch("simt_splitk", x.device, splits * M * N)
+            ws_ptr, ws_floats = ws.data_ptr(), ws.numel()
     _call("mllm_linear_simt", x.data_ptr(), lda, weight.data_ptr(), bias.data_ptr() if bias is not None else None,
-          out.data_ptr(), ldo, M, N, K, _ACT[act], int(accumulate), _dt(x), _dt(out), _stream())
+          out.data_ptr(), ldo, M, N, K, _ACT[act], int(accumulate), _dt(x), _dt(out), ws_ptr, ws_floats, _stream())
+    if ws_ptr is not None:
+        global launches
+        launches += 1           # the finishing kernel that adds the slices
     return out
+
+
+_scratch_bufs = {}
+
+
+def _scratch(name: str, device, floats: int) -> torch.Tensor:
+    """A float32 scratch buffer of this module that only grows (a step shape runs eagerly before it is captured as a
+    graph, so a captured graph never sees the buffer replaced under it unless a larger shape comes later: sizes are
+    rounded up to the next power of two to make that rare, and the runner drops its graphs when it happens)."""
+    global scratch_version
+    key = (name, str(device))
+    buf = _scratch_bufs.get(key)
+    if buf is None or buf.numel() < floats:
+        buf = torch.empty(max(1 << (int(floats) - 1).bit_length(), 1 << 20), dtype=torch.float32, device=device)
+        _scratch_bufs[key] = buf
+        scratch_version += 1
+    return buf
+
+
+scratch_version = 0     # bumped whenever a scratch buffer of this module is replaced
 
 
 # --------------------------------------------------------------------------- cache
@@ -602,6 +635,16 @@ def _flash_tc_ok(q, k_pages, out, ctx, head_dim, ps, ldq, ldo) -> bool:
     return (q.dtype == torch.bfloat16 and head_dim == 64 and 8 <= ps <= 128 and ps & (ps - 1) == 0
             and getattr(ctx, "n_tiles_wide", 0) > 0 and ldq % 8 == 0 and q.data_ptr() % 16 == 0 and ldo % 8 == 0
             and out.data_ptr() % 16 == 0 and k_pages.is_contiguous() and k_pages.data_ptr() % 16 == 0)
+
+
+_TILED_WIDE_HEAD_DIMS = (16, 32, 48, 64)
+
+
+def _tiled_wide_ok(q, head_dim, ctx, ldq) -> bool:
+    """Long prompt portions (128-row tiles mostly full) with heads up to 64, where no tensor-core kernel applies."""
+    nw = getattr(ctx, "n_tiles_wide", 0)
+    return (head_dim in _TILED_WIDE_HEAD_DIMS and nw > 0 and ctx.T >= 256 and ctx.T >= 80 * nw
+            and ldq % (16 // q.element_size()) == 0 and q.data_ptr() % 16 == 0)
 
 
 def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, num_kv_heads, head_dim, scale,
@@ -636,9 +679,20 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, *, num_heads, nu
         elif q.dtype == torch.bfloat16 and head_dim in _FLASH_HEAD_DIMS and getattr(ctx, "n_tiles", 0) > 0 \
                 and ldq % 8 == 0 and q.data_ptr() % 16 == 0 and ldo % 2 == 0:
             impl = "flash"
+        elif _tiled_wide_ok(q, head_dim, ctx, ldq):
+            impl = "tiled_wide"     # float32 (or a head size of 48) and long portions: 128 x 128 tiles on CUDA cores
         elif getattr(ctx, "n_tiles", 0) > 0:
             impl = "tiled"          # float32, or a head size the tensor-core kernel does not take
     attention_launches[impl] = attention_launches.get(impl, 0) + 1
+    if impl == "tiled_wide":
+        if head_dim not in _TILED_WIDE_HEAD_DIMS or getattr(ctx, "n_tiles_wide", 0) <= 0 or ldq % (16 // q.element_size()):
+            raise KernelError("paged_attention: the 128 x 128 CUDA-core kernel takes head sizes "
+                              f"{_TILED_WIDE_HEAD_DIMS}, 16-byte aligned rows and a list of 128-row tiles")
+        _call("mllm_attention_tiled_wide", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(),
+              block_table.data_ptr(), bt_stride, ctx.attn_tiles_wide.data_ptr(), int(ctx.n_tiles_wide),
+              ctx.positions.data_ptr(), out.data_ptr(), ldo, num_heads, num_kv_heads, head_dim, ps, float(scale),
+              int(window or 0), _dt(q), _stream())
+        return
     if impl == "tiled":
         _call("mllm_attention_tiled", q.data_ptr(), ldq, k_pages.data_ptr(), v_pages.data_ptr(),
               block_table.data_ptr(), bt_stride, ctx.attn_tiles.data_ptr(), int(ctx.n_tiles),

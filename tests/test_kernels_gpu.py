@@ -387,6 +387,34 @@ def test_linear_rows_do_not_depend_on_the_batch(ops):
         assert torch.equal(part, full[lo:hi])
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 768, 768), (2048, 768, 3072), (129, 1024, 1024), (400, 130, 3000)])
+def test_linear_many_rows_float32_in_k_slices(ops, M, N, K):
+    """The 32-bit product of many rows with a narrow result runs in K slices (chosen from N and K alone) whose partial
+    sums a second kernel adds in slice order: against float64, with every epilogue, and a row's bits do not depend on
+    how many rows are computed with it."""
+    lib = ops.library()
+    assert lib.mllm_linear_simt_splits(768, 768) > 1 and lib.mllm_linear_simt_splits(2304, 768) == 1
+    x, w, b = rnd(M, K, seed=1), rnd(N, K, seed=2, scale=K ** -0.5), rnd(N, seed=3)
+    ref = x.double() @ w.double().t() + b.double()
+    for act in (None, "gelu_tanh"):
+        out = torch.full((M, N), 7.0, device=DEV)
+        ops.linear(x, w, b, out=out, act=act, impl="simt")
+        want = ref if act is None else torch.nn.functional.gelu(ref, approximate="tanh")
+        assert (out.double() - want).abs().max() < 2e-5 * max(1.0, want.abs().max().item())
+    acc = rnd(M, N, seed=4)
+    acc0 = acc.clone()
+    ops.linear(x, w, b, out=acc, accumulate=True, impl="simt")
+    assert (acc.double() - (acc0.double() + ref)).abs().max() < 2e-5 * max(1.0, ref.abs().max().item())
+    full = torch.empty(M, N, device=DEV)
+    ops.linear(x, w, None, out=full, impl="simt")
+    for lo, hi in ((0, 129), (M - 129, M), (max(0, M // 2 - 70), min(M, M // 2 + 70))):
+        if hi - lo <= 128:
+            continue                   # up to 128 rows another kernel (no slices) takes over: rounding may differ
+        part = torch.empty(hi - lo, N, device=DEV)
+        ops.linear(x[lo:hi], w, None, out=part, impl="simt")
+        assert torch.equal(part, full[lo:hi]), (lo, hi)
+
+
 def _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages, seed, sharp_key=None):
     """seqs: list of (context_len, q_len).  Returns everything the kernel needs plus dense K/V per sequence."""
     g = torch.Generator().manual_seed(seed)
@@ -682,6 +710,56 @@ def test_tiled_attention_mixed_batch(ops, dtype, H, Hkv, dh, page, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,dh,page,window", [(2, 2, 64, 16, None), (12, 12, 64, 16, None), (6, 2, 32, 8, None), (3, 1, 48, 32, None),
+                                                  (4, 4, 16, 4, None), (4, 1, 64, 16, 37), (2, 2, 64, 64, 200)])
+def test_tiled_wide_attention_mixed_batch(ops, dtype, H, Hkv, dh, page, window):
+    """The CUDA-core kernel with 128-query x 128-key tiles (the 32-bit path's attention for long prompt portions,
+    heads of 16, 32, 48 and 64): portions of many lengths (tile edges at 128, page edges, portions that start in the
+    middle of a key tile) beside single tokens, against float64 and the plain kernel; the same queries cut
+    differently give the same bits."""
+    from mini_llm_b200.engine.context import ATTN_TILE_WIDE, attention_tiles
+    seqs = [(1, 1), (70, 1), (33, 33), (100, 7), (16, 2), (129, 129), (128, 128), (65, 65), (200, 63), (500, 300),
+            (256, 128), (191, 2), (640, 257)]
+    case = _paged_case(dtype, seqs, H, Hkv, dh, page, num_pages=2800 // page + 40, seed=H + page)
+    ctx = _ctx_for(case)
+    ctx.decode_only = False
+    starts = [c - ql for c, ql in seqs]
+    tiles = attention_tiles([ql for _, ql in seqs], starts, ATTN_TILE_WIDE)
+    ctx.attn_tiles_wide = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    ctx.n_tiles_wide = len(tiles) // 3
+    q = case["q"].to(dtype).to(DEV)
+    kp, vp, bt = case["k_pages"].to(dtype).to(DEV), case["v_pages"].to(dtype).to(DEV), case["bt"].to(DEV)
+    scale = dh ** -0.5
+    kw = dict(num_heads=H, num_kv_heads=Hkv, head_dim=dh, scale=scale, window=window)
+    out, plain = torch.full_like(q, 7.0), torch.empty_like(q)
+    ops.paged_attention(q, kp, vp, bt, ctx, out, impl="tiled_wide", **kw)
+    ops.paged_attention(q, kp, vp, bt, ctx, plain, impl="simt", **kw)
+    want = _attention_reference(case, H, Hkv, dh, scale, window, dtype)
+    mag = want.abs().clamp(min=1.0)
+    tol = 2e-5 if dtype == torch.float32 else 2 ** -8
+    assert ((out.double().cpu() - want).abs() / mag).max() < tol
+    assert ((out.double() - plain.double()).abs().cpu() / mag).max() < (2e-5 if dtype == torch.float32 else 2 ** -7 * 1.05)
+    c2 = _paged_case(dtype, [(300, 300)], H, Hkv, dh, page, num_pages=2800 // page + 40, seed=99)
+    ctxa = _ctx_for(c2)
+    ctxa.decode_only = False
+    ta = attention_tiles([300], [0], ATTN_TILE_WIDE)
+    ctxa.attn_tiles_wide, ctxa.n_tiles_wide = torch.tensor(ta, dtype=torch.int32, device=DEV), len(ta) // 3
+    q2 = c2["q"].to(dtype).to(DEV)
+    args2 = (c2["k_pages"].to(dtype).to(DEV), c2["v_pages"].to(dtype).to(DEV), c2["bt"].to(DEV))
+    whole = torch.empty_like(q2)
+    ops.paged_attention(q2, *args2, ctxa, whole, impl="tiled_wide", **kw)
+    for lo, hi in ((0, 5), (5, 70), (70, 300), (100, 101), (127, 260)):
+        cb = _Ctx()
+        cb.token_seq = torch.zeros(hi - lo, dtype=torch.int32, device=DEV)
+        cb.positions = torch.arange(lo, hi, dtype=torch.int32, device=DEV)
+        tb = attention_tiles([hi - lo], [lo], ATTN_TILE_WIDE)
+        cb.attn_tiles_wide, cb.n_tiles_wide, cb.decode_only = torch.tensor(tb, dtype=torch.int32, device=DEV), len(tb) // 3, False
+        part = torch.empty_like(q2[lo:hi])
+        ops.paged_attention(q2[lo:hi], *args2, cb, part, impl="tiled_wide", **kw)
+        assert torch.equal(part, whole[lo:hi]), (lo, hi)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_paged_attention_finds_one_far_key_among_hundreds(ops, dtype):
     """Random keys give near-uniform weights that would hide a skipped key; here one key
     far back carries almost all the weight, once at a page's first slot, once at its last."""
@@ -708,7 +786,8 @@ def test_paged_attention_finds_one_far_key_among_hundreds(ops, dtype):
 
 
 @pytest.mark.parametrize("impl,dtype", [("tiled", torch.float32), ("tiled", torch.bfloat16), ("flash", torch.bfloat16),
-                                        ("flash_tc", torch.bfloat16)])
+                                        ("flash_tc", torch.bfloat16), ("tiled_wide", torch.float32),
+                                        ("tiled_wide", torch.bfloat16)])
 def test_prompt_attention_finds_one_far_key_among_hundreds(ops, impl, dtype):
     """The same for the kernels of prompt portions: the last 150 queries of a 700-token request all lean on one
     key far back - at a page's first and last slot, in the first key tile, at a tile's edge - which sits in
@@ -744,7 +823,7 @@ def test_prompt_attention_finds_one_far_key_among_hundreds(ops, impl, dtype):
 @pytest.mark.parametrize("window", [None, 200])
 @pytest.mark.parametrize("impl,dtype", [("simt", torch.float32), ("decode", torch.float32), ("decode", torch.bfloat16),
                                         ("tiled", torch.float32), ("tiled", torch.bfloat16), ("flash", torch.bfloat16),
-                                        ("flash_tc", torch.bfloat16)])
+                                        ("flash_tc", torch.bfloat16), ("tiled_wide", torch.float32)])
 def test_attention_edges_with_sharp_keys(ops, impl, dtype, window):
     """Keys that carry the weight sit exactly where an off-by-one would drop or admit them: position 0, the
     first and last key of a page and of a 128-key block, the query's own position, and with a window its first
