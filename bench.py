@@ -18,7 +18,8 @@ with ``bf16_`` in every key.  ``--dtype bfloat16`` swaps the two.  It prints ONE
               can exceed the W asked for), so the timed steps replay captured graphs; a K
               beyond the 512 positions a request has left is cut to 512;
   e2e         the same through the Python entry point (LLM.step): host token ids in,
-              sampled ids back on the host every step;
+              sampled ids back on the host every step (wall clock around K steps, the
+              median of three such runs, since K steps may be only a millisecond);
   prefill     2,048 prompt tokens (2 x 1024) in one step: tokens/s, ms, and the share of
               the peak for its dtype that its flops reach (bfloat16: the measured cuBLAS
               rate; float32: the CUDA cores' nominal FFMA rate, SMs x 128 x 2 x clock);
@@ -242,17 +243,20 @@ def run_e2e(model_dir, dtype, batch, steps, warmup):
     prompts_in()
     while llm.has_unfinished():
         llm.step()
-    first = prompts_in()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    produced = 0
-    while llm.has_unfinished():
-        produced += len(llm.step())
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
-    produced -= batch - first                  # tokens of the prompts' step that were only handed back inside the clock
+    rates = []
+    for _ in range(3):                         # K steps are a millisecond or so of wall clock: the median of three runs
+        first = prompts_in()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        produced = 0
+        while llm.has_unfinished():
+            produced += len(llm.step())
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        produced -= batch - first              # tokens of the prompts' step that were only handed back inside the clock
+        rates.append(produced / dt)
     lay = llm.runner._last_layout_total if hasattr(llm.runner, "_last_layout_total") else None
-    res = dict(tok_s=produced / dt, h2d=(lay or 0) * 4, d2h=batch * 4, tokens=produced)
+    res = dict(tok_s=sorted(rates)[1], h2d=(lay or 0) * 4, d2h=batch * 4, tokens=produced)
     del llm
     torch.cuda.empty_cache()
     return res
