@@ -7,7 +7,10 @@ Here the same line format is read from --prompt-ids, --prompts-file or standard
 input, and the constants are options named after them: --max-new-tokens
 (DEFAULT_MAX_NEW_TOKENS 8), --kv-block-size (DEFAULT_KV_BLOCK_SIZE 16),
 --total-kv-blocks (DEFAULT_TOTAL_KV_BLOCKS 4096), --max-batch-num (MAX_BATCH_NUM 16)
-(include/constants.h:14-26).
+(include/constants.h:14-26).  --metrics prints the serving figures of the reference's offline bench
+(benchmarks/serving/offline_gpt2_wmma_bench.cu:624-640: TTFT, TPOT and end-to-end latency with
+percentiles), --profile writes a per-kernel CSV in the manner of its stage timer
+(include/profiling/stage_timer.cuh:40-101).
 """
 from __future__ import annotations
 
@@ -49,6 +52,12 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--prompts-file", help="one request per line of token ids ('-' = standard input)")
     ap.add_argument("--stream", action="store_true", help="print every token as it is produced: '<request> <id>'")
     ap.add_argument("--stats", action="store_true", help="print scheduler counters to standard error")
+    ap.add_argument("--metrics", action="store_true",
+                    help="print serving metrics to standard error as 'name,value' lines: requests, tokens per second, "
+                         "time to first token, time per output token and end-to-end latency (mean, p50, p90, p95, p99)")
+    ap.add_argument("--profile", metavar="CSV",
+                    help="time every kernel launch with CUDA events (CUDA graphs off) and write "
+                         "'step,kind,batch_size,total_tokens,stage,launches,ms' rows, one per kernel entry point and step")
     return ap
 
 
@@ -84,7 +93,10 @@ def main(argv=None) -> int:
             return 0
     llm = LLM(model_dir, dtype=args.dtype, page_size=args.page_size, num_pages=args.num_pages,
               max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
-              prefill_chunk=args.prefill_chunk, admission=args.admission)
+              prefill_chunk=args.prefill_chunk, admission=args.admission,
+              **({"use_cuda_graphs": False, "async_scheduling": False} if args.profile else {}))
+    if args.profile:
+        llm.profile = []
     sp = SamplingParams(temperature=args.temperature, seed=args.sample_seed, max_new_tokens=args.max_new_tokens,
                         ignore_eos=args.ignore_eos)
     ids = [llm.add_request(p, sp) for p in prompts]
@@ -99,6 +111,14 @@ def main(argv=None) -> int:
             print(" ".join(str(t) for t in outs[i]) + " [DONE]")
     if args.stats:
         print(json.dumps(vars(llm.scheduler.stats)), file=sys.stderr)
+    if args.metrics:
+        for k, v in llm.metrics.summary().items():
+            print(f"{k},{v:.6f}" if isinstance(v, float) else f"{k},{v}", file=sys.stderr)
+    if args.profile:
+        with open(args.profile, "w") as f:
+            f.write("step,kind,batch_size,total_tokens,stage,launches,ms\n")
+            for step, kind, reqs, toks, stage, n, ms in llm.profile:
+                f.write(f"{step},{kind},{reqs},{toks},{stage},{n},{ms:.4f}\n")
     if tmp is not None:
         tmp.cleanup()
     return 0

@@ -12,6 +12,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Union
 from ..config.base import EngineConfig
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
+from .metrics import ServingMetrics
 from .request import Request, Response
 from .runner import ModelRunner, StepEntry
 from .scheduler import PENDING, Scheduler
@@ -32,6 +33,10 @@ class LLM:
         self._next_id = 0
         self._inflight = None          # (advanced step, sampler ticket, request id -> row) of a step whose tokens are not read yet
         self._held: List[Response] = []     # responses read while aborting, handed out by the next step()
+        self.metrics = ServingMetrics()      # arrival, first and last token of every request (host clock)
+        self.profile = None                  # a list: step() then times every launch and appends a row per kernel
+        self._profile_steps = 0
+        self._last_step_shape = None
 
     # ------------------------------------------------------------------ low level
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -43,6 +48,7 @@ class LLM:
             if not (0 <= int(t) < self.runner.vocab_size):
                 raise ValueError(f"token id {t} is outside the vocabulary of {self.runner.vocab_size}")
         self.scheduler.add(Request(request_id, list(prompt), params or SamplingParams()))
+        self.metrics.arrived(request_id, len(prompt))
         return request_id
 
     def abort(self, request_id: Hashable) -> bool:
@@ -66,6 +72,34 @@ class LLM:
         every other situation (prompts waiting or running, pages short) the tokens are read
         first and a call returns the tokens of its own step, as with
         ``async_scheduling=False``."""
+        if self.profile is not None:
+            return self._profiled_step()
+        out = self._step()
+        if out:
+            now = self.metrics.clock()
+            for r in out:
+                self.metrics.token(r.request_id, r.finished, now)
+        return out
+
+    def _profiled_step(self) -> List[Response]:
+        """One step with every launch timed by CUDA events (needs use_cuda_graphs=False): appends
+        (step, kind, requests, tokens, entry point, launches, ms) per kernel entry point to ``self.profile``, the columns
+        of the reference's stage timer (include/profiling/stage_timer.cuh:40-101) with the kernel as the stage."""
+        from .. import ops
+        self._last_step_shape = None
+        with ops.time_launches() as tl:
+            out = self._step()
+        if self._last_step_shape is not None:         # something was launched
+            kind, reqs, toks = self._last_step_shape
+            for name, n, ms in tl.rows():
+                self.profile.append((self._profile_steps, kind, reqs, toks, name.replace("mllm_", ""), n, ms))
+            self._profile_steps += 1
+        now = self.metrics.clock()
+        for r in out:
+            self.metrics.token(r.request_id, r.finished, now)
+        return out
+
+    def _step(self) -> List[Response]:
         out: List[Response] = self._held
         self._held = []
         ahead = self.engine_config.async_scheduling and self.scheduler.can_run_ahead()
@@ -76,6 +110,10 @@ class LLM:
         if sched.entries:
             rows = self._inflight[2] if self._inflight is not None else {}
             entries = []
+            n_tok = sum(len(e.tokens) for e in sched.entries)
+            self._last_step_shape = ("decode" if n_tok == len(sched.entries) else
+                                     "prefill" if not any(e.is_decode for e in sched.entries) else "mixed",
+                                     len(sched.entries), n_tok)
             for e in sched.entries:
                 toks = e.tokens
                 if e.is_decode and toks[0] == PENDING:

@@ -218,6 +218,37 @@ def test_command_line(setup, tmp_path):
     assert got == want
 
 
+def test_command_line_metrics_and_profile(setup, tmp_path):
+    """--metrics prints the serving figures as name,value lines; --profile writes one CSV row per step and kernel entry
+    point, timed with CUDA events, and the tokens are the ones of an unprofiled run."""
+    cfg, dtype = setup["cfg"], setup["dtype"]
+    p1, p2 = random_ids(20, cfg["vocab_size"], 3), random_ids(7, cfg["vocab_size"], 4)
+    f = tmp_path / "prompts.txt"
+    f.write_text(" ".join(map(str, p1)) + "\n" + " ".join(map(str, p2)) + "\n")
+    csv_path = tmp_path / "profile.csv"
+    base = [sys.executable, os.path.join(ROOT, "bin", "mini_llm"), "--model", setup["dir"], "--dtype", dtype,
+            "--kv-block-size", str(setup["page"]), "--total-kv-blocks", "64", "--max-new-tokens", "6", "--ignore-eos",
+            "--prompts-file", str(f)]
+    plain = subprocess.run(base, capture_output=True, text=True, timeout=600)
+    r = subprocess.run(base + ["--metrics", "--profile", str(csv_path)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout == plain.stdout
+    m = dict(line.split(",") for line in r.stderr.splitlines() if line.count(",") == 1 and not line.startswith("["))
+    assert int(m["completed"]) == 2 and float(m["out_tok_per_s"]) > 0
+    for name in ("ttft", "tpot", "e2e"):
+        assert float(m[f"{name}_mean_ms"]) > 0 and float(m[f"{name}_p50_ms"]) <= float(m[f"{name}_p99_ms"])
+    assert float(m["ttft_mean_ms"]) <= float(m["e2e_mean_ms"])
+    rows = [l.split(",") for l in csv_path.read_text().splitlines()]
+    assert rows[0] == ["step", "kind", "batch_size", "total_tokens", "stage", "launches", "ms"]
+    body = rows[1:]
+    steps = sorted({int(r_[0]) for r_ in body})
+    assert steps == list(range(len(steps))) and len(steps) == 6          # one step for both prompts, five decode steps
+    assert body[0][1] == "prefill" and body[0][2:4] == ["2", "27"] and body[-1][1] == "decode" and body[-1][2:4] == ["2", "2"]
+    stages = {r_[4] for r_ in body}
+    assert "embed" in stages and any(s_.startswith("attention") for s_ in stages) and any(s_.startswith("linear") for s_ in stages)
+    assert all(float(r_[6]) > 0 and int(r_[5]) >= 1 for r_ in body)
+
+
 def test_few_near_ties_had_to_be_forgiven():
     """The tests above accept a token that differs from the plain choice only where that choice was a near-tie.
     All generated tokens were compared (each on the engine's own prefix); here the share of forgiven ones is
