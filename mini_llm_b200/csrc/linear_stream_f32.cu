@@ -469,6 +469,11 @@ MLLM_EXPORT int mllm_linear_stream_f32_slices(int N, int K) {
     return S;
 }
 
+constexpr size_t MANY_SMEM_LIMIT = 200 * 1024;
+size_t many_smem_bytes(int RT, int Ks, int S, int MT) {
+    return ((size_t)RT * (Ks + MANY_WS_PAD) + (size_t)WARPS * MT * (RT + MANY_RED_PAD) + (S > 1 ? (size_t)(S - 1) * MT * RT : 0)) * 4;
+}
+
 // Tile height (16, 24 or 32 weight rows) and K slices (1, 2, 4 or 8 CTAs of a cluster) of the kernel for 17 to 64 rows,
 // from the matrix alone (never from M): the pair with the least estimated time, waves of CTAs (one CTA per SM) times a
 // CTA's work, its tile's RT x Ks products plus a fixed cost of meeting, reducing and finishing worth about 32 x 256 of
@@ -480,14 +485,16 @@ MLLM_EXPORT int mllm_linear_stream_f32_many_shape(int N, int K, int* rt, int* sl
     for (int RT = 32; RT >= 16; RT -= 8)
         for (int S = 1; S <= 8; S *= 2) {
             if (S > 1 && K / S < 192) break;
+            const long long ks = ((K + S - 1) / S + 3) / 4 * 4;
+            if (many_smem_bytes(RT, (int)ks, S, MAX_M) > MANY_SMEM_LIMIT) continue;     // (for 64 rows: the choice must not depend on M)
             const long long ctas = (long long)((N + RT - 1) / RT) * S;
             const long long waves = (ctas + sms - 1) / sms;
-            const long long cost = waves * ((long long)RT * ((K + S - 1) / S) + 8192);
+            const long long cost = waves * ((long long)RT * ks + 8192);
             if (best < 0 || cost < best) best = cost, best_rt = RT, best_s = S;
         }
     *rt = best_rt;
     *slices = best_s;
-    return 0;
+    return best < 0 ? 1 : 0;        // 1: no shape fits shared memory (K beyond about 48,000): the caller takes another kernel
 }
 
 MLLM_EXPORT int mllm_linear_stream_f32_bind_error(int* word) { return tc::bind_host_error(word); }
@@ -568,12 +575,11 @@ MLLM_EXPORT int mllm_linear_stream_f32(const void* x, long long ldx, const void*
     }
     // 17 to 64 rows: tile height and K slices from (N, K) alone, so that the CTAs fill the SMs once as fully as possible
     int RT = 32, S = 1;
-    mllm_linear_stream_f32_many_shape(N, K, &RT, &S);
+    if (mllm_linear_stream_f32_many_shape(N, K, &RT, &S))
+        return mllm_fail(1, "linear_stream_f32: K=%d is too long for shared memory", K);
     const int Ks = ((K + S - 1) / S + 3) / 4 * 4;
     const int MT = M <= 32 ? 32 : 64;
-    const size_t smem = ((size_t)RT * (Ks + MANY_WS_PAD) + (size_t)WARPS * MT * (RT + MANY_RED_PAD) +
-                         (S > 1 ? (size_t)(S - 1) * MT * RT : 0)) * 4;
-    if (smem > 220 * 1024) return mllm_fail(1, "linear_stream_f32: K=%d is too long for shared memory", K);
+    const size_t smem = many_smem_bytes(RT, Ks, S, MT);
     using Many = void (*)(const float*, long long, const float*, const float*, float*, long long, int, int, int, int, int,
                           int, int, KvArgs);
     Many kern = nullptr;

@@ -411,8 +411,12 @@ def _linear_fused(x, weight, bias, out, act, accumulate, norm: Optional[NormedIn
           out.data_ptr(), ldo, M, N, K, _ACT[act], int(accumulate), _dt(out), *nargs, *kargs, _stream())
 
 
+STREAM_F32_MAX_K = 12288      # the longest rows whose tiles fit the streaming product's shared memory in every case
+
+
 def _stream_f32_ok(weight, M, K) -> bool:
-    return weight.dtype == torch.float32 and M <= SMALL_M_F32 and K % 4 == 0 and weight.data_ptr() % 16 == 0
+    return (weight.dtype == torch.float32 and M <= SMALL_M_F32 and K % 4 == 0 and K <= STREAM_F32_MAX_K
+            and weight.data_ptr() % 16 == 0)
 
 
 def _norm_ok_f32(n: NormedInput) -> bool:
@@ -560,8 +564,8 @@ def linear(x, weight, bias, out, act: Optional[str] = None, accumulate: bool = F
         if x.dtype == torch.bfloat16 and K % 8 == 0 and lda % 8 == 0 \
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
             impl = "smallm" if _small_m_wins(M, N, K) else "tcgen05"
-        elif x.dtype == torch.float32 and out.dtype == torch.float32 and M <= SMALL_M_F32 and K % 4 == 0 \
-                and lda % 4 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
+        elif x.dtype == torch.float32 and out.dtype == torch.float32 and _stream_f32_ok(weight, M, K) \
+                and lda % 4 == 0 and x.data_ptr() % 16 == 0:
             impl = "stream_f32"
     if impl == "stream_f32":
         _linear_stream_f32(x, weight, bias, out, act, accumulate, None, None)

@@ -253,7 +253,8 @@ def test_linear_small_m_rows_do_not_depend_on_the_batch(ops):
 
 @pytest.mark.parametrize("M,N,K", [(1, 768, 768), (8, 2304, 768), (3, 50, 40), (16, 1003, 96), (5, 320, 3072), (13, 50257, 64),
                                    (17, 768, 3072), (40, 4800, 1600), (64, 768, 768), (64, 100, 6400), (33, 2304, 768),
-                                   (9, 7, 12), (2, 1600, 6400)])
+                                   (9, 7, 12), (2, 1600, 6400), (64, 1024, 4096), (33, 1600, 6400), (48, 6400, 1600),
+                                   (20, 50257, 1024), (64, 130, 12000)])
 def test_linear_stream_float32(ops, M, N, K):
     """The 32-bit weight-streaming product (weights by bulk copy into shared memory, warps own tokens, K slices
     of narrow matrices shared by a cluster) beside float64, at 1 to 64 rows."""
