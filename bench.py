@@ -274,7 +274,8 @@ def run_prefill(model_dir, dtype, iters=5, warmup=3):
                        max_num_batched_tokens=PREFILL_TOKENS)
     runner = ModelRunner(model_dir, eng)
     g = torch.Generator().manual_seed(99)
-    prompts = [torch.randint(0, cfg["vocab_size"], (l,), generator=g).tolist() for l in lens]
+    # the prompts are host arrays of token ids (int32), as a tokenizer hands them over
+    prompts = [torch.randint(0, cfg["vocab_size"], (l,), generator=g).to(torch.int32).numpy() for l in lens]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=runner.device)
     times = []
     for it in range(warmup + iters):

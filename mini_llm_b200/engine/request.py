@@ -6,6 +6,8 @@ import enum
 from dataclasses import dataclass, field
 from typing import Hashable, List, Optional
 
+import numpy as np
+
 from ..sampling.params import SamplingParams
 
 
@@ -36,6 +38,15 @@ class Request:
         self.tokens = [int(t) for t in self.tokens]
         if not self.prompts_len:
             self.prompts_len = len(self.tokens)
+        self._array = np.asarray(self.tokens, dtype=np.int32)      # the tokens known at admission, for prompt portions
+
+    def portion(self, start: int, stop: int):
+        """tokens[start:stop] as an int32 array: a view of an array made once, so that cutting a prompt into portions
+        costs no conversion per step (a list of a thousand Python ints takes longer to convert than the step's other
+        host work together).  After a preemption the array is rebuilt from the list, which has grown by then."""
+        if stop > self._array.shape[0]:
+            self._array = np.asarray(self.tokens[:stop] if stop == len(self.tokens) else self.tokens, dtype=np.int32)
+        return self._array[start:stop]
 
     @property
     def max_new_tokens(self) -> int:

@@ -213,7 +213,7 @@ class Scheduler:
             return 0
         if not self.cache.reserve(req.request_id, n):
             return 0
-        toks = req.tokens[req.num_computed:req.num_computed + n]
+        toks = req.portion(req.num_computed, req.num_computed + n)
         step.entries.append(ScheduledEntry(req, toks, n == left, False))
         return n
 

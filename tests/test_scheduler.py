@@ -37,7 +37,7 @@ def run(sched, cm, max_steps=10000, on_step=None):
         assert len(ids) == len(set(ids))
         for e in st.entries:                       # tokens fed are exactly the next ones not yet in the cache
             r = e.request
-            assert e.tokens == r.tokens[r.num_computed:r.num_computed + len(e.tokens)]
+            assert list(e.tokens) == r.tokens[r.num_computed:r.num_computed + len(e.tokens)]
             assert cm.computed(r.request_id) == r.num_computed
             assert len(cm.table(r.request_id, 0)) * cm.page_size >= r.num_computed + len(e.tokens)
         if on_step:
