@@ -16,8 +16,11 @@
 // in warp order, then across the slices in rank order.  17 to 64 rows (`many`): every warp takes whole
 // tokens (warp w the tokens w, w + 8, ...), its lanes split K, and the weights are read from shared memory
 // once per warp, which 8 tokens per warp amortise.
-// A token's sum runs over k in an order that depends on K and on the slices only, never on M, so a
-// token's result does not change with the batch (`few` and `many` differ in rounding, as two kernels do).
+// A matrix as tall as a vocabulary (`tall`, at least 8 tiles of 32 rows per SM) has a kernel of its own that
+// stays on its SM: x in shared memory once, a warp's 4 weight rows in registers straight from HBM, no barrier
+// in its loop; it takes all the rows of x that fit shared memory (64 at K = 768).
+// A token's sum runs over k in an order that depends on N, K and on the slices only, never on M, so a
+// token's result does not change with the batch (`few`, `many` and `tall` differ in rounding, as kernels do).
 //
 // Fused on the input (up to 16 rows, no K slices): LayerNorm of the 32-bit residual rows, optionally
 // gathered by `rows`; a warp per token computes mean and variance in two passes from registers, as the
@@ -447,6 +450,162 @@ linear_stream_f32_many_kernel(const float* x, long long ldx, const float* __rest
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Up to 64 rows (as many as fit shared memory) against a matrix with very many rows (a vocabulary): one CTA per SM stays and walks tiles of 32
+// weight rows (16 when K is over 1024); a warp owns 4 (2) rows of the tile and all of K, its lanes split K in float4 steps of 128.  The (normalised)
+// rows of x are put into shared memory once per CTA; the weights come straight from HBM into registers, 4 rows x K in
+// flight per warp, the first tile's before the kernel waits for its predecessor.  A value of x read from shared memory
+// meets 4 weight rows (16 multiply-adds per 16-byte read, which keeps shared memory off the critical path), and the
+// 32 sums of a lane meet inside the warp by the halving butterfly, after which lane 8r + m holds row r, token m: no
+// barrier and no shared memory in the loop.  Per tile that is a third of the instructions of the kernel above, which
+// at 50,257 rows is bound by its instructions, not by HBM.
+template <int KP, int RW, bool LN>     // KP: float4 steps of K per lane (K <= KP * 128); RW: weight rows of a warp (4 or 2)
+__global__ void __launch_bounds__(WARPS * 32, 1)
+linear_stream_f32_tall_kernel(const float* x, long long ldx, const float* __restrict__ W, const float* __restrict__ bias,
+                              float* out, long long ldo, int M, int N, int K, int act, int accumulate, LnArgs ln) {
+    extern __shared__ __align__(16) float xs[];             // [M up to a multiple of 8][K up to a multiple of 128]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    constexpr int TR = WARPS * RW, V = RW * 8;             // rows of a tile; sums of a lane
+    const int tiles = (N + TR - 1) / TR;
+    float4 w[RW][KP];
+    auto load_w = [&](int tile) {
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+            const int n = tile * TR + warp * RW + r;
+            const float* row = W + (size_t)(n < N ? n : 0) * K;
+#pragma unroll
+            for (int c = 0; c < KP; ++c) {
+                const int k = c * 128 + lane * 4;
+                w[r][c] = (k < K && n < N) ? __ldcs(reinterpret_cast<const float4*>(row + k)) : zero4;
+            }
+        }
+    };
+    int tile = blockIdx.x;
+    if (tile < tiles) load_w(tile);          // weights depend on no kernel of the step
+    pdl_wait();
+    pdl_launch();
+    const int KS = (K + 127) / 128 * 128;                   // a row of x in shared memory, its tail beyond K zero
+    const int passes = (M + 7) / 8;
+    for (int m = warp; m < passes * 8; m += WARPS) {   // a warp stages tokens warp, warp + 8, ... (normalised if asked for); rows beyond M are zero
+        if (m >= M) {
+#pragma unroll
+            for (int c = 0; c < KP; ++c)
+                if (c * 128 < K) *reinterpret_cast<float4*>(xs + (size_t)m * KS + c * 128 + lane * 4) = zero4;
+            continue;
+        }
+        float4 rv[KP];
+        const float* xbase = LN ? ln.x : x;
+        const float* row = xbase + (size_t)((LN && ln.rows) ? __ldcg(ln.rows + m) : m) * ldx;
+#pragma unroll
+        for (int c = 0; c < KP; ++c) {
+            const int k = c * 128 + lane * 4;
+            rv[c] = k < K ? __ldcg(reinterpret_cast<const float4*>(row + k)) : zero4;
+        }
+        if constexpr (LN) {
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < KP; ++c) sum += (rv[c].x + rv[c].y) + (rv[c].z + rv[c].w);
+            const float mean = warp_sum(sum) / (float)K;
+            float var = 0.f;
+#pragma unroll
+            for (int c = 0; c < KP; ++c) {
+                if (c * 128 + lane * 4 < K) {
+                    const float a = rv[c].x - mean, b = rv[c].y - mean, cc = rv[c].z - mean, d = rv[c].w - mean;
+                    var += (a * a + b * b) + (cc * cc + d * d);
+                }
+            }
+            const float rstd = rsqrtf(warp_sum(var) / (float)K + ln.eps);
+#pragma unroll
+            for (int c = 0; c < KP; ++c) {
+                const int k = c * 128 + lane * 4;
+                if (k < K) {
+                    const float4 g = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
+                    const float4 b = __ldg(reinterpret_cast<const float4*>(ln.beta + k));
+                    rv[c].x = (rv[c].x - mean) * rstd * g.x + b.x;
+                    rv[c].y = (rv[c].y - mean) * rstd * g.y + b.y;
+                    rv[c].z = (rv[c].z - mean) * rstd * g.z + b.z;
+                    rv[c].w = (rv[c].w - mean) * rstd * g.w + b.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < KP; ++c)
+            if (c * 128 < K) *reinterpret_cast<float4*>(xs + (size_t)m * KS + c * 128 + lane * 4) = rv[c];   // zero beyond K
+    }
+    __syncthreads();
+    for (; tile < tiles; tile += gridDim.x) {
+        const int n_base = tile * TR + warp * RW;
+        for (int p = 0; p < passes; ++p) {                   // 8 tokens at a time against the same registers of weights
+            float acc[V];                                    // [row][token]
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] = 0.f;
+            const int m0 = p * 8;
+            const float* xp = xs + (size_t)m0 * KS + lane * 4;
+            if (M - m0 > 2) {
+                // all 8 rows of the pass without a branch between the reads (rows beyond M hold zeros)
+#pragma unroll
+                for (int c = 0; c < KP; ++c) {
+                    if (c * 128 < K) {
+#pragma unroll
+                        for (int m = 0; m < 8; ++m) {
+                            const float4 xv = *reinterpret_cast<const float4*>(xp + (size_t)m * KS + c * 128);
+#pragma unroll
+                            for (int r = 0; r < RW; ++r) acc[r * 8 + m] = dot4(w[r][c], xv, acc[r * 8 + m]);
+                        }
+                    }
+                }
+            } else {                                         // one or two rows: only these
+#pragma unroll
+                for (int c = 0; c < KP; ++c) {
+                    if (c * 128 < K) {
+#pragma unroll
+                        for (int m = 0; m < 2; ++m) {
+                            if (m0 + m < M) {
+                                const float4 xv = *reinterpret_cast<const float4*>(xp + (size_t)m * KS + c * 128);
+#pragma unroll
+                                for (int r = 0; r < RW; ++r) acc[r * 8 + m] = dot4(w[r][c], xv, acc[r * 8 + m]);
+                            }
+                        }
+                    }
+                }
+            }
+            // the next tile's weights fly while this one's sums meet (all loads in one burst: issued one column at
+            // a time between the multiply-adds they were slower by half)
+            if (p == passes - 1 && tile + (int)gridDim.x < tiles) load_w(tile + gridDim.x);
+#pragma unroll
+            for (int half = V / 2, off = 16; half >= 1; half >>= 1, off >>= 1) {
+                const bool upper = (lane & off) != 0;
+#pragma unroll
+                for (int i = 0; i < half; ++i) {
+                    const float send = upper ? acc[i] : acc[i + half];
+                    const float keep = upper ? acc[i + half] : acc[i];
+                    acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            }
+            if constexpr (V == 16) acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
+            // the lane holds the sum of value v = 8 * row + token: v = lane with 32 sums, lane / 2 with 16
+            const int v = V == 32 ? lane : lane >> 1;
+            const int r = v >> 3, m = m0 + (v & 7), n = n_base + r;
+            if (m < M && n < N && (V == 32 || (lane & 1) == 0)) {
+                float val = apply_act(acc[0] + (bias ? __ldg(bias + n) : 0.f), act);
+                float* o = out + (size_t)m * ldo + n;
+                if (accumulate) val += __ldcg(o);
+                *o = val;
+            }
+        }
+    }
+}
+
+// Rows of x that the kernel above takes at a width K: what fits its shared memory, in eights, 64 at most (a function
+// of K alone, so that which kernel sums a row does not depend on the batch beyond that)
+constexpr int TALL_SMEM_LIMIT = 216 * 1024;
+int tall_rows(int K) {
+    if (K > 2048) return 0;
+    const int fit = TALL_SMEM_LIMIT / ((K + 127) / 128 * 128 * 4) / 8 * 8;
+    return fit < MAX_M ? fit : MAX_M;
+}
+
 int sm_count() {
     static int n = 0;
     if (!n) {
@@ -530,6 +689,22 @@ MLLM_EXPORT int mllm_linear_stream_f32(const void* x, long long ldx, const void*
     LnArgs ln = {(const float*)ln_x, ln_rows, ln_gamma, ln_beta, ln_eps};
     KvArgs kv = {(float*)k_pages, (float*)v_pages, slots, q_size, kv_heads, head_dim, page_size};
     const int tiles = (N + R - 1) / R;
+    if (M <= tall_rows(K) && !kvw && (N + 31) / 32 >= 8 * sm_count()) {
+        // very many rows (a vocabulary): the persistent kernel with a warp per 4 rows
+        const size_t smem = (size_t)((M + 7) / 8 * 8) * ((K + 127) / 128 * 128) * 4;
+        using Tall = void (*)(const float*, long long, const float*, const float*, float*, long long, int, int, int, int, int, LnArgs);
+        const int which = (K <= 1024 ? 0 : 2) + (norm ? 1 : 0);
+        static const Tall kerns[4] = {linear_stream_f32_tall_kernel<8, 4, false>, linear_stream_f32_tall_kernel<8, 4, true>,
+                                      linear_stream_f32_tall_kernel<16, 2, false>, linear_stream_f32_tall_kernel<16, 2, true>};
+        static bool wide[4] = {false, false, false, false};
+        if (smem > 48 * 1024 && !wide[which]) {
+            MLLM_CUDA(cudaFuncSetAttribute(kerns[which], cudaFuncAttributeMaxDynamicSharedMemorySize, TALL_SMEM_LIMIT));
+            wide[which] = true;
+        }
+        MLLM_CUDA(mllm_launch(kerns[which], dim3(sm_count()), dim3(WARPS * 32), smem, stream, true, (const float*)x, ldx,
+                              (const float*)W, bias, (float*)out, ldo, M, N, K, act, accumulate, ln));
+        return 0;
+    }
     if (M <= FEW_M) {
         // threads split K; CTAs own several tiles of narrow K so that the grid is one wave of two CTAs per SM
         int S = norm ? 1 : mllm_linear_stream_f32_slices(N, K);

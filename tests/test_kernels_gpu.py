@@ -254,10 +254,12 @@ def test_linear_small_m_rows_do_not_depend_on_the_batch(ops):
 @pytest.mark.parametrize("M,N,K", [(1, 768, 768), (8, 2304, 768), (3, 50, 40), (16, 1003, 96), (5, 320, 3072), (13, 50257, 64),
                                    (17, 768, 3072), (40, 4800, 1600), (64, 768, 768), (64, 100, 6400), (33, 2304, 768),
                                    (9, 7, 12), (2, 1600, 6400), (64, 1024, 4096), (33, 1600, 6400), (48, 6400, 1600),
-                                   (20, 50257, 1024), (64, 130, 12000)])
+                                   (20, 50257, 1024), (64, 130, 12000), (8, 50257, 768), (16, 40000, 1600), (3, 38000, 2048),
+                                   (1, 50257, 1024), (64, 50257, 768), (40, 40000, 1024), (32, 38000, 1600), (33, 38000, 1600)])
 def test_linear_stream_float32(ops, M, N, K):
     """The 32-bit weight-streaming product (weights by bulk copy into shared memory, warps own tokens, K slices
-    of narrow matrices shared by a cluster) beside float64, at 1 to 64 rows."""
+    of narrow matrices shared by a cluster; for a matrix as tall as a vocabulary and up to 16 rows the kernel that
+    stays on its SM and gives each warp rows of its own) beside float64, at 1 to 64 rows."""
     x, w, b = rnd(M, K, seed=1), rnd(N, K, seed=2, scale=K ** -0.5), rnd(N, seed=3)
     ref = x.double() @ w.double().t() + b.double()
     for act in (None, "gelu_tanh", "gelu_erf"):
@@ -272,15 +274,22 @@ def test_linear_stream_float32(ops, M, N, K):
     assert (acc.double() - (acc0.double() + wide[:, 4:4 + K].double() @ w.double().t())).abs().max() < 1e-4
     # a row does not depend on the batch: alone, in a pair, and in the whole batch it has the same bits, as long
     # as the batch stays on one side of 16 rows (up to 16 rows the threads split K, beyond them the warps split
-    # the tokens: two kernels, whose sums differ in rounding)
+    # the tokens: two kernels, whose sums differ in rounding); a matrix as tall as a vocabulary has one kernel for
+    # all the rows that fit its shared memory, and there every cut has the same bits
     full = torch.empty(M, N, device=DEV)
     ops.linear(x, w, None, out=full, impl="stream_f32")
-    cuts = ((M - 1, M), (0, 1), (max(0, M - 9), M), (0, min(M, 16))) if M <= 16 else ((0, 17), (M - 17, M), (max(0, M - 30), M))
+    side = 16
+    if N >= 38000 and K <= 2048:
+        side = min(64, 216 * 1024 // ((K + 127) // 128 * 128 * 4) // 8 * 8)
+    if M <= side:
+        cuts = ((M - 1, M), (0, 1), (max(0, M - 9), M), (0, min(M, 16)), (M // 2, min(M, M // 2 + 3)))
+    else:
+        cuts = ((0, side + 1), (M - side - 1, M), (max(0, M - side - 14), M))
     for lo, hi in cuts:
         part = torch.empty(hi - lo, N, device=DEV)
         ops.linear(x[lo:hi], w, None, out=part, impl="stream_f32")
         assert torch.equal(part, full[lo:hi]), (lo, hi)
-    if M > 16:
+    if M > side:
         part = torch.empty(5, N, device=DEV)
         ops.linear(x[3:8], w, None, out=part, impl="stream_f32")
         assert (part.double() - full[3:8].double()).abs().max() < 2e-5 * max(1.0, ref.abs().max().item())
@@ -293,7 +302,8 @@ def test_linear_stream_float32(ops, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K,eps", [(1, 768, 768, 1e-5), (8, 2304, 768, 1e-5), (5, 1000, 96, 1e-6), (16, 320, 1600, 1e-5),
-                                       (13, 50257, 64, 1e-3), (9, 200, 1024, 1e-5), (16, 4800, 2048, 1e-5)])
+                                       (13, 50257, 64, 1e-3), (9, 200, 1024, 1e-5), (16, 4800, 2048, 1e-5),
+                                       (8, 50257, 768, 1e-5), (11, 40000, 1600, 1e-5), (2, 50257, 1020, 1e-5)])
 def test_stream_float32_product_with_the_norm_fused_in(ops, M, N, K, eps):
     """LayerNorm fused into the float32 weight-streaming product (the owning warp keeps the row in registers),
     also with gathered rows, against float64 and against the two separate kernels; one launch."""
