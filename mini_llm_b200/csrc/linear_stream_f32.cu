@@ -16,9 +16,10 @@
 // in warp order, then across the slices in rank order.  17 to 64 rows (`many`): every warp takes whole
 // tokens (warp w the tokens w, w + 8, ...), its lanes split K, and the weights are read from shared memory
 // once per warp, which 8 tokens per warp amortise.
-// A matrix as tall as a vocabulary (`tall`, at least 8 tiles of 32 rows per SM) has a kernel of its own that
-// stays on its SM: x in shared memory once, a warp's 4 weight rows in registers straight from HBM, no barrier
-// in its loop; it takes all the rows of x that fit shared memory (64 at K = 768).
+// Rows up to 2048 long (`tall`: the Q|K|V and up-projections, and the vocabulary) have a kernel whose CTAs stay on
+// their SMs: x (normalised) in shared memory once per CTA, a warp's 4 or 2 weight rows in registers straight from
+// HBM, no barrier in its loop.  It takes up to 16 rows of x, and for a matrix as tall as a vocabulary all that fit
+// shared memory (64 at K = 768); where it was measured faster than the tile kernels is written beside its rule.
 // A token's sum runs over k in an order that depends on N, K and on the slices only, never on M, so a
 // token's result does not change with the batch (`few`, `many` and `tall` differ in rounding, as kernels do).
 //
@@ -451,18 +452,21 @@ linear_stream_f32_many_kernel(const float* x, long long ldx, const float* __rest
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Up to 64 rows (as many as fit shared memory) against a matrix with very many rows (a vocabulary): one CTA per SM stays and walks tiles of 32
-// weight rows (16 when K is over 1024); a warp owns 4 (2) rows of the tile and all of K, its lanes split K in float4 steps of 128.  The (normalised)
-// rows of x are put into shared memory once per CTA; the weights come straight from HBM into registers, 4 rows x K in
-// flight per warp, the first tile's before the kernel waits for its predecessor.  A value of x read from shared memory
-// meets 4 weight rows (16 multiply-adds per 16-byte read, which keeps shared memory off the critical path), and the
-// 32 sums of a lane meet inside the warp by the halving butterfly, after which lane 8r + m holds row r, token m: no
-// barrier and no shared memory in the loop.  Per tile that is a third of the instructions of the kernel above, which
-// at 50,257 rows is bound by its instructions, not by HBM.
-template <int KP, int RW, bool LN>     // KP: float4 steps of K per lane (K <= KP * 128); RW: weight rows of a warp (4 or 2)
+// Rows of W up to 2048 long, up to 64 rows of x (as many as fit shared memory): at most one CTA per SM, which stays
+// and walks tiles of 32 weight rows (16 with 2 rows per warp); a warp owns 4 (2) rows of the tile and all of K, its
+// lanes split K in float4 steps of 128.  The (normalised) rows of x are put into shared memory once per CTA; the
+// weights come straight from HBM into registers, 4 rows x K in flight per warp, the first tile's before the kernel
+// waits for its predecessor.  A value of x read from shared memory meets 4 weight rows (16 multiply-adds per
+// 16-byte read, which keeps shared memory off the critical path), and the 32 sums of a lane meet inside the warp by
+// the halving butterfly, after which lane 8r + m holds row r, token m: no barrier and no shared memory in the loop,
+// and the norm's statistics once per SM instead of once per tile.  Per tile that is a third of the instructions of
+// the kernel above, which at 50,257 rows is bound by its instructions, not by HBM, and which at the widths of GPT-2
+// medium and XL needs two or three waves of CTAs.  With a Q|K|V matrix the key and value columns go to their slots.
+template <int KP, int RW, bool LN, bool KVW>     // KP: float4 steps of K per lane (K <= KP * 128); RW: weight rows of a warp (4 or 2)
 __global__ void __launch_bounds__(WARPS * 32, 1)
 linear_stream_f32_tall_kernel(const float* x, long long ldx, const float* __restrict__ W, const float* __restrict__ bias,
-                              float* out, long long ldo, int M, int N, int K, int act, int accumulate, LnArgs ln) {
+                              float* out, long long ldo, int M, int N, int K, int act, int accumulate, LnArgs ln,
+                              KvArgs kv) {
     extern __shared__ __align__(16) float xs[];             // [M up to a multiple of 8][K up to a multiple of 128]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -541,6 +545,17 @@ linear_stream_f32_tall_kernel(const float* x, long long ldx, const float* __rest
 #pragma unroll
             for (int i = 0; i < V; ++i) acc[i] = 0.f;
             const int m0 = p * 8;
+            // what the epilogue of this lane needs (bias, the old value or the cache slot) is fetched before the products
+            const int e_v = V == 32 ? lane : lane >> 1;
+            const int e_m = m0 + (e_v & 7), e_n = n_base + (e_v >> 3);
+            const bool e_ok = e_m < M && e_n < N && (V == 32 || (lane & 1) == 0);
+            float e_bias = 0.f, e_old = 0.f;
+            int e_slot = 0;
+            if (e_ok) {
+                if (bias) e_bias = __ldg(bias + e_n);
+                if (KVW && e_n >= kv.q_size) e_slot = __ldcg(kv.slots + e_m);
+                else if (accumulate) e_old = __ldcg(out + (size_t)e_m * ldo + e_n);
+            }
             const float* xp = xs + (size_t)m0 * KS + lane * 4;
             if (M - m0 > 2) {
                 // all 8 rows of the pass without a branch between the reads (rows beyond M hold zeros)
@@ -585,14 +600,7 @@ linear_stream_f32_tall_kernel(const float* x, long long ldx, const float* __rest
             }
             if constexpr (V == 16) acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
             // the lane holds the sum of value v = 8 * row + token: v = lane with 32 sums, lane / 2 with 16
-            const int v = V == 32 ? lane : lane >> 1;
-            const int r = v >> 3, m = m0 + (v & 7), n = n_base + r;
-            if (m < M && n < N && (V == 32 || (lane & 1) == 0)) {
-                float val = apply_act(acc[0] + (bias ? __ldg(bias + n) : 0.f), act);
-                float* o = out + (size_t)m * ldo + n;
-                if (accumulate) val += __ldcg(o);
-                *o = val;
-            }
+            if (e_ok) finish_one<KVW>(acc[0], e_m, e_n, e_bias, out, ldo, act, accumulate, e_old, e_slot, kv);
         }
     }
 }
@@ -604,6 +612,27 @@ int tall_rows(int K) {
     if (K > 2048) return 0;
     const int fit = TALL_SMEM_LIMIT / ((K + 127) / 128 * 128 * 4) / 8 * 8;
     return fit < MAX_M ? fit : MAX_M;
+}
+
+int sm_count();
+// Whether the kernel above takes a matrix, and with how many weight rows per warp (0: not this kernel), from the
+// matrix alone.  Measured against the tile kernels at the layer shapes of GPT-2 small, medium and XL and 1, 8 and 16
+// rows of x: up to K = 1024 it wins everywhere (3.4-6 us against 3.9-8.5 us), with 4 rows per warp once those
+// tiles of 32 rows fill more than half of the SMs, else with 2; from K = 1025 to 2048 it wins when its tiles of 16
+// rows fill the SMs at least once (N >= 2368 on 148 SMs: 14 against 25 us at 4800 x 1600), and loses for narrower
+// matrices (6.8 against 5.3 us at 1600 x 1600), where the tile kernel's K slices keep more SMs busy.
+int tall_shape(int N, int K) {
+    if (K > 2048) return 0;
+    const int sms = sm_count();
+    if (K <= 1024) return 5 * ((N + 31) / 32) >= 3 * sms ? 4 : 2;
+    return (N + 15) / 16 >= sms ? 2 : 0;
+}
+// Rows of x up to which it is taken: all that fit shared memory for a matrix as tall as a vocabulary, 16 otherwise
+// (beyond them the kernel for 17 to 64 rows is as fast)
+int tall_rows_for(int N, int K) {
+    if (!tall_shape(N, K)) return 0;
+    const int fit = tall_rows(K);
+    return (N + 31) / 32 >= 8 * sm_count() ? fit : (fit < FEW_M ? fit : FEW_M);
 }
 
 int sm_count() {
@@ -656,6 +685,9 @@ MLLM_EXPORT int mllm_linear_stream_f32_many_shape(int N, int K, int* rt, int* sl
     return best < 0 ? 1 : 0;        // 1: no shape fits shared memory (K beyond about 48,000): the caller takes another kernel
 }
 
+// Rows of x up to which a matrix [N, K] goes to the kernel with the weights in registers (0: never).
+MLLM_EXPORT int mllm_linear_stream_f32_tall_rows(int N, int K) { return tall_rows_for(N, K); }
+
 MLLM_EXPORT int mllm_linear_stream_f32_bind_error(int* word) { return tc::bind_host_error(word); }
 
 MLLM_EXPORT int mllm_linear_stream_f32_error(int* code) {
@@ -689,20 +721,28 @@ MLLM_EXPORT int mllm_linear_stream_f32(const void* x, long long ldx, const void*
     LnArgs ln = {(const float*)ln_x, ln_rows, ln_gamma, ln_beta, ln_eps};
     KvArgs kv = {(float*)k_pages, (float*)v_pages, slots, q_size, kv_heads, head_dim, page_size};
     const int tiles = (N + R - 1) / R;
-    if (M <= tall_rows(K) && !kvw && (N + 31) / 32 >= 8 * sm_count()) {
-        // very many rows (a vocabulary): the persistent kernel with a warp per 4 rows
+    const int tall_rw = M <= tall_rows_for(N, K) ? tall_shape(N, K) : 0;
+    if (tall_rw) {
+        // weights from HBM into registers, x in shared memory once per CTA, CTAs that stay and walk the tiles
         const size_t smem = (size_t)((M + 7) / 8 * 8) * ((K + 127) / 128 * 128) * 4;
-        using Tall = void (*)(const float*, long long, const float*, const float*, float*, long long, int, int, int, int, int, LnArgs);
-        const int which = (K <= 1024 ? 0 : 2) + (norm ? 1 : 0);
-        static const Tall kerns[4] = {linear_stream_f32_tall_kernel<8, 4, false>, linear_stream_f32_tall_kernel<8, 4, true>,
-                                      linear_stream_f32_tall_kernel<16, 2, false>, linear_stream_f32_tall_kernel<16, 2, true>};
-        static bool wide[4] = {false, false, false, false};
+        using Tall = void (*)(const float*, long long, const float*, const float*, float*, long long, int, int, int, int, int,
+                              LnArgs, KvArgs);
+        const int shape = K > 1024 ? 2 : (tall_rw == 2 ? 1 : 0);
+        const int which = shape * 4 + (norm ? 2 : 0) + (kvw ? 1 : 0);
+#define MLLM_TALL(KP, RW) linear_stream_f32_tall_kernel<KP, RW, false, false>, linear_stream_f32_tall_kernel<KP, RW, false, true>, \
+                          linear_stream_f32_tall_kernel<KP, RW, true, false>, linear_stream_f32_tall_kernel<KP, RW, true, true>
+        static const Tall kerns[12] = {MLLM_TALL(8, 4), MLLM_TALL(8, 2), MLLM_TALL(16, 2)};
+#undef MLLM_TALL
+        static bool wide[12] = {};
         if (smem > 48 * 1024 && !wide[which]) {
             MLLM_CUDA(cudaFuncSetAttribute(kerns[which], cudaFuncAttributeMaxDynamicSharedMemorySize, TALL_SMEM_LIMIT));
             wide[which] = true;
         }
-        MLLM_CUDA(mllm_launch(kerns[which], dim3(sm_count()), dim3(WARPS * 32), smem, stream, true, (const float*)x, ldx,
-                              (const float*)W, bias, (float*)out, ldo, M, N, K, act, accumulate, ln));
+        const int rows_tile = WARPS * (shape == 0 ? 4 : 2);
+        const int tiles_tall = (N + rows_tile - 1) / rows_tile;
+        const int grid = tiles_tall < sm_count() ? tiles_tall : sm_count();
+        MLLM_CUDA(mllm_launch(kerns[which], dim3(grid), dim3(WARPS * 32), smem, stream, true, (const float*)x, ldx,
+                              (const float*)W, bias, (float*)out, ldo, M, N, K, act, accumulate, ln, kv));
         return 0;
     }
     if (M <= FEW_M) {

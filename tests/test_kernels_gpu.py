@@ -272,27 +272,26 @@ def test_linear_stream_float32(ops, M, N, K):
     wide = rnd(M, K + 8, seed=5)
     ops.linear(wide[:, 4:4 + K], w, None, out=acc, accumulate=True, impl="stream_f32")
     assert (acc.double() - (acc0.double() + wide[:, 4:4 + K].double() @ w.double().t())).abs().max() < 1e-4
-    # a row does not depend on the batch: alone, in a pair, and in the whole batch it has the same bits, as long
-    # as the batch stays on one side of 16 rows (up to 16 rows the threads split K, beyond them the warps split
-    # the tokens: two kernels, whose sums differ in rounding); a matrix as tall as a vocabulary has one kernel for
-    # all the rows that fit its shared memory, and there every cut has the same bits
+    # a row does not depend on the batch: alone, in a pair, and in the whole batch it has the same bits, as long as
+    # the same kernel computes it.  Which kernel that is depends on the matrix and on the side of a row count: the
+    # kernel that keeps its weights in registers takes a matrix up to a count of its own (all rows that fit its shared
+    # memory for a vocabulary, 16 for the layer matrices it wins at); otherwise up to 16 rows the threads split K
+    # and beyond them the warps split the tokens.  Kernels differ in rounding.
     full = torch.empty(M, N, device=DEV)
     ops.linear(x, w, None, out=full, impl="stream_f32")
-    side = 16
-    if N >= 38000 and K <= 2048:
-        side = min(64, 216 * 1024 // ((K + 127) // 128 * 128 * 4) // 8 * 8)
-    if M <= side:
-        cuts = ((M - 1, M), (0, 1), (max(0, M - 9), M), (0, min(M, 16)), (M // 2, min(M, M // 2 + 3)))
-    else:
-        cuts = ((0, side + 1), (M - side - 1, M), (max(0, M - side - 14), M))
-    for lo, hi in cuts:
+    tall = ops.library().mllm_linear_stream_f32_tall_rows(N, K)
+    kernel_of = lambda m: "tall" if m <= tall else ("few" if m <= 16 else "many")
+    cuts = [(M - 1, M), (0, 1), (max(0, M - 9), M), (0, min(M, 16)), (M // 2, min(M, M // 2 + 3)), (0, min(M, 17)),
+            (max(0, M - 17), M), (max(0, M - 30), M), (0, M)]
+    same = [(lo, hi) for lo, hi in cuts if hi > lo and kernel_of(hi - lo) == kernel_of(M)]
+    for lo, hi in same:
         part = torch.empty(hi - lo, N, device=DEV)
         ops.linear(x[lo:hi], w, None, out=part, impl="stream_f32")
         assert torch.equal(part, full[lo:hi]), (lo, hi)
-    if M > side:
-        part = torch.empty(5, N, device=DEV)
-        ops.linear(x[3:8], w, None, out=part, impl="stream_f32")
-        assert (part.double() - full[3:8].double()).abs().max() < 2e-5 * max(1.0, ref.abs().max().item())
+    for lo, hi in [(lo, hi) for lo, hi in cuts if hi > lo and kernel_of(hi - lo) != kernel_of(M)][:1]:
+        part = torch.empty(hi - lo, N, device=DEV)
+        ops.linear(x[lo:hi], w, None, out=part, impl="stream_f32")
+        assert (part.double() - full[lo:hi].double()).abs().max() < 2e-5 * max(1.0, ref.abs().max().item())
     if M <= 64:                                   # and it is what the dispatcher picks for float32 rows up to 64
         auto = torch.empty(M, N, device=DEV)
         n0 = ops.launches
