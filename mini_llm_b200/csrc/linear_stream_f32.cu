@@ -627,12 +627,17 @@ int tall_shape(int N, int K) {
     if (K <= 1024) return 5 * ((N + 31) / 32) >= 3 * sms ? 4 : 2;
     return (N + 15) / 16 >= sms ? 2 : 0;
 }
-// Rows of x up to which it is taken: all that fit shared memory for a matrix as tall as a vocabulary, 16 otherwise
-// (beyond them the kernel for 17 to 64 rows is as fast)
+// Rows of x up to which it is taken: all that fit shared memory for a matrix as tall as a vocabulary; 48 with 4 weight
+// rows per warp (3072 x 768 at 48 rows: 20.9 against 22.1 us of the kernel for 17 to 64 rows, 3072 x 1024: 24.6
+// against 29.4 us; at 64 rows they are even or it loses), 24 with K over 1024 (4800 x 1600 at 24 rows: 38.5 against
+// 42.9 us, at 32 rows 49.2 against 45.4 us), 16 for narrower matrices (2304 x 768 at 24 rows: 13.0 against 12.4 us).
 int tall_rows_for(int N, int K) {
-    if (!tall_shape(N, K)) return 0;
+    const int rw = tall_shape(N, K);
+    if (!rw) return 0;
     const int fit = tall_rows(K);
-    return (N + 31) / 32 >= 8 * sm_count() ? fit : (fit < FEW_M ? fit : FEW_M);
+    if ((N + 31) / 32 >= 8 * sm_count()) return fit;
+    const int cap = K > 1024 ? 24 : (rw == 4 ? 48 : FEW_M);
+    return fit < cap ? fit : cap;
 }
 
 int sm_count() {
