@@ -605,6 +605,151 @@ linear_stream_f32_tall_kernel(const float* x, long long ldx, const float* __rest
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Rows of W longer than 2048 (a down-projection), up to 64 rows of x: the arrangement of the kernel above with K
+// cut twice.  A CTA owns a tile of 32 weight rows (4 per warp) over a slice of K (the S CTAs of a thread-block
+// cluster share a tile's K), and walks its slice in chunks of KP * 128 floats.  Per chunk the CTA puts all rows of
+// x into shared memory once (asynchronous 16-byte copies), every warp holds its 4 x chunk weights in registers
+// (straight from HBM; the first chunk's before the wait on the previous kernel, the next chunk's issued in one
+// burst before the last sums of this one meet), and 8 tokens at a time go against them.  A lane's 32 sums meet
+// inside the warp by the halving butterfly; lane 8r + m then holds row r, token m of the pass.  Chunks are added in
+// chunk order (in shared memory), slices in rank order: rank q finishes the passes q, q + S, ... and reads the
+// other slices' sums over the SM-to-SM network, all at once.
+template <int KP, bool KVW>
+__global__ void __launch_bounds__(WARPS * 32, KP <= 3 ? 2 : 1)
+linear_stream_f32_regs_kernel(const float* x, long long ldx, const float* __restrict__ W, const float* __restrict__ bias,
+                              float* out, long long ldo, int M, int N, int K, int Ls, int S, int act, int accumulate,
+                              KvArgs kv) {
+    constexpr int KC = KP * 128, RW = 4, TR = WARPS * RW;
+    extern __shared__ __align__(16) float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int passes = (M + 7) / 8;
+    float* xs = smem;                                       // [passes * 8][KC]
+    float* red = smem + (size_t)passes * 8 * KC;            // [passes][WARPS][32] sums over the chunks so far
+    const int tile = blockIdx.x / S, rank = blockIdx.x % S;
+    const int k_lo = min(K, rank * Ls), k_hi = min(K, k_lo + Ls);
+    const int chunks = (k_hi - k_lo + KC - 1) / KC;         // 0: an empty slice adds nothing
+    const int n_base = tile * TR + warp * RW;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 w[RW][KP];
+    auto load_w = [&](int c) {
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+            const int n = n_base + r;
+            const float* row = W + (size_t)(n < N ? n : 0) * K;
+#pragma unroll
+            for (int col = 0; col < KP; ++col) {
+                const int k = k_lo + c * KC + col * 128 + lane * 4;
+                w[r][col] = (k < k_hi && n < N) ? __ldcs(reinterpret_cast<const float4*>(row + k)) : zero4;
+            }
+        }
+    };
+    if (chunks > 0) load_w(0);                // weights depend on no kernel of the step
+    // after the butterfly the lane holds row e_r of the warp and token e_m of the pass; rank q finishes the passes
+    // q, q + S, ... and fetches what their epilogue needs (the old value or the cache slot) long before
+    const int e_r = lane >> 3, e_m = lane & 7, e_n = n_base + e_r;
+    const bool e_col = e_n < N;
+    const float e_bias = (e_col && bias) ? __ldg(bias + e_n) : 0.f;
+    pdl_wait();
+    pdl_launch();
+    float e_old[8];
+    int e_slot[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int m = (rank + i * S) * 8 + e_m;
+        e_old[i] = 0.f;
+        e_slot[i] = 0;
+        if (e_col && m < M) {
+            if (KVW && e_n >= kv.q_size) e_slot[i] = __ldcg(kv.slots + m);
+            else if (accumulate) e_old[i] = __ldcg(out + (size_t)m * ldo + e_n);
+        }
+    }
+    const bool direct = S == 1 && chunks == 1;     // the sums go out as they meet
+    const uint32_t xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
+    for (int c = 0; c < chunks; ++c) {
+        if (c > 0) __syncthreads();                // the chunk before has been read by every warp
+        const int kc0 = k_lo + c * KC;
+        // rows of x into shared memory by asynchronous 16-byte copies (zeros beyond M and beyond the slice)
+        for (int m = warp; m < passes * 8; m += WARPS) {
+#pragma unroll
+            for (int col = 0; col < KP; ++col) {
+                const int k = kc0 + col * 128 + lane * 4;
+                const bool in = m < M && k < k_hi;
+                const float* src = in ? x + (size_t)m * ldx + k : x;
+                const uint32_t dst = xs_addr + (uint32_t)(((size_t)m * KC + col * 128 + lane * 4) * 4);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(src), "r"(in ? 16 : 0) : "memory");
+            }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();
+        const int len = min(KC, k_hi - kc0);
+#pragma unroll 1
+        for (int p = 0; p < passes; ++p) {
+            float acc[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+            const float* xp = xs + (size_t)p * 8 * KC + lane * 4;
+#pragma unroll
+            for (int col = 0; col < KP; ++col) {
+                if (col * 128 < len) {
+#pragma unroll
+                    for (int m = 0; m < 8; ++m) {
+                        const float4 xv = *reinterpret_cast<const float4*>(xp + (size_t)m * KC + col * 128);
+#pragma unroll
+                        for (int r = 0; r < RW; ++r) acc[r * 8 + m] = dot4(w[r][col], xv, acc[r * 8 + m]);
+                    }
+                }
+            }
+            if (p == passes - 1 && c + 1 < chunks) load_w(c + 1);
+#pragma unroll
+            for (int half = 16, off = 16; half >= 1; half >>= 1, off >>= 1) {
+                const bool upper = (lane & off) != 0;
+#pragma unroll
+                for (int i = 0; i < half; ++i) {
+                    const float send = upper ? acc[i] : acc[i + half];
+                    const float keep = upper ? acc[i + half] : acc[i];
+                    acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            }
+            if (direct) {
+                const int m = p * 8 + e_m;
+                float old = 0.f;
+                int sl = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (i == p) old = e_old[i], sl = e_slot[i];
+                if (e_col && m < M) finish_one<KVW>(acc[0], m, e_n, e_bias, out, ldo, act, accumulate, old, sl, kv);
+            } else {
+                float* slot = red + ((size_t)p * WARPS + warp) * 32 + lane;
+                *slot = c == 0 ? acc[0] : *slot + acc[0];      // only this lane touches the slot
+            }
+        }
+    }
+    if (direct) return;
+    cg::cluster_group cluster = cg::this_cluster();
+    if (S > 1) cluster.sync();                                 // every slice's sums are in place
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int p = rank + i * S;
+        if (p < passes) {
+            const size_t at = ((size_t)p * WARPS + warp) * 32 + lane;
+            float part[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {                      // all slices' sums on their way at once
+                part[q] = 0.f;
+                if (q < S && q * Ls < K) part[q] = S > 1 ? cluster.map_shared_rank(red, q)[at] : red[at];
+            }
+            float v = part[0];
+#pragma unroll
+            for (int q = 1; q < 8; ++q)
+                if (q < S) v += part[q];                       // rank order
+            const int m = p * 8 + e_m;
+            if (e_col && m < M) finish_one<KVW>(v, m, e_n, e_bias, out, ldo, act, accumulate, e_old[i], e_slot[i], kv);
+        }
+    }
+    if (S > 1) cluster.sync();                                 // the others' shared memory has been read
+}
+
 // Rows of x that the kernel above takes at a width K: what fits its shared memory, in eights, 64 at most (a function
 // of K alone, so that which kernel sums a row does not depend on the batch beyond that)
 constexpr int TALL_SMEM_LIMIT = 216 * 1024;
@@ -615,6 +760,25 @@ int tall_rows(int K) {
 }
 
 int sm_count();
+// K slices with which the kernel for long rows takes M rows of x against a matrix [N, K] (0: another kernel does).
+// From the matrix alone, except for the side of 16 rows.  Measured at the down-projections of GPT-2 small, medium
+// and XL against the tile kernels: with the largest of 4 or 2 slices whose CTAs fit the SMs at once it wins at every
+// row count where the chunks of 768 fill the slice to 4/5 at least (768 x 3072 in 4 slices: 5.0 / 5.1 / 7.0 us at
+// 1 / 8 / 16 rows against 5.6 / 5.9 / 9.4 us, 17.9 against 19.0 us at 64; 1600 x 6400 in 2 slices: 16 against 20 us at
+// 8 rows, 72 against 92 us at 64); where they do not (1024 x 4096: slices of 1024 are a chunk and a third) it loses
+// up to 16 rows (7.8 against 7.2 us) and wins beyond (27 against 32 us at 64).
+constexpr int REGS_KC = 768;
+int regs_slices(int N, int K, int M) {
+    if (K <= 2048 || K % 4 != 0) return 0;
+    const int tiles = (N + 31) / 32, sms = sm_count();
+    int S = tiles * 4 <= sms ? 4 : tiles * 2 <= sms ? 2 : 0;
+    if (!S) return 0;
+    const int Ls = ((K + S - 1) / S + 127) / 128 * 128;
+    const int chunks = (Ls + REGS_KC - 1) / REGS_KC;
+    const bool filled = 4 * chunks * REGS_KC <= 5 * Ls;
+    return (filled || M > FEW_M) ? S : 0;
+}
+
 // Whether the kernel above takes a matrix, and with how many weight rows per warp (0: not this kernel), from the
 // matrix alone.  Measured against the tile kernels at the layer shapes of GPT-2 small, medium and XL and 1, 8 and 16
 // rows of x: up to K = 1024 it wins everywhere (3.4-6 us against 3.9-8.5 us), with 4 rows per warp once those
@@ -693,6 +857,15 @@ MLLM_EXPORT int mllm_linear_stream_f32_many_shape(int N, int K, int* rt, int* sl
 // Rows of x up to which a matrix [N, K] goes to the kernel with the weights in registers (0: never).
 MLLM_EXPORT int mllm_linear_stream_f32_tall_rows(int N, int K) { return tall_rows_for(N, K); }
 
+// Which kernel of this file computes M plain rows (no norm, no cache write) against a matrix [N, K]: 0 threads split K
+// (up to 16 rows), 1 warps own tokens (17 to 64 rows), 2 weights in registers, 3 long rows in cluster slices.  Rows
+// computed by the same kernel have the same bits whatever the batch.
+MLLM_EXPORT int mllm_linear_stream_f32_kernel_of(int M, int N, int K) {
+    if (M <= tall_rows_for(N, K)) return 2;
+    if (regs_slices(N, K, M)) return 3;
+    return M <= FEW_M ? 0 : 1;
+}
+
 MLLM_EXPORT int mllm_linear_stream_f32_bind_error(int* word) { return tc::bind_host_error(word); }
 
 MLLM_EXPORT int mllm_linear_stream_f32_error(int* code) {
@@ -748,6 +921,44 @@ MLLM_EXPORT int mllm_linear_stream_f32(const void* x, long long ldx, const void*
         const int grid = tiles_tall < sm_count() ? tiles_tall : sm_count();
         MLLM_CUDA(mllm_launch(kerns[which], dim3(grid), dim3(WARPS * 32), smem, stream, true, (const float*)x, ldx,
                               (const float*)W, bias, (float*)out, ldo, M, N, K, act, accumulate, ln, kv));
+        return 0;
+    }
+    const int regs_s = regs_slices(N, K, M);
+    if (regs_s && !norm && !kvw) {
+        // long rows: K slices in a cluster, chunks in registers
+        const int S = regs_s;
+        const int Ls = ((K + S - 1) / S + 127) / 128 * 128;
+        const size_t smem = ((size_t)((M + 7) / 8 * 8) * REGS_KC + (size_t)((M + 7) / 8) * WARPS * 32) * 4;
+        auto kern = linear_stream_f32_regs_kernel<REGS_KC / 128, false>;
+        static bool wide_regs = false;
+        if (smem > 48 * 1024 && !wide_regs) {
+            MLLM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (MAX_M * REGS_KC + MAX_M / 8 * WARPS * 32) * 4));
+            wide_regs = true;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((N + 31) / 32 * S);
+        cfg.blockDim = dim3(WARPS * 32);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        int na = 0;
+        if (S > 1) {
+            attr[na].id = cudaLaunchAttributeClusterDimension;
+            attr[na].val.clusterDim.x = S;
+            attr[na].val.clusterDim.y = 1;
+            attr[na].val.clusterDim.z = 1;
+            ++na;
+        }
+        if (g_mllm_pdl) {
+            attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[na].val.programmaticStreamSerializationAllowed = 1;
+            ++na;
+        }
+        cfg.attrs = attr;
+        cfg.numAttrs = na;
+        MLLM_CUDA(cudaLaunchKernelEx(&cfg, kern, (const float*)x, ldx, (const float*)W, bias, (float*)out, ldo, M, N, K, Ls, S,
+                                     act, accumulate, kv));
         return 0;
     }
     if (M <= FEW_M) {

@@ -58,6 +58,7 @@ def _signatures(lib):
                                    c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
                                    c_int, c_int, c_int, c_int, c_void_p],
         "mllm_linear_stream_f32_tall_rows": [c_int, c_int],
+        "mllm_linear_stream_f32_kernel_of": [c_int, c_int, c_int],
         "mllm_linear_stream_f32_bind_error": [c_void_p],
         "mllm_linear_stream_f32_error": [c_void_p],
         "mllm_linear_tcgen05": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,

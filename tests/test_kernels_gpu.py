@@ -255,7 +255,9 @@ def test_linear_small_m_rows_do_not_depend_on_the_batch(ops):
                                    (17, 768, 3072), (40, 4800, 1600), (64, 768, 768), (64, 100, 6400), (33, 2304, 768),
                                    (9, 7, 12), (2, 1600, 6400), (64, 1024, 4096), (33, 1600, 6400), (48, 6400, 1600),
                                    (20, 50257, 1024), (64, 130, 12000), (8, 50257, 768), (16, 40000, 1600), (3, 38000, 2048),
-                                   (1, 50257, 1024), (64, 50257, 768), (40, 40000, 1024), (32, 38000, 1600), (33, 38000, 1600)])
+                                   (1, 50257, 1024), (64, 50257, 768), (40, 40000, 1024), (32, 38000, 1600), (33, 38000, 1600),
+                                   (8, 768, 3072), (16, 1600, 6400), (3, 1024, 4096), (64, 768, 3072), (24, 1600, 6400), (40, 1024, 4096),
+                                   (5, 100, 2500), (48, 1000, 2052)])
 def test_linear_stream_float32(ops, M, N, K):
     """The 32-bit weight-streaming product (weights by bulk copy into shared memory, warps own tokens, K slices
     of narrow matrices shared by a cluster; for a matrix as tall as a vocabulary and up to 16 rows the kernel that
@@ -275,12 +277,12 @@ def test_linear_stream_float32(ops, M, N, K):
     # a row does not depend on the batch: alone, in a pair, and in the whole batch it has the same bits, as long as
     # the same kernel computes it.  Which kernel that is depends on the matrix and on the side of a row count: the
     # kernel that keeps its weights in registers takes a matrix up to a count of its own (all rows that fit its shared
-    # memory for a vocabulary, 16 for the layer matrices it wins at); otherwise up to 16 rows the threads split K
-    # and beyond them the warps split the tokens.  Kernels differ in rounding.
+    # memory for a vocabulary, 16 to 48 for the layer matrices it wins at), long rows go to cluster slices where
+    # those win; otherwise up to 16 rows the threads split K and beyond them the warps split the tokens.  The
+    # library says which kernel takes which count; kernels differ in rounding.
     full = torch.empty(M, N, device=DEV)
     ops.linear(x, w, None, out=full, impl="stream_f32")
-    tall = ops.library().mllm_linear_stream_f32_tall_rows(N, K)
-    kernel_of = lambda m: "tall" if m <= tall else ("few" if m <= 16 else "many")
+    kernel_of = lambda m: ops.library().mllm_linear_stream_f32_kernel_of(m, N, K)
     cuts = [(M - 1, M), (0, 1), (max(0, M - 9), M), (0, min(M, 16)), (M // 2, min(M, M // 2 + 3)), (0, min(M, 17)),
             (max(0, M - 17), M), (max(0, M - 30), M), (0, M)]
     same = [(lo, hi) for lo, hi in cuts if hi > lo and kernel_of(hi - lo) == kernel_of(M)]
