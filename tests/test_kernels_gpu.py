@@ -302,6 +302,34 @@ def test_linear_stream_float32(ops, M, N, K):
     ops.check_device_errors()
 
 
+def test_linear_stream_float32_at_random_shapes(ops):
+    """Forty shapes drawn at random (1 to 64 rows, widths and lengths that are no multiples of a tile, K in steps of 4)
+    through whichever kernel the library picks for them, beside float64; bias, residual sum and GELU at every second."""
+    import random
+    rng = random.Random(7)
+    seen = set()
+    for i in range(40):
+        M = rng.choice([1, 2, 3, 5, 8, 9, 15, 16, 17, 23, 24, 25, 31, 32, 33, 47, 48, 49, 63, 64])
+        N = rng.choice([rng.randint(1, 300), rng.randint(300, 2400), rng.randint(2400, 7000)])
+        K = 4 * rng.choice([rng.randint(1, 64), rng.randint(64, 512), rng.randint(512, 1800)])
+        seen.add(ops.library().mllm_linear_stream_f32_kernel_of(M, N, K))
+        x, w, b = rnd(M, K, seed=3 * i), rnd(N, K, seed=3 * i + 1, scale=K ** -0.5), rnd(N, seed=3 * i + 2)
+        ref = x.double() @ w.double().t() + b.double()
+        out = torch.full((M + 1, N + 1), 5.0, device=DEV)
+        if i % 2:
+            acc0 = rnd(M, N, seed=1000 + i)
+            out[:M, :N] = acc0
+            ops.linear(x, w, b, out=out[:M, :N], act="gelu_tanh", accumulate=True)
+            want = acc0.double() + torch.nn.functional.gelu(ref, approximate="tanh")
+        else:
+            ops.linear(x, w, b, out=out[:M, :N])
+            want = ref
+        assert (out[:M, :N].double() - want).abs().max() < 2e-5 * max(1.0, want.abs().max().item()), (M, N, K)
+        assert torch.all(out[M] == 5.0) and torch.all(out[:, N] == 5.0), (M, N, K)
+    assert seen == {0, 1, 2, 3}                       # every kernel of the file had its turn
+    ops.check_device_errors()
+
+
 @pytest.mark.parametrize("M,N,K,eps", [(1, 768, 768, 1e-5), (8, 2304, 768, 1e-5), (5, 1000, 96, 1e-6), (16, 320, 1600, 1e-5),
                                        (13, 50257, 64, 1e-3), (9, 200, 1024, 1e-5), (16, 4800, 2048, 1e-5),
                                        (8, 50257, 768, 1e-5), (11, 40000, 1600, 1e-5), (2, 50257, 1020, 1e-5)])
