@@ -97,7 +97,8 @@ template <> struct Exp<__nv_bfloat16> {
 };
 
 // Keys and values of a split can be staged in shared memory when a split's rows fit there: heads up to 64
-// (32 KB per CTA with a bfloat16 cache, 64 KB with a 32-bit one; dynamic shared memory).  The rows of one (page, head) are contiguous, so one thread brings each page's visible rows with one
+// (32 KB per CTA with a bfloat16 cache, 64 KB with a 32-bit one, or 32 KB there too with half a split staged at a time
+// once the grid is large; dynamic shared memory).  The rows of one (page, head) are contiguous, so one thread brings each page's visible rows with one
 // bulk copy (cp.async.bulk onto an mbarrier): no thread computes an address per key, no register is held while
 // the rows fly, and six CTAs fit an SM instead of four.  That pays as soon as the grid is larger than about two
 // CTAs per SM; smaller grids keep the rows in registers, one hop less on the way.  The arithmetic is the same
@@ -109,9 +110,12 @@ template <typename T, int LPK> struct Staged {
     static constexpr int CTAS = BYTES <= 32 * 1024 ? 6 : 3;                             // resident CTAs per SM to aim for
 };
 
-// ONE: every CTA takes exactly one split.  STG: keys and values go through shared memory.
-template <typename T, int LPK, int MODE, bool ONE, bool STG>
-__global__ void __launch_bounds__(THREADS, STG ? Staged<T, LPK>::CTAS : 0)
+// ONE: every CTA takes exactly one split.  STG: keys and values go through shared memory.  TWO: the staging area holds
+// half a split (possible where the lane groups take a split's keys in two rounds of 64: 32-bit heads of 64): the
+// halves are staged one after the other in the same 32 KB, so that six CTAs fit an SM instead of three; the second
+// half's rows are asked for (into L2) when the kernel starts.  Which keys meet in which order does not change.
+template <typename T, int LPK, int MODE, bool ONE, bool STG, bool TWO = false>
+__global__ void __launch_bounds__(THREADS, STG ? (TWO ? 6 : Staged<T, LPK>::CTAS) : 0)
 attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // written by kernels of this step: no __restrict__,
                    const T* v_pages,                                        // the compiler must not read them on the non-coherent path
                    const int* __restrict__ block_table, int bt_stride,
@@ -131,6 +135,8 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
     constexpr bool PUSH = MODE == MODE_CLUSTER && ONE;
     constexpr bool STAGE = STG;
     static_assert(!STG || Staged<T, LPK>::value, "a split's rows do not fit the staging area");
+    static_assert(!TWO || (STG && NG * UNR * 2 == SPLIT), "two rounds of staging need groups that take a split in two rounds");
+    constexpr int STAGE_KEYS = TWO ? SPLIT / 2 : SPLIT;       // keys that the staging area holds
     __shared__ float sm_m[NG], sm_l[NG], sm_w[NG];
     extern __shared__ __align__(16) uint4 s_stage[];          // STAGE: a split's keys, then its values: [key][16-byte piece]
     __shared__ float sm_o_own[STAGE ? 1 : NG * DH];
@@ -205,13 +211,14 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
         for (int i = 0; i < VEC; ++i) qv[i] *= scale * Exp<T>::QSCALE;
     };
 
-    if constexpr (!ONE) {
+    if constexpr (!ONE || TWO) {
         // A CTA that walks several splits asks for the rows of its later splits right away (into L2), one
-        // key per thread, so that HBM streams them while the first splits are computed.
+        // key per thread, so that HBM streams them while the first splits are computed; with half a split
+        // staged at a time that goes for everything beyond the first half.
         const int k_end = min((my_hi + 1) * SPLIT, p + 1);
         constexpr int ROW_BYTES = DH * (int)sizeof(T);
 #pragma unroll 4
-        for (int kp = (my_lo + 1) * SPLIT + (int)threadIdx.x; kp < k_end; kp += THREADS) {
+        for (int kp = my_lo * SPLIT + STAGE_KEYS + (int)threadIdx.x; kp < k_end; kp += THREADS) {
             if (kp < first) continue;
             const size_t off = (((size_t)__ldcg(bt + page_index(kp)) * Hkv + hk) * page_size + page_offset(kp)) * DH;
 #pragma unroll
@@ -229,40 +236,49 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
 #pragma unroll
         for (int i = 0; i < VEC; ++i) o[i] = 0.f;
         uint4* sk = s_stage;
-        uint4* sv = s_stage + SPLIT * LPK;
-        if constexpr (STAGE) {
-            // The split's visible rows [v_lo, k_hi), page by page: thread c brings the rows of the c-th page that
-            // the range touches.  Rows of earlier steps go out before the wait on the previous kernel, the
-            // token's own row (position p) after it.  Rows that are not visible are not copied: their places
-            // hold whatever was there, and the arithmetic below skips them.
+        uint4* sv = s_stage + STAGE_KEYS * LPK;
+        // Brings the visible rows of [lo, hi) into the staging area (row r to place r - lo), page by page: thread c
+        // brings the rows of the c-th page that the range touches.  Rows of earlier steps go out before the wait on
+        // the previous kernel, the token's own row (position p) after it.  Rows that are not visible are not
+        // copied: their places hold whatever was there, and the arithmetic below skips them.
+        auto stage = [&](int lo, int hi) {
             constexpr uint32_t ROW = DH * (uint32_t)sizeof(T);
-            const int v_lo = max(k_lo, first);
-            const int pre_hi = min(k_hi, p);
-            if (threadIdx.x == 0) tc::mbar_expect_tx(&s_bar, (uint32_t)(k_hi - v_lo) * ROW * 2);
+            const int v_lo = max(lo, first);
+            const int pre_hi = min(hi, p);
+            if (threadIdx.x == 0) tc::mbar_expect_tx(&s_bar, (uint32_t)max(0, hi - v_lo) * ROW * 2);
             if (pre_hi > v_lo) {
                 const int pg0 = page_index(v_lo), pg1 = page_index(pre_hi - 1);
                 for (int pg = pg0 + (int)threadIdx.x; pg <= pg1; pg += THREADS) {
                     const int r0 = max(v_lo, pg * page_size), r1 = min(pre_hi, (pg + 1) * page_size);
                     const size_t off = (((size_t)__ldcg(bt + pg) * Hkv + hk) * page_size + (r0 - pg * page_size)) * DH;
                     const uint32_t bytes = (uint32_t)(r1 - r0) * ROW;
-                    tc::bulk_load(sk + (r0 - k_lo) * LPK, k_pages + off, bytes, &s_bar);
-                    tc::bulk_load(sv + (r0 - k_lo) * LPK, v_pages + off, bytes, &s_bar);
+                    tc::bulk_load(sk + (r0 - lo) * LPK, k_pages + off, bytes, &s_bar);
+                    tc::bulk_load(sv + (r0 - lo) * LPK, v_pages + off, bytes, &s_bar);
                 }
             }
             if (!waited) wait_and_load_q();
-            if (threadIdx.x == 0 && p >= v_lo && p < k_hi) {
+            if (threadIdx.x == 0 && p >= v_lo && p < hi) {
                 const size_t off = (((size_t)__ldcg(bt + page_index(p)) * Hkv + hk) * page_size + page_offset(p)) * DH;
-                tc::bulk_load(sk + (p - k_lo) * LPK, k_pages + off, ROW, &s_bar);
-                tc::bulk_load(sv + (p - k_lo) * LPK, v_pages + off, ROW, &s_bar);
+                tc::bulk_load(sk + (p - lo) * LPK, k_pages + off, ROW, &s_bar);
+                tc::bulk_load(sv + (p - lo) * LPK, v_pages + off, ROW, &s_bar);
             }
             if (!tc::mbar_wait(&s_bar, phase)) {              // gave up: tell the host, let copies in flight land, go on
                 if (threadIdx.x == 0) { atomicCAS(&g_decode_error, 0, 1); tc::report_to_host(301); }
                 for (int i = 0; i < 2000; ++i) __nanosleep(100);
             }
             phase ^= 1;
-        }
+        };
+        if constexpr (STAGE && !TWO) stage(k_lo, k_hi);
 #pragma unroll 1
         for (int kb = k_lo + gi; kb < k_lo + SPLIT; kb += NG * UNR) {   // same trip count for every lane
+            const int s_base = TWO ? kb - gi : k_lo;          // the key whose row lies first in the staging area
+            if constexpr (TWO) {
+                if (s_base > k_lo) {                          // second round: every group has left the first half
+                    tc::fence_async_smem();
+                    __syncthreads();
+                }
+                stage(s_base, min(s_base + STAGE_KEYS, k_hi));
+            }
             bool ok[UNR];
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
@@ -298,14 +314,14 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
                 float d = 0.f;
                 if constexpr (MIXED) {
                     // bfloat16 x bfloat16 + 32-bit in one instruction: the products are exact, nothing is unpacked
-                    const uint4 kw = sk[(kb + u * NG - k_lo) * LPK + li];
+                    const uint4 kw = sk[(kb + u * NG - s_base) * LPK + li];
                     d = dot2_bf16(qw.x, kw.x, d);
                     d = dot2_bf16(qw.y, kw.y, d);
                     d = dot2_bf16(qw.z, kw.z, d);
                     d = dot2_bf16(qw.w, kw.w, d);
                 } else {
                     float kv[VEC];
-                    if constexpr (STAGE) Vec16<T>::unpack(sk[(kb + u * NG - k_lo) * LPK + li], kv);
+                    if constexpr (STAGE) Vec16<T>::unpack(sk[(kb + u * NG - s_base) * LPK + li], kv);
                     else Vec16<T>::unpack(kr[u], kv);
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) d = fmaf(qv[i], kv[i], d);
@@ -326,7 +342,7 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
                     if (STAGE && !ok[u]) continue;            // nothing was copied to this key's place
                     const float pr = ok[u] ? Exp<T>::of(s[u] - mx) : 0.f;
                     float vv[VEC];
-                    if constexpr (STAGE) Vec16<T>::unpack(sv[(kb + u * NG - k_lo) * LPK + li], vv);
+                    if constexpr (STAGE) Vec16<T>::unpack(sv[(kb + u * NG - s_base) * LPK + li], vv);
                     else Vec16<T>::unpack(vr[u], vv);
                     l += pr;
 #pragma unroll
@@ -460,6 +476,8 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
     }
 }
 
+int g_last_staging = 0;   // how the most recent launch staged keys and values: 0 not, 1 a split at a time, 2 half a split
+
 int decode_sm_count() {
     static int n = 0;
     if (!n) {
@@ -499,15 +517,24 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
     const int mode = scratch_path ? MODE_SCRATCH : ctas == 1 ? MODE_LOCAL : ctas <= MAX_CLUSTER ? MODE_CLUSTER : MODE_SCRATCH;
     const bool one = spc == 1 && mode != MODE_LOCAL;
     K kern;
+    // Half a split staged at a time (32-bit heads of 64) lets six CTAs share an SM instead of three, at the price of a
+    // second round of copies (from L2) per split.  Measured at contexts of 520 and 1,000: it loses while the grid is
+    // small (5.3 against 6.4 us at 240 CTAs) and wins from about two CTAs per SM on (8.7 against 8.2 us at 384 CTAs,
+    // 10.3 against 8.3 us at 480, where 96 clusters of 5 with 64 KB each do not fit the SMs at once; 54 against 47 us
+    // with one CTA for each of 768 pairs).  The bits are the same either way.
+    constexpr bool CAN_TWO = CAN_STAGE && Staged<T, LPK>::BYTES > 32 * 1024 && LPK == 16 && sizeof(T) == 4;
+    const bool two = CAN_TWO && stg && pairs * ctas > 2LL * decode_sm_count();
+    g_last_staging = two ? 2 : stg ? 1 : 0;
 #define PICK(M, O)                                                                     \
-    kern = stg ? (K)attn_decode_kernel<T, LPK, M, O, CAN_STAGE> : (K)attn_decode_kernel<T, LPK, M, O, false>
+    kern = two ? (K)attn_decode_kernel<T, LPK, M, O, CAN_TWO, CAN_TWO>                 \
+         : stg ? (K)attn_decode_kernel<T, LPK, M, O, CAN_STAGE> : (K)attn_decode_kernel<T, LPK, M, O, false>
     if (mode == MODE_LOCAL) PICK(MODE_LOCAL, false);
     else if (mode == MODE_CLUSTER && one) PICK(MODE_CLUSTER, true);
     else if (mode == MODE_CLUSTER) PICK(MODE_CLUSTER, false);
     else if (one) PICK(MODE_SCRATCH, true);
     else PICK(MODE_SCRATCH, false);
 #undef PICK
-    const size_t smem = stg ? (size_t)Staged<T, LPK>::BYTES : 0;
+    const size_t smem = stg ? (size_t)Staged<T, LPK>::BYTES / (two ? 2 : 1) : 0;
     if (smem > 48 * 1024) MLLM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (mode == MODE_CLUSTER) {
         cudaLaunchConfig_t cfg = {};
@@ -535,6 +562,10 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
 }  // namespace
 
 MLLM_EXPORT int mllm_attention_decode_split_len() { return SPLIT; }
+
+// How the most recent launch of this file's kernel staged keys and values in shared memory: 0 not at all, 1 a split at a
+// time, 2 half a split at a time (for tests of the arrangements).
+MLLM_EXPORT int mllm_attention_decode_last_staging() { return g_last_staging; }
 
 // The pinned host word that this file's kernels write when they give up on a wait.
 MLLM_EXPORT int mllm_attention_decode_bind_error(int* word) { return tc::bind_host_error(word); }

@@ -73,6 +73,7 @@ def _signatures(lib):
         "mllm_attention_decode": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                   c_int, c_int, c_int, c_int, c_void_p],
+        "mllm_attention_decode_last_staging": [],
         "mllm_attention_flash": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                  c_void_p, c_ll, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mllm_attention_tcgen05": [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,

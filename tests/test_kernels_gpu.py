@@ -562,6 +562,8 @@ def test_decode_attention_split_keys(ops, dtype, H, Hkv, dh, page, window):
         o1 = torch.empty_like(q[t:t + 1])
         ops.paged_attention(q[t:t + 1], kp, vp, bt, c1, o1, impl="decode", **kw)
         assert torch.equal(o1, out[t:t + 1])
+        if dtype == torch.float32 and dh == 64:               # a small grid stages a split at a time
+            assert ops.library().mllm_attention_decode_last_staging() == 1
     # nor on the size of the batch: with many tokens a CTA walks several splits (down to one CTA per token
     # and head), with few every split has its own CTA; the bits stay the same
     for reps in (4, 20):
@@ -572,6 +574,8 @@ def test_decode_attention_split_keys(ops, dtype, H, Hkv, dh, page, window):
         ob = torch.empty_like(qb)
         ops.paged_attention(qb, kp, vp, bt, cb, ob, impl="decode", **kw)
         assert torch.equal(ob, out.repeat(reps, 1))
+        if dtype == torch.float32 and dh == 64:               # a large one half a split at a time: the same bits
+            assert ops.library().mllm_attention_decode_last_staging() == 2
         ops.paged_attention(qb, kp, vp, bt, cb, ob.zero_(), impl="decode_scratch", **kw)
         assert torch.equal(ob, out.repeat(reps, 1))
 
