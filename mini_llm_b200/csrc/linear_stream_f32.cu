@@ -560,13 +560,25 @@ linear_stream_f32_tall_kernel(const float* x, long long ldx, const float* __rest
                 else if (accumulate) e_old = __ldcg(out + (size_t)e_m * ldo + e_n);
             }
             const float* xp = xs + (size_t)m0 * KS + lane * 4;
-            if (M - m0 > 2) {
+            if (M - m0 > 4) {
                 // all 8 rows of the pass without a branch between the reads (rows beyond M hold zeros)
 #pragma unroll
                 for (int c = 0; c < KP; ++c) {
                     if (c * 128 < K) {
 #pragma unroll
                         for (int m = 0; m < 8; ++m) {
+                            const float4 xv = *reinterpret_cast<const float4*>(xp + (size_t)m * KS + c * 128);
+#pragma unroll
+                            for (int r = 0; r < RW; ++r) acc[r * 8 + m] = dot4(w[r][c], xv, acc[r * 8 + m]);
+                        }
+                    }
+                }
+            } else if (M - m0 > 2) {                         // three or four rows: the first four
+#pragma unroll
+                for (int c = 0; c < KP; ++c) {
+                    if (c * 128 < K) {
+#pragma unroll
+                        for (int m = 0; m < 4; ++m) {
                             const float4 xv = *reinterpret_cast<const float4*>(xp + (size_t)m * KS + c * 128);
 #pragma unroll
                             for (int r = 0; r < RW; ++r) acc[r * 8 + m] = dot4(w[r][c], xv, acc[r * 8 + m]);
