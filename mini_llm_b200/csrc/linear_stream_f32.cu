@@ -704,14 +704,31 @@ linear_stream_f32_regs_kernel(const float* x, long long ldx, const float* __rest
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[i] = 0.f;
             const float* xp = xs + (size_t)p * 8 * KC + lane * 4;
+            const int rows = M - p * 8;                       // rows of x in this pass (8 or more: all 8)
+            if (rows > 4) {
 #pragma unroll
-            for (int col = 0; col < KP; ++col) {
-                if (col * 128 < len) {
+                for (int col = 0; col < KP; ++col) {
+                    if (col * 128 < len) {
 #pragma unroll
-                    for (int m = 0; m < 8; ++m) {
-                        const float4 xv = *reinterpret_cast<const float4*>(xp + (size_t)m * KC + col * 128);
+                        for (int m = 0; m < 8; ++m) {
+                            const float4 xv = *reinterpret_cast<const float4*>(xp + (size_t)m * KC + col * 128);
 #pragma unroll
-                        for (int r = 0; r < RW; ++r) acc[r * 8 + m] = dot4(w[r][col], xv, acc[r * 8 + m]);
+                            for (int r = 0; r < RW; ++r) acc[r * 8 + m] = dot4(w[r][col], xv, acc[r * 8 + m]);
+                        }
+                    }
+                }
+            } else {                                          // up to four rows: the first two, then the next two if any
+#pragma unroll
+                for (int col = 0; col < KP; ++col) {
+                    if (col * 128 < len) {
+#pragma unroll
+                        for (int m = 0; m < 4; ++m) {
+                            if (m < 2 || rows > 2) {
+                                const float4 xv = *reinterpret_cast<const float4*>(xp + (size_t)m * KC + col * 128);
+#pragma unroll
+                                for (int r = 0; r < RW; ++r) acc[r * 8 + m] = dot4(w[r][col], xv, acc[r * 8 + m]);
+                            }
+                        }
                     }
                 }
             }
