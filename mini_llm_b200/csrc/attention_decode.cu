@@ -211,15 +211,12 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
         for (int i = 0; i < VEC; ++i) qv[i] *= scale * Exp<T>::QSCALE;
     };
 
-    if constexpr (!ONE || TWO) {
-        // A CTA that walks several splits asks for the rows of its later splits right away (into L2), one
-        // key per thread, so that HBM streams them while the first splits are computed; with half a split
-        // staged at a time that goes for everything beyond the first half.
-        const int k_end = min((my_hi + 1) * SPLIT, p + 1);
+    // Asks for the rows of the keys [lo, hi) that this CTA will come to (visible ones only) to be brought into L2, one
+    // key per thread.
+    auto ask_for = [&](int lo, int hi) {
         constexpr int ROW_BYTES = DH * (int)sizeof(T);
-#pragma unroll 4
-        for (int kp = my_lo * SPLIT + STAGE_KEYS + (int)threadIdx.x; kp < k_end; kp += THREADS) {
-            if (kp < first) continue;
+        hi = min(hi, min((my_hi + 1) * SPLIT, p + 1));
+        for (int kp = max(lo, first) + (int)threadIdx.x; kp < hi; kp += THREADS) {
             const size_t off = (((size_t)__ldcg(bt + page_index(kp)) * Hkv + hk) * page_size + page_offset(kp)) * DH;
 #pragma unroll
             for (int b = 0; b < ROW_BYTES; b += 128) {
@@ -227,6 +224,15 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(v_pages + off) + b));
             }
         }
+    };
+    if constexpr (TWO) {
+        // half a split staged at a time: the half after the first one now, every later half two rounds before its turn
+        // (asking for all of them at once evicts them again when many CTAs do it: 274 MB read for 201 MB at batch 64)
+        ask_for(my_lo * SPLIT + STAGE_KEYS, my_lo * SPLIT + 2 * STAGE_KEYS);
+    } else if constexpr (!ONE) {
+        // A CTA that walks several splits asks for the rows of its next split right away and for every later one two
+        // splits before its turn, so that HBM streams them while the splits before are computed.
+        ask_for((my_lo + 1) * SPLIT, (my_lo + 2) * SPLIT);
     }
 
 #pragma unroll 1
@@ -269,6 +275,7 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
             phase ^= 1;
         };
         if constexpr (STAGE && !TWO) stage(k_lo, k_hi);
+        if constexpr (!ONE && !TWO) ask_for((split + 2) * SPLIT, (split + 3) * SPLIT);
 #pragma unroll 1
         for (int kb = k_lo + gi; kb < k_lo + SPLIT; kb += NG * UNR) {   // same trip count for every lane
             const int s_base = TWO ? kb - gi : k_lo;          // the key whose row lies first in the staging area
@@ -278,6 +285,7 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
                     __syncthreads();
                 }
                 stage(s_base, min(s_base + STAGE_KEYS, k_hi));
+                ask_for(s_base + 2 * STAGE_KEYS, s_base + 3 * STAGE_KEYS);     // the half after the next one
             }
             bool ok[UNR];
 #pragma unroll
