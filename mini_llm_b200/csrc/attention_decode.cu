@@ -6,9 +6,9 @@
 // from position 0, so which keys are added together never depends on the batch.
 // Inside a CTA (4 warps) a group of LPK lanes owns one key at a time: each lane takes
 // 16 bytes of the key row and of the value row (the cache layout keeps one
-// (page, head, slot) row contiguous).  With a bfloat16 cache and heads up to 64 a
-// split's rows are first brought into shared memory by bulk copies, one per page (see
-// Staged below); otherwise a group fetches the page ids of all its keys, then issues
+// (page, head, slot) row contiguous).  With heads up to 64 a split's rows (or, with a
+// 32-bit cache and a large grid, half a split's at a time) are first brought into shared
+// memory by bulk copies, one per page (see Staged below); otherwise a group fetches the page ids of all its keys, then issues
 // all its key and value loads at once (up to 8 keys in flight per group), and only
 // then starts computing.  Either way it is three dependent memory round trips per CTA
 // instead of two per key.  The group reduces each dot product with shuffles and keeps its
@@ -26,7 +26,9 @@
 // SM-to-SM network in split order and writes the result; no scratch in global memory, no
 // fence, no counter.  With few (token, head) pairs every split gets a CTA of its own; with
 // many, a CTA walks up to 8 splits one after the other (the other resident CTAs hide its
-// waits), down to one CTA per pair, which then needs no cluster at all.  The partial
+// waits, and it asks for the rows two splits ahead into L2: not for all of them at once,
+// which with hundreds of CTAs evicts them again), down to one CTA per pair, which then
+// needs no cluster at all.  The partial
 // results and the order of their merge are the same in every arrangement, so a token's
 // result does not depend on the size of the batch.  Longer contexts use the scratch path.
 #include "common.cuh"
