@@ -26,9 +26,7 @@
 // SM-to-SM network in split order and writes the result; no scratch in global memory, no
 // fence, no counter.  With few (token, head) pairs every split gets a CTA of its own; with
 // many, a CTA walks up to 8 splits one after the other (the other resident CTAs hide its
-// waits, and it asks for the rows two splits ahead into L2: not for all of them at once,
-// which with hundreds of CTAs evicts them again), down to one CTA per pair, which then
-// needs no cluster at all.  The partial
+// waits), down to one CTA per pair, which then needs no cluster at all.  The partial
 // results and the order of their merge are the same in every arrangement, so a token's
 // result does not depend on the size of the batch.  Longer contexts use the scratch path.
 #include "common.cuh"
@@ -114,8 +112,8 @@ template <typename T, int LPK> struct Staged {
 
 // ONE: every CTA takes exactly one split.  STG: keys and values go through shared memory.  TWO: the staging area holds
 // half a split (possible where the lane groups take a split's keys in two rounds of 64: 32-bit heads of 64): the
-// halves are staged one after the other in the same 32 KB, so that six CTAs fit an SM instead of three; the second
-// half's rows are asked for (into L2) when the kernel starts.  Which keys meet in which order does not change.
+// halves are staged one after the other in the same 32 KB, so that six CTAs fit an SM instead of three.  Which keys
+// meet in which order does not change.
 template <typename T, int LPK, int MODE, bool ONE, bool STG, bool TWO = false>
 __global__ void __launch_bounds__(THREADS, STG ? (TWO ? 6 : Staged<T, LPK>::CTAS) : 0)
 attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // written by kernels of this step: no __restrict__,
@@ -227,15 +225,12 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
             }
         }
     };
-    if constexpr (TWO) {
-        // half a split staged at a time: the half after the first one now, every later half two rounds before its turn
-        // (asking for all of them at once evicts them again when many CTAs do it: 274 MB read for 201 MB at batch 64)
-        ask_for(my_lo * SPLIT + STAGE_KEYS, my_lo * SPLIT + 2 * STAGE_KEYS);
-    } else if constexpr (!ONE) {
-        // A CTA that walks several splits asks for the rows of its next split right away and for every later one two
-        // splits before its turn, so that HBM streams them while the splits before are computed.
-        ask_for((my_lo + 1) * SPLIT, (my_lo + 2) * SPLIT);
-    }
+    // Only CTAs that load rows straight into registers ask for later splits ahead of time (the next one now, each later
+    // one two splits before its turn).  With staging through shared memory the bulk copies of the resident CTAs keep
+    // HBM busy by themselves, and asking ahead made every large grid slower: all later splits at once evicted each
+    // other from L2 (274 MB read for 201 MB of cache at batch 64), two rounds ahead still cost 7-8 % against none
+    // (39.5 against 36.5 us in float32, 22.7 against 22.0 us in bfloat16 at batch 64).
+    if constexpr (!ONE && !STAGE) ask_for((my_lo + 1) * SPLIT, (my_lo + 2) * SPLIT);
 
 #pragma unroll 1
     for (int split = my_lo; split <= my_hi; ++split) {
@@ -277,7 +272,7 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
             phase ^= 1;
         };
         if constexpr (STAGE && !TWO) stage(k_lo, k_hi);
-        if constexpr (!ONE && !TWO) ask_for((split + 2) * SPLIT, (split + 3) * SPLIT);
+        if constexpr (!ONE && !STAGE) ask_for((split + 2) * SPLIT, (split + 3) * SPLIT);
 #pragma unroll 1
         for (int kb = k_lo + gi; kb < k_lo + SPLIT; kb += NG * UNR) {   // same trip count for every lane
             const int s_base = TWO ? kb - gi : k_lo;          // the key whose row lies first in the staging area
@@ -287,7 +282,6 @@ attn_decode_kernel(const T* q, long long q_stride, const T* k_pages,      // wri
                     __syncthreads();
                 }
                 stage(s_base, min(s_base + STAGE_KEYS, k_hi));
-                ask_for(s_base + 2 * STAGE_KEYS, s_base + 3 * STAGE_KEYS);     // the half after the next one
             }
             bool ok[UNR];
 #pragma unroll
