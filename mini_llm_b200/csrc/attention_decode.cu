@@ -522,12 +522,13 @@ int launch(const void* q, long long q_stride, const void* k_pages, const void* v
     const bool one = spc == 1 && mode != MODE_LOCAL;
     K kern;
     // Half a split staged at a time (32-bit heads of 64) lets six CTAs share an SM instead of three, at the price of a
-    // second round of copies (from L2) per split.  Measured at contexts of 520 and 1,000: it loses while the grid is
-    // small (5.3 against 6.4 us at 240 CTAs) and wins from about two CTAs per SM on (8.7 against 8.2 us at 384 CTAs,
-    // 10.3 against 8.3 us at 480, where 96 clusters of 5 with 64 KB each do not fit the SMs at once; 54 against 47 us
-    // with one CTA for each of 768 pairs).  The bits are the same either way.
+    // second round of copies per split.  Measured at contexts of 520 and 1,000: it loses while the whole-split CTAs
+    // still fit the SMs at once (5.3 against 6.4 us at 240 CTAs, 6.0 against 7.4 us at 300, 6.6 against 7.9 us at 360)
+    // and wins beyond (8.7 against 8.2 us at 384 CTAs in clusters of 8, 10.3 against 8.5 us at 480, where 96 clusters
+    // of 5 with 64 KB each need a second wave; 54 against 36 us with one CTA for each of 768 pairs): from two and a
+    // half CTAs per SM on.  The bits are the same either way.
     constexpr bool CAN_TWO = CAN_STAGE && Staged<T, LPK>::BYTES > 32 * 1024 && LPK == 16 && sizeof(T) == 4;
-    const bool two = CAN_TWO && stg && pairs * ctas > 2LL * decode_sm_count();
+    const bool two = CAN_TWO && stg && 2 * pairs * ctas > 5LL * decode_sm_count();
     g_last_staging = two ? 2 : stg ? 1 : 0;
 #define PICK(M, O)                                                                     \
     kern = two ? (K)attn_decode_kernel<T, LPK, M, O, CAN_TWO, CAN_TWO>                 \
